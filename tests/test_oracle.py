@@ -1,0 +1,86 @@
+"""CPU tests of the oracle: pinned to the reference-generated golden vectors, and self-consistent
+(closed-form backward == autograd backward)."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import diffattn_oracle as oracle
+
+GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
+GRADS = ("dq1", "dq2", "dk1", "dk2", "dv")
+
+
+def _load(path):
+    z = np.load(path)
+    b, h, n, d, seed = (int(x) for x in z["meta"])
+    scale, lam, lam_init, rms, dyu = (float(x) for x in z["fmeta"])
+    return z, (b, h, n, d, seed, scale, lam, lam_init, bool(rms), bool(dyu)), int(z["row_step"][0])
+
+
+def test_golden_files_present():
+    assert len(GOLDEN) >= 5
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[:-4] for p in GOLDEN])
+def test_oracle_literal_mode_matches_reference_golden(path):
+    """round_p_half=True follows the reference's .half() on P (src/layers.py:65,68) and must
+    reproduce the vectors the reference itself produced, to fp32 round-off."""
+    z, (b, h, n, d, seed, scale, lam, lam_init, rms, dyu), step = _load(path)
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(b, h, n, d, seed, scale, torch.float16, dyu)
+    got = oracle.forward_backward_autograd(q1, q2, k1, k2, v, torch.tensor([lam]), dy, lam_init, rms,
+                                           dtype=torch.float32, round_p_half=True)
+    for key in ("y",) + GRADS:
+        m = oracle.error_metrics(got[key][:, :, ::step, :], torch.from_numpy(z[key]))
+        assert m["rel_l2"] < 2e-5, (key, m)
+    want = float(z["dlambda"][0])
+    assert abs(float(got["dlambda"]) - want) <= 2e-4 * max(1.0, abs(want))
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[:-4] for p in GOLDEN])
+def test_oracle_fp32_mode_close_to_reference_golden(path):
+    """The pure-fp32 parity target differs from the literal reference only by the fp16 rounding of P:
+    a few 1e-4 relative (well inside the 1e-3 budget of the CUDA parity tests)."""
+    z, (b, h, n, d, seed, scale, lam, lam_init, rms, dyu), step = _load(path)
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(b, h, n, d, seed, scale, torch.float16, dyu)
+    got = oracle.backward_closed_form(q1, q2, k1, k2, v, torch.tensor([lam]), dy, lam_init, rms)
+    for key in ("y",) + GRADS:
+        m = oracle.error_metrics(got[key][:, :, ::step, :], torch.from_numpy(z[key]))
+        assert m["rel_l2"] < 6e-4, (key, m)
+    want = float(z["dlambda"][0])
+    assert abs(float(got["dlambda"]) - want) <= 5e-3 * max(1.0, abs(want))
+
+
+@pytest.mark.parametrize("rms,lam,lam_init", [(True, 0.5, 0.8), (False, 0.7, 0.2), (True, -0.5, 0.8),
+                                              (True, 0.0, 0.8), (True, 0.5, 1.0)])
+def test_closed_form_backward_equals_autograd_fp64(rms, lam, lam_init):
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(1, 2, 96, 16, seed=3, dtype=torch.float64)
+    lam_t = torch.tensor([lam], dtype=torch.float64)
+    a = oracle.backward_closed_form(q1, q2, k1, k2, v, lam_t, dy, lam_init, rms, dtype=torch.float64)
+    g = oracle.forward_backward_autograd(q1, q2, k1, k2, v, lam_t, dy, lam_init, rms, dtype=torch.float64)
+    for key in ("y",) + GRADS:
+        assert torch.allclose(a[key], g[key], rtol=1e-10, atol=1e-12), key
+    assert abs(float(a["dlambda"]) - float(g["dlambda"])) < 1e-10 * max(1.0, abs(float(g["dlambda"])))
+
+
+def test_lse_and_identities():
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(1, 1, 64, 16, seed=9, dtype=torch.float64)
+    lam = torch.tensor([0.3], dtype=torch.float64)
+    r = oracle.backward_closed_form(q1, q2, k1, k2, v, lam, dy, 0.8, False, dtype=torch.float64)
+    f = oracle.forward(q1, q2, k1, k2, v, lam, 0.8, False, dtype=torch.float64)
+    # softmax rows sum to one; exp(S - lse) reproduces P
+    s1 = (q1 @ k1.transpose(2, 3)) / 4.0
+    assert torch.allclose(torch.exp(s1 - f["lse1"][..., None]), f["p1"], atol=1e-12)
+    # E1 - lam E2 = rowsum(dA * A)
+    assert torch.allclose(r["e1"] - 0.3 * r["e2"], (r["da"] * f["a"]).sum(-1), atol=1e-10)
+    # rms off => lambda_init has no effect
+    f2 = oracle.forward(q1, q2, k1, k2, v, lam, 0.1, False, dtype=torch.float64)
+    assert torch.equal(f["y"], f2["y"])
+
+
+def test_empty_batch():
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(0, 2, 32, 16, seed=1, dtype=torch.float32)
+    f = oracle.forward(q1, q2, k1, k2, v, torch.tensor([0.5]), 0.8, True)
+    assert f["y"].shape == (0, 2, 32, 32)
