@@ -1,0 +1,94 @@
+/* C ABI of libdiffattn: differential attention forward/backward for NVIDIA B200 (sm_100a).
+ *
+ * This is the boundary the Python autograd function binds with ctypes.  It stands where the
+ * reference's autograd Function launches its Triton kernels:
+ *   diffattn_fwd  <->  _diff_attention.forward  (reference src/kernel.py:463-514, kernel :21-207)
+ *   diffattn_bwd  <->  _diff_attention.backward (reference src/kernel.py:516-575, kernel :221-458)
+ * The caller owns every buffer; the library allocates nothing on the device.  All device work is
+ * enqueued on `stream`; no call synchronises the host with the device except diffattn_status().
+ * Every function returns 0 on success or a negative DIFFATTN_ERR_* code; nothing is launched after a
+ * failed check.  diffattn_last_error() gives the message of the calling thread's last failure.
+ */
+#ifndef DIFFATTN_H_
+#define DIFFATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DIFFATTN_VERSION 1
+
+enum {
+  DIFFATTN_OK = 0,
+  DIFFATTN_ERR_NULL_PTR = -1,
+  DIFFATTN_ERR_BAD_STRUCT = -2,     /* struct_size does not match this library */
+  DIFFATTN_ERR_BAD_SHAPE = -3,      /* negative sizes, N not a multiple of 128 */
+  DIFFATTN_ERR_UNSUPPORTED_D = -4,  /* head dim not compiled in */
+  DIFFATTN_ERR_BAD_STRIDE = -5,     /* strides not a multiple of 8 elements (16 bytes) */
+  DIFFATTN_ERR_MISALIGNED = -6,     /* base pointer not 16-byte aligned */
+  DIFFATTN_ERR_BAD_DTYPE = -7,      /* lambda dtype tag unknown */
+  DIFFATTN_ERR_WORKSPACE = -8,      /* workspace missing or too small */
+  DIFFATTN_ERR_CUDA = -9,           /* a CUDA runtime/driver call failed */
+  DIFFATTN_ERR_TIMEOUT = -10        /* a device-side wait gave up (reported by diffattn_status) */
+};
+
+enum { DIFFATTN_LAMBDA_F16 = 0, DIFFATTN_LAMBDA_F32 = 1 };
+
+/* q1,q2,k1,k2: fp16 [B,H,N,D] sharing one set of element strides (last dim contiguous), as the
+ * reference takes them from Q1 alone (src/kernel.py:487-490).  v: fp16 [B,H,N,2D] with its own
+ * strides (src/kernel.py:491-494).  Everything the library writes is dense row-major:
+ * y, a2, dy, dv [B,H,N,2D] fp16; dq1,dq2,dk1,dk2 [B,H,N,D] fp16; lse1,lse2,rstd [B,H,N] fp32. */
+typedef struct DiffAttnParams {
+  uint32_t struct_size;            /* sizeof(DiffAttnParams) */
+  int32_t device;                  /* CUDA device ordinal owning all pointers */
+  void* stream;                    /* cudaStream_t */
+  int32_t B, H, N, D;
+  int64_t qk_stride_b, qk_stride_h, qk_stride_n;   /* in elements */
+  int64_t v_stride_b, v_stride_h, v_stride_n;
+  const void* q1; const void* q2; const void* k1; const void* k2; const void* v;
+  const void* lambda_scale;        /* device pointer to ONE element (src/kernel.py:138,496) */
+  int32_t lambda_dtype;            /* DIFFATTN_LAMBDA_* */
+  int32_t rms_norm;                /* 0/1; (1 - lambda_init) is applied only when 1 (src/layers.py:74-78) */
+  float sm_scale;                  /* 1/sqrt(D) (src/layers.py:20-22) */
+  float lambda_init;
+  float eps;                       /* 1e-5 (src/kernel.py:50) */
+  int32_t reserved0;
+  /* forward outputs (inputs of the backward) */
+  void* y; void* a2; float* lse1; float* lse2; float* rstd;
+  /* backward */
+  const void* dy;
+  void* dq1; void* dq2; void* dk1; void* dk2; void* dv;
+  float* dlambda;                  /* ONE fp32 on the device; the backward ADDS -sum(E2) into it */
+  void* workspace;                 /* diffattn_workspace_bytes() bytes, 256-byte aligned */
+  uint64_t workspace_bytes;
+} DiffAttnParams;
+
+/* Forward.  Reads q1,q2,k1,k2,v,lambda_scale; writes y,a2,lse1,lse2,rstd.
+ * Replaces _diff_attention.forward + diff_attn_fwd (reference src/kernel.py:463-514, :21-207). */
+int diffattn_fwd(const DiffAttnParams* p);
+
+/* Backward.  Reads the forward's inputs and outputs plus dy; writes dq1,dq2,dk1,dk2,dv and adds the
+ * lambda gradient into *dlambda (zero it first; partials of several shards add up on the host).
+ * Replaces _diff_attention.backward + diff_attn_bwd (reference src/kernel.py:516-575, :221-458). */
+int diffattn_bwd(const DiffAttnParams* p);
+
+/* Scratch bytes diffattn_bwd needs for these shapes (the reference allocates its D1/D2 and
+ * dLambda partial buffers itself, src/kernel.py:522-529).  The forward needs none. */
+uint64_t diffattn_workspace_bytes(const DiffAttnParams* p);
+
+/* Synchronises `device` and reads the device-side status word: 0, or DIFFATTN_ERR_TIMEOUT with the
+ * site in diffattn_last_error().  Clears the word.  (No counterpart in the reference.) */
+int diffattn_status(int32_t device);
+
+const char* diffattn_last_error(void);   /* thread-local, never NULL */
+int diffattn_version(void);
+/* 1 when head dim d is compiled in for the forward (dir 0) / backward (dir 1) */
+int diffattn_supports(int32_t d, int32_t dir);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DIFFATTN_H_ */

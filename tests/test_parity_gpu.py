@@ -1,0 +1,209 @@
+"""GPU parity tests: the sm_100a kernels, called through the Python operator (which goes through the
+C ABI), against the CPU oracle on the same seeded inputs.
+
+Tolerance (fp16 outputs and gradients against the fp32 oracle evaluated on the same fp16-rounded
+inputs): max-abs <= 2e-2 (times max|reference| where that exceeds 1) and relative L2 <= 1e-3; d(lambda) (a cancelling sum) relative <= 1e-2 of
+max(|dlambda|, 1e-3 * sum|E2|)."""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import diffattn_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS = 2e-2
+REL_L2 = 1e-3
+GRADS = ("dq1", "dq2", "dk1", "dk2", "dv")
+
+
+@pytest.fixture(scope="module")
+def op():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import triton_diff_attn_b200 as pkg     # raises if libdiffattn.so is missing: no fallback
+    return pkg
+
+
+def run_gpu(pkg, q1, q2, k1, k2, v, dy, lam, lam_init, rms, lam_dtype=torch.float32):
+    dev = torch.device("cuda", 0)
+    leaves = [t.to(dev).clone().requires_grad_(True) for t in (q1, q2, k1, k2, v)]
+    lam_t = torch.tensor([lam], dtype=lam_dtype, device=dev, requires_grad=True)
+    y = pkg.MultiheadDiffAttnKernel(*leaves, lam_t, lam_init, rms)
+    y.backward(dy.to(dev))
+    pkg.device_status(0)
+    out = {"y": y.detach().cpu()}
+    for nm, t in zip(GRADS, leaves):
+        out[nm] = t.grad.detach().cpu()
+    out["dlambda"] = float(lam_t.grad.float().cpu())
+    out["dlambda_fp32"] = float(pkg.DiffAttnFunction.last_dlambda_fp32.cpu())
+    return out
+
+
+def check(got, want, keys=("y",) + GRADS):
+    for k in keys:
+        m = oracle.error_metrics(got[k], want[k])
+        # the absolute bound is stated for O(1) values; it scales with the tensor's own magnitude
+        # when that exceeds 1 (peaky-softmax case: gradients reach several tens)
+        bound = MAX_ABS * max(1.0, float(want[k].abs().max()))
+        assert m["max_abs"] <= bound and m["rel_l2"] <= REL_L2, (k, m)
+    e2_abs = float(want["e2"].abs().sum())
+    tol = 1e-2 * max(abs(float(want["dlambda"])), 1e-3 * e2_abs)
+    assert abs(got["dlambda_fp32"] - float(want["dlambda"])) <= tol, (got["dlambda_fp32"], float(want["dlambda"]), tol)
+
+
+CASES = [
+    # b, h, n, d, scale, lam, lam_init, rms, seed
+    (1, 1, 128, 64, 1.0, 0.5, 0.8, True, 11),
+    (1, 2, 256, 64, 1.0, 0.5, 0.8, True, 12),
+    (2, 2, 512, 64, 1.0, 0.5, 0.8, True, 13),
+    (1, 2, 256, 64, 1.0, 0.5, 0.8, False, 14),
+    (1, 2, 384, 64, 1.0, 0.0, 0.8, True, 15),       # lambda = 0
+    (1, 2, 256, 64, 1.0, -0.5, 0.2, True, 16),      # negative lambda
+    (1, 1, 256, 64, 2.5, 0.7, 0.2, False, 17),      # peaky softmax: exercises the rescale path
+    (1, 1, 1024, 64, 0.5, 0.3, 0.8, True, 18),
+]
+
+
+@pytest.mark.parametrize("b,h,n,d,scale,lam,lam_init,rms,seed", CASES)
+def test_fwd_bwd_matches_oracle(op, b, h, n, d, scale, lam, lam_init, rms, seed):
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(b, h, n, d, seed, scale)
+    want = oracle.backward_closed_form(q1, q2, k1, k2, v, torch.tensor([lam]), dy, lam_init, rms)
+    got = run_gpu(op, q1, q2, k1, k2, v, dy, lam, lam_init, rms)
+    check(got, want)
+
+
+def test_saved_statistics(op):
+    """lse1/lse2/rstd/a2 written by the forward equal the oracle's."""
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(1, 2, 256, 64, 21)
+    want = oracle.forward(q1, q2, k1, k2, v, torch.tensor([0.5]), 0.8, True)
+    dev = torch.device("cuda", 0)
+    leaves = [t.to(dev).requires_grad_(True) for t in (q1, q2, k1, k2, v)]
+    lam_t = torch.tensor([0.5], device=dev, requires_grad=True)
+    y = op.MultiheadDiffAttnKernel(*leaves, lam_t, 0.8, True)
+    saved = y.grad_fn.saved_tensors
+    a2, lse1, lse2, rstd = (t.cpu() for t in saved[7:11])
+    assert torch.allclose(lse1, want["lse1"], atol=2e-3, rtol=0)
+    assert torch.allclose(lse2, want["lse2"], atol=2e-3, rtol=0)
+    assert oracle.error_metrics(rstd, want["rstd"])["rel_l2"] < 1e-3
+    assert oracle.error_metrics(a2, want["a2"])["rel_l2"] < 1e-3
+
+
+def test_lambda_init_one_gives_zero(op):
+    """c = 1 - lambda_init = 0 with rms_norm: Y = 0 and every gradient is exactly 0."""
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(1, 1, 128, 64, 22)
+    got = run_gpu(op, q1, q2, k1, k2, v, dy, 0.5, 1.0, True)
+    for k in ("y",) + GRADS:
+        assert float(got[k].abs().max()) == 0.0, k
+    assert got["dlambda_fp32"] == 0.0
+
+
+def test_lambda_fp16_tensor_and_grad_dtype(op):
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(1, 1, 128, 64, 23)
+    dev = torch.device("cuda", 0)
+    leaves = [t.to(dev).requires_grad_(True) for t in (q1, q2, k1, k2, v)]
+    lam_t = torch.tensor([0.5], dtype=torch.float16, device=dev, requires_grad=True)   # README.md:17
+    y = op.MultiheadDiffAttnKernel(*leaves, lam_t, rms_norm=True)
+    y.backward(dy.to(dev))
+    assert lam_t.grad.dtype == torch.float16 and lam_t.grad.shape == (1,)
+    assert y.dtype == torch.float16 and y.shape == (1, 1, 128, 128)
+
+
+def test_strided_inputs(op):
+    """[B,N,H,D]-resident tensors viewed as [B,H,N,D] go straight through the 4-D tensor maps."""
+    b, h, n, d = 2, 2, 256, 64
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(b, h, n, d, 24)
+    want = oracle.backward_closed_form(q1, q2, k1, k2, v, torch.tensor([0.5]), dy, 0.8, True)
+    dev = torch.device("cuda", 0)
+    def bnhd(t):
+        return t.to(dev).transpose(1, 2).contiguous().transpose(1, 2).requires_grad_(True)
+    leaves = [bnhd(t) for t in (q1, q2, k1, k2, v)]
+    assert not leaves[0].is_contiguous()
+    lam_t = torch.tensor([0.5], device=dev, requires_grad=True)
+    y = op.MultiheadDiffAttnKernel(*leaves, lam_t, 0.8, True)
+    y.backward(dy.to(dev))
+    got = {"y": y.detach().cpu(), "dlambda_fp32": float(op.DiffAttnFunction.last_dlambda_fp32.cpu())}
+    for nm, t in zip(GRADS, leaves):
+        got[nm] = t.grad.cpu()
+    check(got, want)
+
+
+def test_deterministic_repeat(op):
+    """Every output tile has one owner CTA: two runs agree bit for bit (d(lambda) up to atomic order)."""
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(1, 2, 512, 64, 25)
+    a = run_gpu(op, q1, q2, k1, k2, v, dy, 0.5, 0.8, True)
+    b = run_gpu(op, q1, q2, k1, k2, v, dy, 0.5, 0.8, True)
+    for k in ("y",) + GRADS:
+        assert torch.equal(a[k], b[k]), k
+    assert abs(a["dlambda_fp32"] - b["dlambda_fp32"]) <= 1e-4 * max(1.0, abs(a["dlambda_fp32"]))
+
+
+def test_reference_golden_selfcheck_tolerance(op, golden_dir):
+    """Against the vectors the reference's own PyTorch path produced, with the reference's own
+    acceptance test: allclose(atol=1e-2, rtol=0) (reference src/benchmark.py:293,312-316)."""
+    z = np.load(os.path.join(golden_dir, "small_d64_rms.npz"))
+    b, h, n, d, seed = (int(x) for x in z["meta"])
+    scale, lam, lam_init, rms, dyu = (float(x) for x in z["fmeta"])
+    step = int(z["row_step"][0])
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(b, h, n, d, seed, scale, torch.float16, bool(dyu))
+    got = run_gpu(op, q1, q2, k1, k2, v, dy, lam, lam_init, bool(rms))
+    for k in ("y",) + GRADS:
+        assert torch.allclose(got[k][:, :, ::step, :].float(), torch.from_numpy(z[k]), atol=1e-2, rtol=0), k
+    assert abs(got["dlambda_fp32"] - float(z["dlambda"][0])) <= 1e-2 * abs(float(z["dlambda"][0]))
+
+
+def test_full_size_properties_config2(op):
+    """BASELINE config 2 (B4 H16 N4096 D64): size-independent properties instead of a full oracle
+    pass, plus the oracle on one sampled (batch, head).
+      * heads are independent: the sampled head computed alone equals its slice of the full run;
+      * linearity in dY: backward(2 dY) = 2 backward(dY) exactly in fp16 (power-of-two scaling)."""
+    b, h, n, d = 4, 16, 4096, 64
+    g = torch.Generator(device="cpu").manual_seed(1234)
+    dev = torch.device("cuda", 0)
+    def draw(*s):
+        return torch.randn(*s, generator=g, dtype=torch.float32).to(torch.float16)
+    q1, q2, k1, k2 = (draw(b, h, n, d) for _ in range(4))
+    v, dy = draw(b, h, n, 2 * d), draw(b, h, n, 2 * d)
+    leaves = [t.to(dev).requires_grad_(True) for t in (q1, q2, k1, k2, v)]
+    lam_t = torch.tensor([0.5], device=dev, requires_grad=True)
+    y = op.MultiheadDiffAttnKernel(*leaves, lam_t, 0.8, True)
+    y.backward(dy.to(dev), retain_graph=True)
+    op.device_status(0)
+    full = {"y": y.detach().cpu()}
+    for nm, t in zip(GRADS, leaves):
+        full[nm] = t.grad.detach().cpu().clone()
+        t.grad = None
+    # linearity
+    y.backward((2 * dy).to(dev))
+    for nm, t in zip(GRADS, leaves):
+        assert torch.equal(t.grad.cpu(), 2 * full[nm]), nm
+    # sampled head against the oracle and against the full run
+    bi, hi = 2, 5
+    sl = lambda t: t[bi:bi + 1, hi:hi + 1].contiguous()
+    want = oracle.backward_closed_form(sl(q1), sl(q2), sl(k1), sl(k2), sl(v), torch.tensor([0.5]), sl(dy), 0.8, True)
+    for k in ("y",) + GRADS:
+        m = oracle.error_metrics(sl(full[k]), want[k])
+        assert m["max_abs"] <= MAX_ABS and m["rel_l2"] <= REL_L2, (k, m)
+    alone = run_gpu(op, sl(q1), sl(q2), sl(k1), sl(k2), sl(v), sl(dy), 0.5, 0.8, True)
+    for k in ("y",) + GRADS:
+        assert torch.equal(alone[k], sl(full[k])), k
+
+
+def test_errors_raise_without_launch(op):
+    dev = torch.device("cuda", 0)
+    q = torch.zeros(1, 1, 100, 64, dtype=torch.float16, device=dev)
+    v = torch.zeros(1, 1, 100, 128, dtype=torch.float16, device=dev)
+    lam = torch.tensor([0.5], device=dev)
+    with pytest.raises(ValueError, match="multiple of 128"):
+        op.MultiheadDiffAttnKernel(q, q, q, q, v, lam)
+    q = torch.zeros(1, 1, 128, 48, dtype=torch.float16, device=dev)
+    v = torch.zeros(1, 1, 128, 96, dtype=torch.float16, device=dev)
+    with pytest.raises(ValueError, match="UNSUPPORTED_D"):
+        op.MultiheadDiffAttnKernel(q, q, q, q, v, lam)
+    with pytest.raises(ValueError, match="float16"):
+        op.MultiheadDiffAttnKernel(q.float(), q, q, q, v, lam)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        op.MultiheadDiffAttnKernel(q.cpu(), q, q, q, v, lam)

@@ -1,0 +1,521 @@
+// Differential-attention backward for sm_100a, head dim D = 64 (value width 128).
+//
+// Three kernels replace the reference's single Triton backward (src/kernel.py:221-458):
+//   1. bwd_pre      per row: dA = RMSNorm-backward(dY) (src/kernel.py:283-290), E1, E2 row sums
+//                   (the reference's D1 and D2/(-lambda), :295-296), d(lambda) = -sum E2 with one
+//                   atomic per CTA (division-free; the reference divides by lambda+eps, :293).
+//   2. bwd_dkdv64   key/value-stationary: S^T, dP^T on tensor cores, dV += (P1-lam P2)^T dA,
+//                   dK_b += dS_b^T Q_b (src/kernel.py:410-424).
+//   3. bwd_dq64     query-stationary: dQ_b += dS_b K_b (src/kernel.py:426-436); every dQ tile has one
+//                   owner CTA, so the accumulation is race-free and deterministic.
+// Both tensor-core kernels recompute P_b = exp(s S_b - lse_b) from the saved logsumexp.
+#pragma once
+#include "sm100.cuh"
+#include "fwd.cuh"
+
+namespace da {
+
+struct BwdArgs {
+  const __half* y;      // [B*H, N, 2D]
+  const __half* a2;     // [B*H, N, 2D]
+  const __half* dy;     // [B*H, N, 2D] dense
+  const float* lse1;
+  const float* lse2;
+  const float* rstd;
+  __half* da;           // workspace [B*H, N, 2D]
+  float4* stats;        // workspace [B*H, N] = {lse1*log2e, lse2*log2e, E1, E2}
+  __half* dq1; __half* dq2; __half* dk1; __half* dk2; __half* dv;   // dense
+  float* dlambda;
+  const void* lambda_ptr;
+  int lambda_dtype;
+  float sm_scale;
+  float out_scale;      // 1 - lambda_init
+  int rms_norm;
+  int n;
+  int h;
+  long long rows;       // B*H*N
+};
+
+// ------------------------------------------------------------------------------------------------
+// 1. preprocess: one warp per row, DV = 32 * VPL halves per row
+// ------------------------------------------------------------------------------------------------
+template <int VPL>   // halves per lane: 2 (DV=64), 4 (DV=128), 8 (DV=256)
+__global__ void __launch_bounds__(256) diffattn_bwd_pre_kernel(const BwdArgs args) {
+  constexpr int DV = 32 * VPL;
+  constexpr float LOG2E = 1.4426950408889634f;
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const long long warps_total = (long long)gridDim.x * (blockDim.x >> 5);
+  const float lam = load_lambda(args.lambda_ptr, args.lambda_dtype);
+  const float c = args.out_scale;
+  float dl_acc = 0.f;
+  __shared__ float red[8];
+
+  for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + warp; row < args.rows; row += warps_total) {
+    const size_t off = size_t(row) * DV + lane * VPL;
+    float dy[VPL], yv[VPL], a2[VPL];
+    {
+      __half hd[VPL], hy[VPL], ha[VPL];
+      if constexpr (VPL == 8) {
+        *reinterpret_cast<uint4*>(hd) = *reinterpret_cast<const uint4*>(args.dy + off);
+        *reinterpret_cast<uint4*>(hy) = *reinterpret_cast<const uint4*>(args.y + off);
+        *reinterpret_cast<uint4*>(ha) = *reinterpret_cast<const uint4*>(args.a2 + off);
+      } else if constexpr (VPL == 4) {
+        *reinterpret_cast<uint2*>(hd) = *reinterpret_cast<const uint2*>(args.dy + off);
+        *reinterpret_cast<uint2*>(hy) = *reinterpret_cast<const uint2*>(args.y + off);
+        *reinterpret_cast<uint2*>(ha) = *reinterpret_cast<const uint2*>(args.a2 + off);
+      } else {
+        *reinterpret_cast<uint32_t*>(hd) = *reinterpret_cast<const uint32_t*>(args.dy + off);
+        *reinterpret_cast<uint32_t*>(hy) = *reinterpret_cast<const uint32_t*>(args.y + off);
+        *reinterpret_cast<uint32_t*>(ha) = *reinterpret_cast<const uint32_t*>(args.a2 + off);
+      }
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) { dy[i] = __half2float(hd[i]); yv[i] = __half2float(hy[i]); a2[i] = __half2float(ha[i]); }
+    }
+    float da[VPL], av[VPL];
+    if (args.rms_norm) {
+      // Y = c r A  =>  A = Y/(c r),  dA = r (c dY - Y (dY.Y) / (c Dv));  c == 0 gives dA = 0
+      float t = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) t += dy[i] * yv[i];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+      const float r = args.rstd[row];
+      const float inv_c = c != 0.f ? 1.f / c : 0.f;
+      const float k1 = r * c, k2 = r * inv_c * t * (1.f / DV), k3 = inv_c / r;
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) { da[i] = k1 * dy[i] - k2 * yv[i]; av[i] = yv[i] * k3; }
+    } else {
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) { da[i] = dy[i]; av[i] = yv[i]; }
+    }
+    // round dA to fp16 first: the row sums below must agree with what the MMAs will see
+    __half hda[VPL];
+    float e2 = 0.f, ea = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      hda[i] = __float2half_rn(da[i]);
+      const float d = __half2float(hda[i]);
+      e2 += d * a2[i];
+      ea += d * av[i];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      e2 += __shfl_xor_sync(0xffffffffu, e2, o);
+      ea += __shfl_xor_sync(0xffffffffu, ea, o);
+    }
+    if constexpr (VPL == 8) *reinterpret_cast<uint4*>(args.da + off) = *reinterpret_cast<uint4*>(hda);
+    else if constexpr (VPL == 4) *reinterpret_cast<uint2*>(args.da + off) = *reinterpret_cast<uint2*>(hda);
+    else *reinterpret_cast<uint32_t*>(args.da + off) = *reinterpret_cast<uint32_t*>(hda);
+    if (lane == 0) {
+      // E1 - lam E2 = rowsum(dA * A)
+      args.stats[row] = make_float4(args.lse1[row] * LOG2E, args.lse2[row] * LOG2E, ea + lam * e2, e2);
+      dl_acc -= e2;
+    }
+  }
+  if (lane == 0) red[warp] = dl_acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int i = 0; i < (blockDim.x >> 5); ++i) s += red[i];
+    atomicAdd(args.dlambda, s);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// 2. dK1, dK2, dV: one CTA = 128 key/value rows of one (batch, head); query tiles of 64 stream by.
+// TMEM: dV [0,128) dK1 [128,192) dK2 [192,256) S1^T [256,320) S2^T [320,384) dP^T [384,448).
+// Thread = key row.  Warpgroup g handles query columns [32g, 32g+32) of the three score tiles and
+// writes the fp16 A-operands back in place: (P1 - lam P2)^T over dP^T, dS_b^T over S_b^T, each at
+// column offset 32g (16 packed columns).
+// ------------------------------------------------------------------------------------------------
+namespace dkdv64 {
+constexpr int BKV = 128, BQ = 64, HD = 64, DV = 128, ST = 3;
+constexpr int K_BYTES = BKV * HD * 2;       // 16 KB
+constexpr int V_BYTES = BKV * DV * 2;       // 32 KB, two boxes of 16 KB
+constexpr int Q_BYTES = BQ * HD * 2;        // 8 KB
+constexpr int DA_BYTES = BQ * DV * 2;       // 16 KB, two boxes of 8 KB
+constexpr int STAT_BYTES = BQ * 16;         // 1 KB
+constexpr int STAGE_BYTES = 2 * Q_BYTES + DA_BYTES + STAT_BYTES;   // 33 KB
+constexpr int OFF_K1 = 0, OFF_K2 = K_BYTES, OFF_V = 2 * K_BYTES;
+constexpr int OFF_STAGE = OFF_V + V_BYTES;                         // 64 KB
+constexpr int OFF_MISC = OFF_STAGE + ST * STAGE_BYTES;
+constexpr int MISC_BYTES = 1024;
+constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
+constexpr int NUM_THREADS = 320;
+constexpr int T_DV = 0, T_DK1 = 128, T_DK2 = 192, T_S1 = 256, T_S2 = 320, T_DP = 384;
+struct Misc {
+  uint64_t bar_kv;
+  uint64_t full[ST], empty[ST];
+  uint64_t s_full, e_done, acc_full;
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+}  // namespace dkdv64
+
+__global__ void __launch_bounds__(dkdv64::NUM_THREADS, 1)
+diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
+                           const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k2,
+                           const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_da,
+                           const BwdArgs args) {
+  using namespace dkdv64;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Misc* misc = reinterpret_cast<Misc*>(smem + OFF_MISC);
+  volatile int* abort_flag = &misc->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kv_tile = blockIdx.x, bh = blockIdx.y;
+  const int b_idx = bh / args.h, h_idx = bh % args.h;
+  const int nq = args.n / BQ;
+
+  if (warp == 8 && lane == 0) {
+    mbar_init(&misc->bar_kv, 1);
+    for (int i = 0; i < ST; ++i) { mbar_init(&misc->full[i], 1); mbar_init(&misc->empty[i], 1); }
+    mbar_init(&misc->s_full, 1);
+    mbar_init(&misc->e_done, 256);
+    mbar_init(&misc->acc_full, 1);
+    misc->abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == 9) tmem_alloc(&misc->tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&misc->tmem_slot);
+
+  if (warp == 8) {
+    if (lane == 0) {
+      mbar_expect_tx(&misc->bar_kv, 2 * K_BYTES + V_BYTES);
+      tma_load_4d(smem + OFF_K1, &tm_k1, &misc->bar_kv, 0, kv_tile * BKV, h_idx, b_idx);
+      tma_load_4d(smem + OFF_K2, &tm_k2, &misc->bar_kv, 0, kv_tile * BKV, h_idx, b_idx);
+      tma_load_4d(smem + OFF_V, &tm_v, &misc->bar_kv, 0, kv_tile * BKV, h_idx, b_idx);
+      tma_load_4d(smem + OFF_V + V_BYTES / 2, &tm_v, &misc->bar_kv, 64, kv_tile * BKV, h_idx, b_idx);
+      for (int i = 0; i < nq; ++i) {
+        const int st = i % ST;
+        uint8_t* sp = smem + OFF_STAGE + st * STAGE_BYTES;
+        if (!mbar_wait(&misc->empty[st], ((i / ST) & 1) ^ 1, abort_flag, 401, i)) break;
+        mbar_expect_tx(&misc->full[st], STAGE_BYTES);
+        tma_load_4d(sp, &tm_q1, &misc->full[st], 0, i * BQ, h_idx, b_idx);
+        tma_load_4d(sp + Q_BYTES, &tm_q2, &misc->full[st], 0, i * BQ, h_idx, b_idx);
+        tma_load_4d(sp + 2 * Q_BYTES, &tm_da, &misc->full[st], 0, i * BQ, bh, 0);
+        tma_load_4d(sp + 2 * Q_BYTES + DA_BYTES / 2, &tm_da, &misc->full[st], 64, i * BQ, bh, 0);
+        bulk_load_1d(sp + 2 * Q_BYTES + DA_BYTES, args.stats + (size_t(bh) * args.n + size_t(i) * BQ), STAT_BYTES,
+                     &misc->full[st]);
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {
+      constexpr uint32_t IDESC_S = make_idesc(BKV, BQ, 0, 0);     // S^T = K Q^T, dP^T = V dA^T
+      constexpr uint32_t IDESC_DV = make_idesc(BKV, DV, 0, 1);    // dV += Pc^T dA   (dA MN-major)
+      constexpr uint32_t IDESC_DK = make_idesc(BKV, HD, 0, 1);    // dK += dS^T Q    (Q MN-major)
+      const uint32_t k1a = smem_u32(smem + OFF_K1), k2a = smem_u32(smem + OFF_K2), va = smem_u32(smem + OFF_V);
+      bool ok = mbar_wait(&misc->bar_kv, 0, abort_flag, 501);
+      for (int i = 0; ok && i < nq; ++i) {
+        const int st = i % ST;
+        const uint32_t sp = smem_u32(smem + OFF_STAGE + st * STAGE_BYTES);
+        const uint32_t q1a = sp, q2a = sp + Q_BYTES, daa = sp + 2 * Q_BYTES;
+        if (!mbar_wait(&misc->full[st], (i / ST) & 1, abort_flag, 502, i)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          mma_ss(tmem_base + T_S1, sdesc_kmajor(k1a + k * 32), sdesc_kmajor(q1a + k * 32), IDESC_S, k > 0);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          mma_ss(tmem_base + T_S2, sdesc_kmajor(k2a + k * 32), sdesc_kmajor(q2a + k * 32), IDESC_S, k > 0);
+#pragma unroll
+        for (int k = 0; k < DV / 16; ++k)
+          mma_ss(tmem_base + T_DP, sdesc_kmajor(va + (k / 4) * (V_BYTES / 2) + (k % 4) * 32),
+                 sdesc_kmajor(daa + (k / 4) * (DA_BYTES / 2) + (k % 4) * 32), IDESC_S, k > 0);
+        mma_commit(&misc->s_full);
+        if (!mbar_wait(&misc->e_done, i & 1, abort_flag, 503, i)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < BQ / 16; ++k) {
+          const uint32_t a_col = (k / 2) * 32 + (k % 2) * 8;   // warpgroup k/2 wrote these 16 query columns
+          mma_ts(tmem_base + T_DV, tmem_base + T_DP + a_col, make_sdesc(daa + k * 2048, DA_BYTES / 2, 1024), IDESC_DV,
+                 (i > 0 || k > 0));
+        }
+#pragma unroll
+        for (int k = 0; k < BQ / 16; ++k) {
+          const uint32_t a_col = (k / 2) * 32 + (k % 2) * 8;
+          mma_ts(tmem_base + T_DK1, tmem_base + T_S1 + a_col, make_sdesc(q1a + k * 2048, 16, 1024), IDESC_DK,
+                 (i > 0 || k > 0));
+        }
+#pragma unroll
+        for (int k = 0; k < BQ / 16; ++k) {
+          const uint32_t a_col = (k / 2) * 32 + (k % 2) * 8;
+          mma_ts(tmem_base + T_DK2, tmem_base + T_S2 + a_col, make_sdesc(q2a + k * 2048, 16, 1024), IDESC_DK,
+                 (i > 0 || k > 0));
+        }
+        mma_commit(&misc->empty[st]);
+      }
+      mma_commit(&misc->acc_full);
+    }
+  } else {
+    const int g = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
+    const uint32_t tb = tmem_base + lane_base;
+    const float sl2 = args.sm_scale * 1.4426950408889634f;
+    const float lam = load_lambda(args.lambda_ptr, args.lambda_dtype);
+    bool ok = true;
+    for (int i = 0; i < nq; ++i) {
+      const int st = i % ST;
+      const float4* stats = reinterpret_cast<const float4*>(smem + OFF_STAGE + st * STAGE_BYTES + 2 * Q_BYTES + DA_BYTES) + g * 32;
+      if (!mbar_wait(&misc->s_full, i & 1, abort_flag, 601 + g, i)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t s1[32], s2[32], dp[32];
+      tmem_ld32(tb + T_S1 + g * 32, s1);
+      tmem_ld32(tb + T_S2 + g * 32, s2);
+      tmem_ld32(tb + T_DP + g * 32, dp);
+      tc_wait_ld();
+      uint32_t pc[16], d1[16], d2[16];
+#pragma unroll
+      for (int jj = 0; jj < 16; ++jj) {
+        float pcv[2], d1v[2], d2v[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int j = 2 * jj + u;
+          const float4 sv = stats[j];
+          const float p1 = ex2(fmaf(__uint_as_float(s1[j]), sl2, -sv.x));
+          const float p2l = -lam * ex2(fmaf(__uint_as_float(s2[j]), sl2, -sv.y));
+          const float dpv = __uint_as_float(dp[j]);
+          pcv[u] = p1 + p2l;
+          d1v[u] = p1 * (dpv - sv.z);
+          d2v[u] = p2l * (dpv - sv.w);
+        }
+        pc[jj] = pack_half2(pcv[0], pcv[1]);
+        d1[jj] = pack_half2(d1v[0], d1v[1]);
+        d2[jj] = pack_half2(d2v[0], d2v[1]);
+      }
+      tmem_st16(tb + T_DP + g * 32, pc);
+      tmem_st16(tb + T_S1 + g * 32, d1);
+      tmem_st16(tb + T_S2 + g * 32, d2);
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&misc->e_done);
+    }
+    ok = ok && mbar_wait(&misc->acc_full, 0, abort_flag, 611 + g);
+    tc_fence_after();
+    // warpgroup g: dV columns [64g, 64g+64) and dK_{g+1}
+    uint32_t acc[64];
+    const size_t grow = size_t(bh) * args.n + size_t(kv_tile) * BKV + row;
+    tmem_ld32(tb + T_DV + g * 64, acc);
+    tmem_ld32(tb + T_DV + g * 64 + 32, acc + 32);
+    tc_wait_ld();
+    if (ok && !*abort_flag) {
+      uint4* p = reinterpret_cast<uint4*>(args.dv + grow * DV + g * 64);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        uint4 v;
+        v.x = pack_half2(__uint_as_float(acc[8 * i + 0]), __uint_as_float(acc[8 * i + 1]));
+        v.y = pack_half2(__uint_as_float(acc[8 * i + 2]), __uint_as_float(acc[8 * i + 3]));
+        v.z = pack_half2(__uint_as_float(acc[8 * i + 4]), __uint_as_float(acc[8 * i + 5]));
+        v.w = pack_half2(__uint_as_float(acc[8 * i + 6]), __uint_as_float(acc[8 * i + 7]));
+        p[i] = v;
+      }
+    }
+    tmem_ld32(tb + (g ? T_DK2 : T_DK1), acc);
+    tmem_ld32(tb + (g ? T_DK2 : T_DK1) + 32, acc + 32);
+    tc_wait_ld();
+    if (ok && !*abort_flag) {
+      const float s = args.sm_scale;
+      uint4* p = reinterpret_cast<uint4*>((g ? args.dk2 : args.dk1) + grow * HD);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        uint4 v;
+        v.x = pack_half2(__uint_as_float(acc[8 * i + 0]) * s, __uint_as_float(acc[8 * i + 1]) * s);
+        v.y = pack_half2(__uint_as_float(acc[8 * i + 2]) * s, __uint_as_float(acc[8 * i + 3]) * s);
+        v.z = pack_half2(__uint_as_float(acc[8 * i + 4]) * s, __uint_as_float(acc[8 * i + 5]) * s);
+        v.w = pack_half2(__uint_as_float(acc[8 * i + 6]) * s, __uint_as_float(acc[8 * i + 7]) * s);
+        p[i] = v;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// 3. dQ1, dQ2: one CTA = 128 query rows; key/value tiles of 128 stream by.
+// TMEM: S1 [0,128) S2 [128,256) dP [256,384) dQ1 [384,448) dQ2 [448,512).  Thread = query row;
+// warpgroup b forms dS_b = +-P_b (dP - E_b) and writes it as fp16 over S_b (TMEM A-operand of dS_b K_b).
+// ------------------------------------------------------------------------------------------------
+namespace dq64 {
+constexpr int BM = 128, BN = 128, HD = 64, DV = 128, ST = 2;
+constexpr int Q_BYTES = BM * HD * 2;        // 16 KB
+constexpr int DA_BYTES = BM * DV * 2;       // 32 KB
+constexpr int K_BYTES = BN * HD * 2;        // 16 KB
+constexpr int V_BYTES = BN * DV * 2;        // 32 KB
+constexpr int STAGE_BYTES = 2 * K_BYTES + V_BYTES;   // 64 KB
+constexpr int OFF_Q1 = 0, OFF_Q2 = Q_BYTES, OFF_DA = 2 * Q_BYTES;
+constexpr int OFF_STAGE = OFF_DA + DA_BYTES;         // 64 KB
+constexpr int OFF_MISC = OFF_STAGE + ST * STAGE_BYTES;
+constexpr int MISC_BYTES = 1024;
+constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
+constexpr int NUM_THREADS = 320;
+constexpr int T_S1 = 0, T_S2 = 128, T_DP = 256, T_DQ1 = 384, T_DQ2 = 448;
+struct Misc {
+  uint64_t bar_q;
+  uint64_t full[ST], empty[ST];
+  uint64_t s_full[2], ds_full[2], acc_full;
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+}  // namespace dq64
+
+__global__ void __launch_bounds__(dq64::NUM_THREADS, 1)
+diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
+                         const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k2,
+                         const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_da,
+                         const BwdArgs args) {
+  using namespace dq64;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Misc* misc = reinterpret_cast<Misc*>(smem + OFF_MISC);
+  volatile int* abort_flag = &misc->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_tile = blockIdx.x, bh = blockIdx.y;
+  const int b_idx = bh / args.h, h_idx = bh % args.h;
+  const int nkv = args.n / BN;
+
+  if (warp == 8 && lane == 0) {
+    mbar_init(&misc->bar_q, 1);
+    for (int i = 0; i < ST; ++i) { mbar_init(&misc->full[i], 1); mbar_init(&misc->empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&misc->s_full[i], 1); mbar_init(&misc->ds_full[i], 128); }
+    mbar_init(&misc->acc_full, 1);
+    misc->abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == 9) tmem_alloc(&misc->tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&misc->tmem_slot);
+
+  if (warp == 8) {
+    if (lane == 0) {
+      mbar_expect_tx(&misc->bar_q, 2 * Q_BYTES + DA_BYTES);
+      tma_load_4d(smem + OFF_Q1, &tm_q1, &misc->bar_q, 0, q_tile * BM, h_idx, b_idx);
+      tma_load_4d(smem + OFF_Q2, &tm_q2, &misc->bar_q, 0, q_tile * BM, h_idx, b_idx);
+      tma_load_4d(smem + OFF_DA, &tm_da, &misc->bar_q, 0, q_tile * BM, bh, 0);
+      tma_load_4d(smem + OFF_DA + DA_BYTES / 2, &tm_da, &misc->bar_q, 64, q_tile * BM, bh, 0);
+      for (int j = 0; j < nkv; ++j) {
+        const int st = j % ST;
+        uint8_t* sp = smem + OFF_STAGE + st * STAGE_BYTES;
+        if (!mbar_wait(&misc->empty[st], ((j / ST) & 1) ^ 1, abort_flag, 701, j)) break;
+        mbar_expect_tx(&misc->full[st], STAGE_BYTES);
+        tma_load_4d(sp, &tm_k1, &misc->full[st], 0, j * BN, h_idx, b_idx);
+        tma_load_4d(sp + K_BYTES, &tm_k2, &misc->full[st], 0, j * BN, h_idx, b_idx);
+        tma_load_4d(sp + 2 * K_BYTES, &tm_v, &misc->full[st], 0, j * BN, h_idx, b_idx);
+        tma_load_4d(sp + 2 * K_BYTES + V_BYTES / 2, &tm_v, &misc->full[st], 64, j * BN, h_idx, b_idx);
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {
+      constexpr uint32_t IDESC_S = make_idesc(BM, BN, 0, 0);     // S = Q K^T, dP = dA V^T
+      constexpr uint32_t IDESC_DQ = make_idesc(BM, HD, 0, 1);    // dQ += dS K   (K MN-major)
+      const uint32_t q1a = smem_u32(smem + OFF_Q1), q2a = smem_u32(smem + OFF_Q2), daa = smem_u32(smem + OFF_DA);
+      bool ok = mbar_wait(&misc->bar_q, 0, abort_flag, 801);
+      for (int j = 0; ok && j < nkv; ++j) {
+        const int st = j % ST;
+        const uint32_t sp = smem_u32(smem + OFF_STAGE + st * STAGE_BYTES);
+        const uint32_t k1a = sp, k2a = sp + K_BYTES, va = sp + 2 * K_BYTES;
+        if (!mbar_wait(&misc->full[st], (j / ST) & 1, abort_flag, 802, j)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          mma_ss(tmem_base + T_S1, sdesc_kmajor(q1a + k * 32), sdesc_kmajor(k1a + k * 32), IDESC_S, k > 0);
+#pragma unroll
+        for (int k = 0; k < DV / 16; ++k)
+          mma_ss(tmem_base + T_DP, sdesc_kmajor(daa + (k / 4) * (DA_BYTES / 2) + (k % 4) * 32),
+                 sdesc_kmajor(va + (k / 4) * (V_BYTES / 2) + (k % 4) * 32), IDESC_S, k > 0);
+        mma_commit(&misc->s_full[0]);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          mma_ss(tmem_base + T_S2, sdesc_kmajor(q2a + k * 32), sdesc_kmajor(k2a + k * 32), IDESC_S, k > 0);
+        mma_commit(&misc->s_full[1]);
+        if (!mbar_wait(&misc->ds_full[0], j & 1, abort_flag, 803, j)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < BN / 16; ++k)
+          mma_ts(tmem_base + T_DQ1, tmem_base + T_S1 + k * 8, make_sdesc(k1a + k * 2048, 16, 1024), IDESC_DQ,
+                 (j > 0 || k > 0));
+        if (!mbar_wait(&misc->ds_full[1], j & 1, abort_flag, 804, j)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < BN / 16; ++k)
+          mma_ts(tmem_base + T_DQ2, tmem_base + T_S2 + k * 8, make_sdesc(k2a + k * 2048, 16, 1024), IDESC_DQ,
+                 (j > 0 || k > 0));
+        mma_commit(&misc->empty[st]);
+      }
+      mma_commit(&misc->acc_full);
+    }
+  } else {
+    const int br = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
+    const uint32_t tb = tmem_base + lane_base;
+    const uint32_t t_s = tb + (br ? T_S2 : T_S1);
+    const float sl2 = args.sm_scale * 1.4426950408889634f;
+    const float lam = load_lambda(args.lambda_ptr, args.lambda_dtype);
+    const size_t grow = size_t(bh) * args.n + size_t(q_tile) * BM + row;
+    const float4 sv = args.stats[grow];
+    const float neg_l = br ? -sv.y : -sv.x;
+    const float e = br ? sv.w : sv.z;
+    const float coef = br ? -lam : 1.f;
+    bool ok = true;
+    for (int j = 0; j < nkv; ++j) {
+      if (!mbar_wait(&misc->s_full[br], j & 1, abort_flag, 901 + br, j)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s[32], dp[32], ds[16];
+        tmem_ld32(t_s + c * 32, s);
+        tmem_ld32(tb + T_DP + c * 32, dp);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = coef * ex2(fmaf(__uint_as_float(s[2 * i]), sl2, neg_l));
+          const float p1 = coef * ex2(fmaf(__uint_as_float(s[2 * i + 1]), sl2, neg_l));
+          ds[i] = pack_half2(p0 * (__uint_as_float(dp[2 * i]) - e), p1 * (__uint_as_float(dp[2 * i + 1]) - e));
+        }
+        tmem_st16(t_s + c * 16, ds);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&misc->ds_full[br]);
+    }
+    ok = ok && mbar_wait(&misc->acc_full, 0, abort_flag, 911 + br);
+    tc_fence_after();
+    uint32_t acc[64];
+    tmem_ld32(tb + (br ? T_DQ2 : T_DQ1), acc);
+    tmem_ld32(tb + (br ? T_DQ2 : T_DQ1) + 32, acc + 32);
+    tc_wait_ld();
+    if (ok && !*abort_flag) {
+      const float s = args.sm_scale;
+      uint4* p = reinterpret_cast<uint4*>((br ? args.dq2 : args.dq1) + grow * HD);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        uint4 v;
+        v.x = pack_half2(__uint_as_float(acc[8 * i + 0]) * s, __uint_as_float(acc[8 * i + 1]) * s);
+        v.y = pack_half2(__uint_as_float(acc[8 * i + 2]) * s, __uint_as_float(acc[8 * i + 3]) * s);
+        v.z = pack_half2(__uint_as_float(acc[8 * i + 4]) * s, __uint_as_float(acc[8 * i + 5]) * s);
+        v.w = pack_half2(__uint_as_float(acc[8 * i + 6]) * s, __uint_as_float(acc[8 * i + 7]) * s);
+        p[i] = v;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace da

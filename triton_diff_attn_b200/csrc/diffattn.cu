@@ -1,0 +1,241 @@
+// C ABI of libdiffattn (see include/diffattn.h): argument checks, TMA descriptors, launches.
+// Single translation unit: the kernels live in the .cuh files included below.
+#include "../../include/diffattn.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "bwd.cuh"
+#include "fwd.cuh"
+#include "sm100.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define DA_CUDA(call)                                                                       \
+  do {                                                                                      \
+    cudaError_t e_ = (call);                                                                \
+    if (e_ != cudaSuccess) return fail(DIFFATTN_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e_)); \
+  } while (0)
+
+PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+  });
+  return fn;
+}
+
+// fp16 tensor [d3, d2, rows, cols] with element strides (s3, s2, s_row, 1); box = box_rows x 64 columns,
+// 128-byte swizzle (the layout the tcgen05 shared-memory descriptors in sm100.cuh describe).
+int make_map(CUtensorMap* map, const void* base, int cols, int rows, int d2, int d3, int64_t s_row, int64_t s2, int64_t s3,
+             int box_rows, const char* what) {
+  auto enc = get_encode();
+  if (!enc) return fail(DIFFATTN_ERR_CUDA, "cuTensorMapEncodeTiled not available from the driver");
+  cuuint64_t dims[4] = {cuuint64_t(cols), cuuint64_t(rows), cuuint64_t(d2), cuuint64_t(d3)};
+  cuuint64_t strides[3] = {cuuint64_t(s_row) * 2, cuuint64_t(s2) * 2, cuuint64_t(s3) * 2};
+  // a size-1 dimension's stride is never used, but the encoder still wants a legal value
+  if (d2 == 1) strides[1] = strides[0] * cuuint64_t(rows);
+  if (d3 == 1) strides[2] = strides[1] * cuuint64_t(d2);
+  cuuint32_t box[4] = {cuuint32_t(cols < 64 ? cols : 64), cuuint32_t(box_rows), 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUtensorMapSwizzle sw = cols >= 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(DIFFATTN_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, int(r));
+  return DIFFATTN_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int check_common(const DiffAttnParams* p, bool bwd) {
+  if (!p) return fail(DIFFATTN_ERR_NULL_PTR, "params is NULL");
+  if (p->struct_size != sizeof(DiffAttnParams))
+    return fail(DIFFATTN_ERR_BAD_STRUCT, "struct_size %u != %zu", p->struct_size, sizeof(DiffAttnParams));
+  if (p->B < 0 || p->H < 0 || p->N < 0 || p->D <= 0)
+    return fail(DIFFATTN_ERR_BAD_SHAPE, "negative size: B=%d H=%d N=%d D=%d", p->B, p->H, p->N, p->D);
+  if (!diffattn_supports(p->D, bwd ? 1 : 0))
+    return fail(DIFFATTN_ERR_UNSUPPORTED_D, "head dim %d is not compiled in (supported: 64)", p->D);
+  if (p->N % 128 != 0)
+    return fail(DIFFATTN_ERR_BAD_SHAPE, "N=%d must be a multiple of 128 (no masking, as the reference)", p->N);
+  if (p->lambda_dtype != DIFFATTN_LAMBDA_F16 && p->lambda_dtype != DIFFATTN_LAMBDA_F32)
+    return fail(DIFFATTN_ERR_BAD_DTYPE, "lambda_dtype %d unknown", p->lambda_dtype);
+  if ((long long)p->B * p->H > 65535)
+    return fail(DIFFATTN_ERR_BAD_SHAPE, "B*H=%lld exceeds the grid limit 65535", (long long)p->B * p->H);
+  if (p->B == 0 || p->H == 0 || p->N == 0) return 1;   // empty: nothing to do
+  const void* ptrs[] = {p->q1, p->q2, p->k1, p->k2, p->v, p->lambda_scale, p->y, p->a2, p->lse1, p->lse2, p->rstd};
+  const char* names[] = {"q1", "q2", "k1", "k2", "v", "lambda_scale", "y", "a2", "lse1", "lse2", "rstd"};
+  for (int i = 0; i < 11; ++i)
+    if (!ptrs[i]) return fail(DIFFATTN_ERR_NULL_PTR, "%s is NULL", names[i]);
+  for (int i = 0; i < 5; ++i)
+    if (!aligned16(ptrs[i])) return fail(DIFFATTN_ERR_MISALIGNED, "%s is not 16-byte aligned", names[i]);
+  if (!aligned16(p->y) || !aligned16(p->a2)) return fail(DIFFATTN_ERR_MISALIGNED, "y/a2 not 16-byte aligned");
+  const int64_t st[] = {p->qk_stride_b, p->qk_stride_h, p->qk_stride_n, p->v_stride_b, p->v_stride_h, p->v_stride_n};
+  for (int i = 0; i < 6; ++i)
+    if (st[i] <= 0 || st[i] % 8 != 0)
+      return fail(DIFFATTN_ERR_BAD_STRIDE, "stride %d = %lld must be a positive multiple of 8 elements", i, (long long)st[i]);
+  if (p->qk_stride_n < p->D || p->v_stride_n < 2 * p->D)
+    return fail(DIFFATTN_ERR_BAD_STRIDE, "row stride smaller than the row");
+  if (bwd) {
+    const void* bp[] = {p->dy, p->dq1, p->dq2, p->dk1, p->dk2, p->dv, p->dlambda};
+    const char* bn[] = {"dy", "dq1", "dq2", "dk1", "dk2", "dv", "dlambda"};
+    for (int i = 0; i < 7; ++i)
+      if (!bp[i]) return fail(DIFFATTN_ERR_NULL_PTR, "%s is NULL", bn[i]);
+    for (int i = 0; i < 6; ++i)
+      if (!aligned16(bp[i])) return fail(DIFFATTN_ERR_MISALIGNED, "%s is not 16-byte aligned", bn[i]);
+    const uint64_t need = diffattn_workspace_bytes(p);
+    if (!p->workspace || p->workspace_bytes < need)
+      return fail(DIFFATTN_ERR_WORKSPACE, "workspace %llu bytes, need %llu", (unsigned long long)p->workspace_bytes,
+                  (unsigned long long)need);
+    if (reinterpret_cast<uintptr_t>(p->workspace) & 255) return fail(DIFFATTN_ERR_MISALIGNED, "workspace not 256-byte aligned");
+  }
+  return DIFFATTN_OK;
+}
+
+uint64_t round256(uint64_t x) { return (x + 255) & ~uint64_t(255); }
+
+template <typename K>
+int set_smem(K kernel, int bytes) {
+  DA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  return DIFFATTN_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* diffattn_last_error(void) { return g_err; }
+int diffattn_version(void) { return DIFFATTN_VERSION; }
+int diffattn_supports(int32_t d, int32_t dir) {
+  (void)dir;
+  return d == 64 ? 1 : 0;
+}
+
+uint64_t diffattn_workspace_bytes(const DiffAttnParams* p) {
+  if (!p || p->B <= 0 || p->H <= 0 || p->N <= 0 || p->D <= 0) return 0;
+  const uint64_t rows = uint64_t(p->B) * p->H * p->N;
+  return round256(rows * 2 * p->D * 2) + round256(rows * 16);   // dA fp16 + per-row {lse1', lse2', E1, E2}
+}
+
+int diffattn_fwd(const DiffAttnParams* p) {
+  int rc = check_common(p, false);
+  if (rc < 0) return rc;
+  if (rc == 1) return DIFFATTN_OK;
+  DA_CUDA(cudaSetDevice(p->device));
+  cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+  CUtensorMap mq1, mq2, mk1, mk2, mv;
+  const int D = p->D, DV = 2 * p->D;
+  if ((rc = make_map(&mq1, p->q1, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "q1"))) return rc;
+  if ((rc = make_map(&mq2, p->q2, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "q2"))) return rc;
+  if ((rc = make_map(&mk1, p->k1, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "k1"))) return rc;
+  if ((rc = make_map(&mk2, p->k2, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "k2"))) return rc;
+  if ((rc = make_map(&mv, p->v, DV, p->N, p->H, p->B, p->v_stride_n, p->v_stride_h, p->v_stride_b, 128, "v"))) return rc;
+  da::FwdArgs a;
+  a.y = static_cast<__half*>(p->y);
+  a.a2 = static_cast<__half*>(p->a2);
+  a.lse1 = p->lse1; a.lse2 = p->lse2; a.rstd = p->rstd;
+  a.lambda_ptr = p->lambda_scale; a.lambda_dtype = p->lambda_dtype;
+  a.sm_scale = p->sm_scale; a.out_scale = 1.f - p->lambda_init; a.eps = p->eps;
+  a.rms_norm = p->rms_norm; a.n = p->N; a.h = p->H;
+  if ((rc = set_smem(da::diffattn_fwd64_kernel, da::fwd64::SMEM_BYTES))) return rc;
+  dim3 grid(p->N / da::fwd64::BM, p->B * p->H);
+  da::diffattn_fwd64_kernel<<<grid, da::fwd64::NUM_THREADS, da::fwd64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, a);
+  DA_CUDA(cudaGetLastError());
+  return DIFFATTN_OK;
+}
+
+int diffattn_bwd(const DiffAttnParams* p) {
+  int rc = check_common(p, true);
+  if (rc < 0) return rc;
+  if (rc == 1) return DIFFATTN_OK;
+  DA_CUDA(cudaSetDevice(p->device));
+  cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+  const int D = p->D, DV = 2 * p->D;
+  const long long bh = (long long)p->B * p->H;
+  const uint64_t rows = uint64_t(bh) * p->N;
+  da::BwdArgs a;
+  a.y = static_cast<const __half*>(p->y);
+  a.a2 = static_cast<const __half*>(p->a2);
+  a.dy = static_cast<const __half*>(p->dy);
+  a.lse1 = p->lse1; a.lse2 = p->lse2; a.rstd = p->rstd;
+  a.da = static_cast<__half*>(p->workspace);
+  a.stats = reinterpret_cast<float4*>(static_cast<uint8_t*>(p->workspace) + round256(rows * DV * 2));
+  a.dq1 = static_cast<__half*>(p->dq1); a.dq2 = static_cast<__half*>(p->dq2);
+  a.dk1 = static_cast<__half*>(p->dk1); a.dk2 = static_cast<__half*>(p->dk2);
+  a.dv = static_cast<__half*>(p->dv);
+  a.dlambda = p->dlambda;
+  a.lambda_ptr = p->lambda_scale; a.lambda_dtype = p->lambda_dtype;
+  a.sm_scale = p->sm_scale; a.out_scale = 1.f - p->lambda_init; a.rms_norm = p->rms_norm;
+  a.n = p->N; a.h = p->H; a.rows = (long long)rows;
+
+  // 1. preprocess (grid-stride; one atomic per CTA for d(lambda))
+  {
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p->device);
+    long long blocks = (long long)((rows + 7) / 8);
+    if (blocks > (long long)sms * 8) blocks = (long long)sms * 8;
+    da::diffattn_bwd_pre_kernel<4><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    DA_CUDA(cudaGetLastError());
+  }
+  CUtensorMap mq1, mq2, mk1, mk2, mv, mda;
+  // 2. dK, dV: key/value tiles of 128 rows resident, query-side tiles of 64 rows streamed
+  if ((rc = make_map(&mq1, p->q1, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 64, "q1"))) return rc;
+  if ((rc = make_map(&mq2, p->q2, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 64, "q2"))) return rc;
+  if ((rc = make_map(&mk1, p->k1, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "k1"))) return rc;
+  if ((rc = make_map(&mk2, p->k2, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "k2"))) return rc;
+  if ((rc = make_map(&mv, p->v, DV, p->N, p->H, p->B, p->v_stride_n, p->v_stride_h, p->v_stride_b, 128, "v"))) return rc;
+  if ((rc = make_map(&mda, a.da, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 64, "dA"))) return rc;
+  if ((rc = set_smem(da::diffattn_bwd_dkdv64_kernel, da::dkdv64::SMEM_BYTES))) return rc;
+  {
+    dim3 grid(p->N / da::dkdv64::BKV, (unsigned)bh);
+    da::diffattn_bwd_dkdv64_kernel<<<grid, da::dkdv64::NUM_THREADS, da::dkdv64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, mda, a);
+    DA_CUDA(cudaGetLastError());
+  }
+  // 3. dQ: query tiles of 128 rows resident, key/value tiles of 128 rows streamed
+  if ((rc = make_map(&mq1, p->q1, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "q1"))) return rc;
+  if ((rc = make_map(&mq2, p->q2, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "q2"))) return rc;
+  if ((rc = make_map(&mda, a.da, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 128, "dA"))) return rc;
+  if ((rc = set_smem(da::diffattn_bwd_dq64_kernel, da::dq64::SMEM_BYTES))) return rc;
+  {
+    dim3 grid(p->N / da::dq64::BM, (unsigned)bh);
+    da::diffattn_bwd_dq64_kernel<<<grid, da::dq64::NUM_THREADS, da::dq64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, mda, a);
+    DA_CUDA(cudaGetLastError());
+  }
+  return DIFFATTN_OK;
+}
+
+int diffattn_status(int32_t device) {
+  DA_CUDA(cudaSetDevice(device));
+  DA_CUDA(cudaDeviceSynchronize());
+  int st[4] = {0, 0, 0, 0};
+  DA_CUDA(cudaMemcpyFromSymbol(st, da::g_status, sizeof(st)));
+  if (st[0] != 0) {
+    int zero[4] = {0, 0, 0, 0};
+    cudaMemcpyToSymbol(da::g_status, zero, sizeof(zero));
+    return fail(DIFFATTN_ERR_TIMEOUT, "device-side wait gave up at site %d (block %d,%d iteration %d)", st[0], st[1], st[2], st[3]);
+  }
+  return DIFFATTN_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,308 @@
+// Differential-attention forward for sm_100a, head dim D = 64 (value width 128).
+//
+// One CTA owns one tile of 128 query rows of one (batch, head).  Roles (10 warps):
+//   warps 0-3  softmax of branch 1 (thread = query row; S1/P1/O1 in TMEM)
+//   warps 4-7  softmax of branch 2
+//   warp  8    TMA producer: Q1,Q2 once; K1,K2 and V tiles through two mbarrier rings
+//   warp  9    tcgen05.mma issuer (one elected thread) and TMEM owner
+// TMEM (512 columns of 128 lanes x 32 bit): S1 [0,128) S2 [128,256) O1 [256,384) O2 [384,512);
+// P_b (fp16, two per column) overwrites the first 64 columns of S_b and is the TMEM A-operand of P_b V.
+// Replaces the reference's Triton forward (src/kernel.py:21-207): same math (two online softmaxes,
+// O = O1/l1 - lambda O2/l2, RMSNorm * (1 - lambda_init)), but saves lse1, lse2, rstd and A2 = P2 V
+// instead of O1/O2.
+#pragma once
+#include "sm100.cuh"
+
+namespace da {
+
+struct FwdArgs {
+  __half* y;          // [B*H, N, 2D] dense
+  __half* a2;         // [B*H, N, 2D] dense, branch-2 output P2 V (kept for the backward)
+  float* lse1;        // [B*H, N] natural-log logsumexp of s Q1 K1^T
+  float* lse2;
+  float* rstd;        // [B*H, N] rsqrt(mean(A^2) + eps)   (written also when rms_norm is off)
+  const void* lambda_ptr;
+  int lambda_dtype;   // 0 = fp16, 1 = fp32
+  float sm_scale;
+  float out_scale;    // 1 - lambda_init
+  float eps;
+  int rms_norm;
+  int n;              // sequence length
+  int h;              // heads
+};
+
+__device__ __forceinline__ float load_lambda(const void* p, int dtype) {
+  return dtype == 0 ? __half2float(*reinterpret_cast<const __half*>(p)) : *reinterpret_cast<const float*>(p);
+}
+
+namespace fwd64 {
+constexpr int BM = 128;            // query rows per CTA
+constexpr int BN = 128;            // key/value rows per iteration
+constexpr int HD = 64;
+constexpr int DV = 128;
+constexpr int KS = 3;              // K ring depth
+constexpr int VS = 2;              // V ring depth
+constexpr int Q_BYTES = BM * HD * 2;            // 16 KB per Q
+constexpr int K_BYTES = BN * HD * 2;            // 16 KB per K
+constexpr int V_BYTES = BN * DV * 2;            // 32 KB (two 64-column boxes)
+constexpr int OFF_Q1 = 0;
+constexpr int OFF_Q2 = Q_BYTES;
+constexpr int OFF_K = 2 * Q_BYTES;                       // stage s: K1 at +s*2*K_BYTES, K2 right after
+constexpr int OFF_V = OFF_K + KS * 2 * K_BYTES;
+constexpr int OFF_MISC = OFF_V + VS * V_BYTES;           // barriers, coefficients
+constexpr int MISC_BYTES = 4096;
+constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024; // +1024 for manual alignment
+constexpr int NUM_THREADS = 320;
+
+struct Misc {
+  uint64_t bar_q;
+  uint64_t k_full[KS], k_empty[KS];
+  uint64_t v_full[VS], v_empty[VS];
+  uint64_t s_full[2];
+  uint64_t p_full[2];
+  uint64_t o_full;
+  uint32_t tmem_slot;
+  int abort_flag;
+  float coef1[BM];     // 1 / l1
+  float coef2[BM];     // 1 / l2
+  float ssq[2][BM];    // partial sums of squares per column half
+};
+static_assert(sizeof(Misc) <= MISC_BYTES, "misc area too small");
+}  // namespace fwd64
+
+__global__ void __launch_bounds__(fwd64::NUM_THREADS, 1)
+diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
+                      const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k2,
+                      const __grid_constant__ CUtensorMap tm_v, const FwdArgs args) {
+  using namespace fwd64;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Misc* misc = reinterpret_cast<Misc*>(smem + OFF_MISC);
+  volatile int* abort_flag = &misc->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int q_tile = blockIdx.x;
+  const int bh = blockIdx.y;
+  const int b_idx = bh / args.h;
+  const int h_idx = bh % args.h;
+  const int nkv = args.n / BN;
+
+  if (warp == 8 && lane == 0) {
+    mbar_init(&misc->bar_q, 1);
+    for (int i = 0; i < KS; ++i) { mbar_init(&misc->k_full[i], 1); mbar_init(&misc->k_empty[i], 1); }
+    for (int i = 0; i < VS; ++i) { mbar_init(&misc->v_full[i], 1); mbar_init(&misc->v_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&misc->s_full[i], 1); mbar_init(&misc->p_full[i], 128); }
+    mbar_init(&misc->o_full, 1);
+    misc->abort_flag = 0;
+    mbar_init_fence();
+    tma_prefetch_desc(&tm_q1); tma_prefetch_desc(&tm_q2); tma_prefetch_desc(&tm_k1);
+    tma_prefetch_desc(&tm_k2); tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 9) {
+    tmem_alloc(&misc->tmem_slot, 512);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&misc->tmem_slot);
+
+  if (warp == 8) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0) {
+      mbar_expect_tx(&misc->bar_q, 2 * Q_BYTES);
+      tma_load_4d(smem + OFF_Q1, &tm_q1, &misc->bar_q, 0, q_tile * BM, h_idx, b_idx);
+      tma_load_4d(smem + OFF_Q2, &tm_q2, &misc->bar_q, 0, q_tile * BM, h_idx, b_idx);
+      for (int j = 0; j < nkv; ++j) {
+        const int ks = j % KS, vs = j % VS;
+        if (!mbar_wait(&misc->k_empty[ks], ((j / KS) & 1) ^ 1, abort_flag, 101, j)) break;
+        mbar_expect_tx(&misc->k_full[ks], 2 * K_BYTES);
+        tma_load_4d(smem + OFF_K + ks * 2 * K_BYTES, &tm_k1, &misc->k_full[ks], 0, j * BN, h_idx, b_idx);
+        tma_load_4d(smem + OFF_K + ks * 2 * K_BYTES + K_BYTES, &tm_k2, &misc->k_full[ks], 0, j * BN, h_idx, b_idx);
+        if (!mbar_wait(&misc->v_empty[vs], ((j / VS) & 1) ^ 1, abort_flag, 102, j)) break;
+        mbar_expect_tx(&misc->v_full[vs], V_BYTES);
+        tma_load_4d(smem + OFF_V + vs * V_BYTES, &tm_v, &misc->v_full[vs], 0, j * BN, h_idx, b_idx);
+        tma_load_4d(smem + OFF_V + vs * V_BYTES + V_BYTES / 2, &tm_v, &misc->v_full[vs], 64, j * BN, h_idx, b_idx);
+      }
+    }
+  } else if (warp == 9) {
+    // -------------------------------- MMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr uint32_t IDESC_S = make_idesc(BM, BN, 0, 0);    // S = Q K^T, both K-major
+      constexpr uint32_t IDESC_O = make_idesc(BM, DV, 0, 1);    // O += P V, V is MN-major
+      const uint32_t q_addr[2] = {smem_u32(smem + OFF_Q1), smem_u32(smem + OFF_Q2)};
+      auto issue_s = [&](int br, int j) {
+        const uint32_t k_addr = smem_u32(smem + OFF_K + (j % KS) * 2 * K_BYTES + br * K_BYTES);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          mma_ss(tmem_base + br * 128, sdesc_kmajor(q_addr[br] + k * 32), sdesc_kmajor(k_addr + k * 32), IDESC_S, k > 0);
+        mma_commit(&misc->s_full[br]);
+      };
+      auto issue_pv = [&](int br, int j) {
+        const uint32_t v_addr = smem_u32(smem + OFF_V + (j % VS) * V_BYTES);
+#pragma unroll
+        for (int k = 0; k < BN / 16; ++k)
+          mma_ts(tmem_base + 256 + br * 128, tmem_base + br * 128 + k * 8,
+                 make_sdesc(v_addr + k * 2048, V_BYTES / 2, 1024), IDESC_O, (j > 0 || k > 0));
+      };
+      bool ok = mbar_wait(&misc->bar_q, 0, abort_flag, 201);
+      ok = ok && mbar_wait(&misc->k_full[0], 0, abort_flag, 202);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0, 0);
+        issue_s(1, 0);
+        mma_commit(&misc->k_empty[0]);
+        for (int j = 0; j < nkv; ++j) {
+          const int vs = j % VS;
+          if (!mbar_wait(&misc->v_full[vs], (j / VS) & 1, abort_flag, 203, j)) break;
+          if (!mbar_wait(&misc->p_full[0], j & 1, abort_flag, 204, j)) break;
+          tc_fence_after();
+          issue_pv(0, j);
+          if (j + 1 < nkv) {
+            if (!mbar_wait(&misc->k_full[(j + 1) % KS], ((j + 1) / KS) & 1, abort_flag, 205, j)) break;
+            tc_fence_after();
+            issue_s(0, j + 1);
+          }
+          if (!mbar_wait(&misc->p_full[1], j & 1, abort_flag, 206, j)) break;
+          tc_fence_after();
+          issue_pv(1, j);
+          mma_commit(&misc->v_empty[vs]);
+          if (j + 1 < nkv) {
+            issue_s(1, j + 1);
+            mma_commit(&misc->k_empty[(j + 1) % KS]);
+          }
+        }
+        mma_commit(&misc->o_full);
+      }
+    }
+  } else {
+    // ------------------------- softmax warpgroups + epilogue -------------------------
+    const int br = warp >> 2;                       // branch handled by this warpgroup
+    const int row = (warp & 3) * 32 + lane;         // query row inside the tile = TMEM lane
+    const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
+    const uint32_t t_s = tmem_base + lane_base + br * 128;
+    const uint32_t t_o = tmem_base + lane_base + 256 + br * 128;
+    const float sl2 = args.sm_scale * 1.4426950408889634f;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < nkv; ++j) {
+      if (!mbar_wait(&misc->s_full[br], j & 1, abort_flag, 301 + br, j)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t sr[128];
+      tmem_ld32(t_s + 0, sr);
+      tmem_ld32(t_s + 32, sr + 32);
+      tmem_ld32(t_s + 64, sr + 64);
+      tmem_ld32(t_s + 96, sr + 96);
+      tc_wait_ld();
+      float mx = __uint_as_float(sr[0]);
+#pragma unroll
+      for (int i = 1; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(sr[i]));
+      const float m_new = fmaxf(m_run, mx);
+      if (j == 0) {
+        m_run = m_new;
+      } else {
+        // Rescale only when the running maximum moved by more than 2^8; otherwise keep the stale
+        // maximum (P stays below 256, exact in the final normalisation).
+        const bool need = (m_new - m_run) * sl2 > 8.f;
+        if (__any_sync(0xffffffffu, need)) {
+          const float scale = need ? ex2((m_run - m_new) * sl2) : 1.f;
+          if (need) m_run = m_new;
+          l_run *= scale;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            tmem_ld32(t_o + c * 32, o);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * scale);
+            tmem_st32(t_o + c * 32, o);
+          }
+        }
+      }
+      const float neg = -m_run * sl2;
+      float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        const float p0 = ex2(fmaf(__uint_as_float(sr[2 * i]), sl2, neg));
+        const float p1 = ex2(fmaf(__uint_as_float(sr[2 * i + 1]), sl2, neg));
+        sum0 += p0;
+        sum1 += p1;
+        sr[i] = pack_half2(p0, p1);
+      }
+      l_run += sum0 + sum1;
+      tmem_st32(t_s + 0, sr);
+      tmem_st32(t_s + 32, sr + 32);
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&misc->p_full[br]);
+    }
+
+    // ---- epilogue: every thread runs every barrier; only the global writes depend on `ok`
+    ok = ok && mbar_wait(&misc->o_full, 0, abort_flag, 311 + br);
+    tc_fence_after();
+    const float inv_l = 1.f / l_run;
+    if (br == 0) misc->coef1[row] = inv_l; else misc->coef2[row] = inv_l;
+    named_bar_sync(1, 256);
+    const float lam = load_lambda(args.lambda_ptr, args.lambda_dtype);
+    const float c1 = misc->coef1[row];
+    const float c2 = misc->coef2[row];
+    // this warpgroup owns value columns [64*br, 64*br+64) of both accumulators
+    const uint32_t t_o1 = tmem_base + lane_base + 256 + br * 64;
+    const uint32_t t_o2 = tmem_base + lane_base + 384 + br * 64;
+    uint32_t o1[64], o2[64];
+    tmem_ld32(t_o1, o1);
+    tmem_ld32(t_o1 + 32, o1 + 32);
+    tmem_ld32(t_o2, o2);
+    tmem_ld32(t_o2 + 32, o2 + 32);
+    tc_wait_ld();
+    float ssq = 0.f;
+#pragma unroll
+    for (int i = 0; i < 64; ++i) {
+      const float a2v = __uint_as_float(o2[i]) * c2;
+      const float av = __uint_as_float(o1[i]) * c1 - lam * a2v;
+      ssq += av * av;
+      o1[i] = __float_as_uint(av);
+      o2[i] = __float_as_uint(a2v);
+    }
+    misc->ssq[br][row] = ssq;
+    named_bar_sync(1, 256);
+    const float rstd = rsqrtf((misc->ssq[0][row] + misc->ssq[1][row]) * (1.f / DV) + args.eps);
+    const float yscale = args.rms_norm ? args.out_scale * rstd : 1.f;
+    if (ok && !*abort_flag) {
+      const size_t grow = size_t(bh) * args.n + size_t(q_tile) * BM + row;
+      uint4* yp = reinterpret_cast<uint4*>(args.y + grow * DV + br * 64);
+      uint4* ap = reinterpret_cast<uint4*>(args.a2 + grow * DV + br * 64);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        uint4 yv, av;
+        yv.x = pack_half2(__uint_as_float(o1[8 * i + 0]) * yscale, __uint_as_float(o1[8 * i + 1]) * yscale);
+        yv.y = pack_half2(__uint_as_float(o1[8 * i + 2]) * yscale, __uint_as_float(o1[8 * i + 3]) * yscale);
+        yv.z = pack_half2(__uint_as_float(o1[8 * i + 4]) * yscale, __uint_as_float(o1[8 * i + 5]) * yscale);
+        yv.w = pack_half2(__uint_as_float(o1[8 * i + 6]) * yscale, __uint_as_float(o1[8 * i + 7]) * yscale);
+        av.x = pack_half2(__uint_as_float(o2[8 * i + 0]), __uint_as_float(o2[8 * i + 1]));
+        av.y = pack_half2(__uint_as_float(o2[8 * i + 2]), __uint_as_float(o2[8 * i + 3]));
+        av.z = pack_half2(__uint_as_float(o2[8 * i + 4]), __uint_as_float(o2[8 * i + 5]));
+        av.w = pack_half2(__uint_as_float(o2[8 * i + 6]), __uint_as_float(o2[8 * i + 7]));
+        yp[i] = yv;
+        ap[i] = av;
+      }
+      const float lse = m_run * args.sm_scale + logf(l_run);
+      if (br == 0) {
+        args.lse1[grow] = lse;
+        args.rstd[grow] = rstd;
+      } else {
+        args.lse2[grow] = lse;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace da

@@ -1,0 +1,149 @@
+"""Drop-in for the reference's `MultiheadDiffAttnKernel` (reference src/layers.py:10-26) and its
+autograd function `_diff_attention` (reference src/kernel.py:461-575).
+
+Host side only: argument checks, output allocation through torch, and two calls into the C ABI
+(`diffattn_fwd`, `diffattn_bwd`).  All arithmetic runs in the hand-written sm_100a kernels of
+libdiffattn.so.  Differences from the reference's host code, on purpose:
+  * no host synchronisation in the backward (the reference calls `.item()`, src/kernel.py:573):
+    d(lambda) is accumulated on the device and returned as a tensor of lambda_scale's shape/dtype;
+  * the backward keeps logsumexp per branch, rstd and A2 = P2 V instead of O1 and O2
+    (src/kernel.py:505);
+  * no global autotune state (src/kernel.py:511-512).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+
+EPS = 1e-5   # reference src/kernel.py:50
+
+
+def _check_inputs(q1, q2, k1, k2, v, lambda_scale):
+    for name, t in (("q1", q1), ("q2", q2), ("k1", k1), ("k2", k2), ("v", v)):
+        if not torch.is_tensor(t):
+            raise TypeError(f"{name} must be a tensor")
+        if not t.is_cuda:
+            raise RuntimeError(f"{name} must be a CUDA tensor: this operator has no CPU path")
+        if t.dtype != torch.float16:
+            raise ValueError(f"{name} must be float16 (got {t.dtype}); the kernels compute P in fp16 like "
+                             "the reference (src/kernel.py:175-176)")
+        if t.dim() != 4:
+            raise ValueError(f"{name} must be [B, H, N, D]")
+    if not torch.is_tensor(lambda_scale):
+        raise TypeError("lambda_scale must be a 1-element CUDA tensor (the reference loads it from a "
+                        "device pointer, src/kernel.py:138)")
+    if lambda_scale.numel() != 1 or lambda_scale.dtype not in (torch.float16, torch.float32):
+        raise ValueError("lambda_scale must hold one float16 or float32 element")
+    if lambda_scale.device != q1.device:
+        raise RuntimeError("lambda_scale must live on the same device as q1")
+    b, h, n, d = q1.shape
+    for name, t in (("q2", q2), ("k1", k1), ("k2", k2)):
+        if tuple(t.shape) != (b, h, n, d):
+            raise ValueError(f"{name} shape {tuple(t.shape)} != q1 shape {(b, h, n, d)}")
+        if t.device != q1.device:
+            raise RuntimeError(f"{name} is on {t.device}, q1 on {q1.device}")
+    if tuple(v.shape) != (b, h, n, 2 * d):
+        raise ValueError(f"v shape {tuple(v.shape)} != {(b, h, n, 2 * d)}")
+    if v.device != q1.device:
+        raise RuntimeError("v is on another device")
+
+
+def _same_layout(ts):
+    """q1,q2,k1,k2 must share strides (the reference reads them from Q1 only, src/kernel.py:487-490)."""
+    ts = [t if t.stride(-1) == 1 else t.contiguous() for t in ts]
+    if any(t.stride() != ts[0].stride() for t in ts):
+        ts = [t.contiguous() for t in ts]
+    return ts
+
+
+def _fill_common(p, q1, q2, k1, k2, v, lam, lambda_init, rms_norm, saved):
+    b, h, n, d = q1.shape
+    p.device = q1.device.index if q1.device.index is not None else torch.cuda.current_device()
+    p.stream = torch.cuda.current_stream(q1.device).cuda_stream
+    p.B, p.H, p.N, p.D = b, h, n, d
+    p.qk_stride_b, p.qk_stride_h, p.qk_stride_n = q1.stride(0), q1.stride(1), q1.stride(2)
+    p.v_stride_b, p.v_stride_h, p.v_stride_n = v.stride(0), v.stride(1), v.stride(2)
+    p.q1, p.q2, p.k1, p.k2, p.v = (t.data_ptr() for t in (q1, q2, k1, k2, v))
+    p.lambda_scale = lam.data_ptr()
+    p.lambda_dtype = _lib.LAMBDA_F16 if lam.dtype == torch.float16 else _lib.LAMBDA_F32
+    p.rms_norm = 1 if rms_norm else 0
+    p.sm_scale = 1.0 / math.sqrt(d)          # reference src/layers.py:20-22 (D, not 2D)
+    p.lambda_init = float(lambda_init)
+    p.eps = EPS
+    y, a2, lse1, lse2, rstd = saved
+    p.y, p.a2, p.lse1, p.lse2, p.rstd = (t.data_ptr() for t in (y, a2, lse1, lse2, rstd))
+
+
+class DiffAttnFunction(torch.autograd.Function):
+    """forward/backward pair bound to the C ABI; counterpart of `_diff_attention`
+    (reference src/kernel.py:461-575)."""
+
+    @staticmethod
+    def forward(ctx, q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm):
+        _check_inputs(q1, q2, k1, k2, v, lambda_scale)
+        q1, q2, k1, k2 = _same_layout([q1, q2, k1, k2])
+        if v.stride(-1) != 1:
+            v = v.contiguous()
+        b, h, n, d = q1.shape
+        dev = q1.device
+        with torch.cuda.device(dev):
+            y = torch.empty((b, h, n, 2 * d), dtype=torch.float16, device=dev)
+            a2 = torch.empty_like(y)
+            lse1 = torch.empty((b, h, n), dtype=torch.float32, device=dev)
+            lse2 = torch.empty_like(lse1)
+            rstd = torch.empty_like(lse1)
+            p = _lib.new_params()
+            _fill_common(p, q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, (y, a2, lse1, lse2, rstd))
+            _lib.check(_lib.lib.diffattn_fwd(p), "diffattn_fwd")
+        ctx.save_for_backward(q1, q2, k1, k2, v, lambda_scale, y, a2, lse1, lse2, rstd)
+        ctx.lambda_init = float(lambda_init)
+        ctx.rms_norm = bool(rms_norm)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        q1, q2, k1, k2, v, lam, y, a2, lse1, lse2, rstd = ctx.saved_tensors
+        b, h, n, d = q1.shape
+        dev = q1.device
+        dy = dy.to(torch.float16).contiguous()   # the kernels index dY densely (as src/kernel.py:278-280)
+        with torch.cuda.device(dev):
+            dq1 = torch.empty((b, h, n, d), dtype=torch.float16, device=dev)
+            dq2, dk1, dk2 = torch.empty_like(dq1), torch.empty_like(dq1), torch.empty_like(dq1)
+            dv = torch.empty((b, h, n, 2 * d), dtype=torch.float16, device=dev)
+            dlam = torch.zeros(1, dtype=torch.float32, device=dev)
+            p = _lib.new_params()
+            _fill_common(p, q1, q2, k1, k2, v, lam, ctx.lambda_init, ctx.rms_norm, (y, a2, lse1, lse2, rstd))
+            nbytes = int(_lib.lib.diffattn_workspace_bytes(p))
+            ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
+            p.dy = dy.data_ptr()
+            p.dq1, p.dq2, p.dk1, p.dk2, p.dv = (t.data_ptr() for t in (dq1, dq2, dk1, dk2, dv))
+            p.dlambda = dlam.data_ptr()
+            p.workspace, p.workspace_bytes = ws.data_ptr(), nbytes
+            _lib.check(_lib.lib.diffattn_bwd(p), "diffattn_bwd")
+        # fp32 partial kept for callers that shard (batch*head) and sum partials themselves
+        DiffAttnFunction.last_dlambda_fp32 = dlam
+        dlam_out = dlam.to(lam.dtype).reshape(lam.shape) if ctx.needs_input_grad[5] else None
+        return dq1, dq2, dk1, dk2, dv, dlam_out, None, None
+
+    last_dlambda_fp32 = None
+
+
+def MultiheadDiffAttnKernel(q1, q2, k1, k2, v, lambda_scale=-0.5, lambda_init: float = 0.8, rms_norm: bool = False):
+    """Fused differential attention, same signature as the reference (src/layers.py:10-26).
+
+    q1,q2,k1,k2: fp16 CUDA [B,H,N,D]; v: fp16 CUDA [B,H,N,2D]; lambda_scale: 1-element fp16/fp32
+    CUDA tensor (the reference's float default cannot be loaded by its kernel either,
+    src/layers.py:16 vs src/kernel.py:138).  Returns fp16 [B,H,N,2D].  The softmax scale is
+    1/sqrt(D) (src/layers.py:20-22); (1 - lambda_init) is applied only with rms_norm
+    (src/layers.py:74-78).  N must be a multiple of 128 (no masking, README.md:2).
+    """
+    return DiffAttnFunction.apply(q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm)
+
+
+def device_status(device=None) -> None:
+    """Synchronise and raise RuntimeError if a device-side bounded wait gave up in any kernel."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    _lib.check(_lib.lib.diffattn_status(int(dev)), "diffattn_status")
