@@ -75,6 +75,13 @@ int diffattn_fwd(const DiffAttnParams* p);
  * Replaces _diff_attention.backward + diff_attn_bwd (reference src/kernel.py:516-575, :221-458). */
 int diffattn_bwd(const DiffAttnParams* p);
 
+/* The backward is three kernels (row preprocess, dK/dV, dQ).  This entry runs a subset, for timing
+ * each kernel on its own; DKDV and DQ read what PRE wrote to the workspace.  diffattn_bwd(p) is
+ * diffattn_bwd_stages(p, DIFFATTN_STAGE_ALL).  (The reference's backward is one kernel,
+ * src/kernel.py:221-458: stage 1 at :273-299, the dK/dV half at :410-424, the dQ half at :426-436.) */
+enum { DIFFATTN_STAGE_PRE = 1, DIFFATTN_STAGE_DKDV = 2, DIFFATTN_STAGE_DQ = 4, DIFFATTN_STAGE_ALL = 7 };
+int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages);
+
 /* Scratch bytes diffattn_bwd needs for these shapes (the reference allocates its D1/D2 and
  * dLambda partial buffers itself, src/kernel.py:522-529).  The forward needs none. */
 uint64_t diffattn_workspace_bytes(const DiffAttnParams* p);

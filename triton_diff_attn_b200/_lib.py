@@ -11,7 +11,7 @@ import os
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libdiffattn.so")
 
-EXPORTS = ("diffattn_fwd", "diffattn_bwd", "diffattn_workspace_bytes", "diffattn_status",
+EXPORTS = ("diffattn_fwd", "diffattn_bwd", "diffattn_bwd_stages", "diffattn_workspace_bytes", "diffattn_status",
            "diffattn_last_error", "diffattn_version", "diffattn_supports")
 
 ERR_NAMES = {
@@ -21,6 +21,7 @@ ERR_NAMES = {
 VALUE_ERRORS = (-1, -2, -3, -4, -5, -6, -7, -8)   # caller mistakes -> ValueError; the rest RuntimeError
 
 LAMBDA_F16, LAMBDA_F32 = 0, 1
+STAGE_PRE, STAGE_DKDV, STAGE_DQ, STAGE_ALL = 1, 2, 4, 7
 
 
 class DiffAttnParams(C.Structure):
@@ -43,13 +44,15 @@ class DiffAttnParams(C.Structure):
 def _load() -> C.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m triton_diff_attn_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python triton_diff_attn_b200/build.py` "
             "(needs nvcc with sm_100a support). There is no CPU or PyTorch fallback.")
     lib = C.CDLL(LIB_PATH)
     lib.diffattn_fwd.argtypes = [C.POINTER(DiffAttnParams)]
     lib.diffattn_fwd.restype = C.c_int
     lib.diffattn_bwd.argtypes = [C.POINTER(DiffAttnParams)]
     lib.diffattn_bwd.restype = C.c_int
+    lib.diffattn_bwd_stages.argtypes = [C.POINTER(DiffAttnParams), C.c_int32]
+    lib.diffattn_bwd_stages.restype = C.c_int
     lib.diffattn_workspace_bytes.argtypes = [C.POINTER(DiffAttnParams)]
     lib.diffattn_workspace_bytes.restype = C.c_uint64
     lib.diffattn_status.argtypes = [C.c_int32]

@@ -1,6 +1,6 @@
 """Build recipe for libdiffattn.so (hand-written sm_100a CUDA behind a C ABI).
 
-`python -m triton_diff_attn_b200.build` compiles `csrc/diffattn.cu` in-tree with nvcc.  The shared
+`python triton_diff_attn_b200/build.py` (run as a script: importing the package needs the library) compiles `csrc/diffattn.cu` in-tree with nvcc.  The shared
 object sits next to this file so that it travels with the source tree; nothing is JIT-compiled at
 import time.
 """

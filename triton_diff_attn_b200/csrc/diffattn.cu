@@ -165,7 +165,9 @@ int diffattn_fwd(const DiffAttnParams* p) {
   return DIFFATTN_OK;
 }
 
-int diffattn_bwd(const DiffAttnParams* p) {
+int diffattn_bwd(const DiffAttnParams* p) { return diffattn_bwd_stages(p, DIFFATTN_STAGE_ALL); }
+
+int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages) {
   int rc = check_common(p, true);
   if (rc < 0) return rc;
   if (rc == 1) return DIFFATTN_OK;
@@ -190,7 +192,7 @@ int diffattn_bwd(const DiffAttnParams* p) {
   a.n = p->N; a.h = p->H; a.rows = (long long)rows;
 
   // 1. preprocess (grid-stride; one atomic per CTA for d(lambda))
-  {
+  if (stages & DIFFATTN_STAGE_PRE) {
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p->device);
     long long blocks = (long long)((rows + 7) / 8);
@@ -207,7 +209,7 @@ int diffattn_bwd(const DiffAttnParams* p) {
   if ((rc = make_map(&mv, p->v, DV, p->N, p->H, p->B, p->v_stride_n, p->v_stride_h, p->v_stride_b, 128, "v"))) return rc;
   if ((rc = make_map(&mda, a.da, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 64, "dA"))) return rc;
   if ((rc = set_smem(da::diffattn_bwd_dkdv64_kernel, da::dkdv64::SMEM_BYTES))) return rc;
-  {
+  if (stages & DIFFATTN_STAGE_DKDV) {
     dim3 grid(p->N / da::dkdv64::BKV, (unsigned)bh);
     da::diffattn_bwd_dkdv64_kernel<<<grid, da::dkdv64::NUM_THREADS, da::dkdv64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, mda, a);
     DA_CUDA(cudaGetLastError());
@@ -217,7 +219,7 @@ int diffattn_bwd(const DiffAttnParams* p) {
   if ((rc = make_map(&mq2, p->q2, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "q2"))) return rc;
   if ((rc = make_map(&mda, a.da, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 128, "dA"))) return rc;
   if ((rc = set_smem(da::diffattn_bwd_dq64_kernel, da::dq64::SMEM_BYTES))) return rc;
-  {
+  if (stages & DIFFATTN_STAGE_DQ) {
     dim3 grid(p->N / da::dq64::BM, (unsigned)bh);
     da::diffattn_bwd_dq64_kernel<<<grid, da::dq64::NUM_THREADS, da::dq64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, mda, a);
     DA_CUDA(cudaGetLastError());

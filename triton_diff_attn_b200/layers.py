@@ -22,6 +22,9 @@ EPS = 1e-5   # reference src/kernel.py:50
 
 
 def _check_inputs(q1, q2, k1, k2, v, lambda_scale):
+    if not torch.is_tensor(lambda_scale):
+        raise TypeError("lambda_scale must be a 1-element CUDA tensor (the reference loads it from a "
+                        "device pointer, src/kernel.py:138)")
     for name, t in (("q1", q1), ("q2", q2), ("k1", k1), ("k2", k2), ("v", v)):
         if not torch.is_tensor(t):
             raise TypeError(f"{name} must be a tensor")
@@ -32,9 +35,6 @@ def _check_inputs(q1, q2, k1, k2, v, lambda_scale):
                              "the reference (src/kernel.py:175-176)")
         if t.dim() != 4:
             raise ValueError(f"{name} must be [B, H, N, D]")
-    if not torch.is_tensor(lambda_scale):
-        raise TypeError("lambda_scale must be a 1-element CUDA tensor (the reference loads it from a "
-                        "device pointer, src/kernel.py:138)")
     if lambda_scale.numel() != 1 or lambda_scale.dtype not in (torch.float16, torch.float32):
         raise ValueError("lambda_scale must hold one float16 or float32 element")
     if lambda_scale.device != q1.device:
