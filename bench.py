@@ -101,9 +101,11 @@ class ClockSampler:
             for nm, val in zip(names, parts[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(nm)
-        # keep the samples taken under load (upper half of the clock-sorted list)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+        # "under load" = samples whose power draw is at least 60 % of the highest one seen
+        load = [c for c, w in zip(sm, power) if w >= 0.6 * max(power)] if power else []
+        return {"sm_mhz": statistics.median(load) if load else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "samples_under_load": len(load),
+                "reasons": sorted(reasons)}
 
 
 def cpu_sample(workload, heads, steps, warmup, threads=None):
@@ -152,8 +154,8 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -236,13 +238,12 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms) / iters
 
-    for _ in range(args.warmup):
-        step()
-    device_status(local_rank)
-
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(args.warmup):
+        step()
+    device_status(local_rank)
     ms_step = timed(step, args.steps)
     # per-kernel durations (each kernel alone, same resident inputs); L2 is smaller than the inputs
     ms_fwd = timed(fwd, args.steps)

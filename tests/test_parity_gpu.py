@@ -159,7 +159,7 @@ def test_full_size_properties_config2(op):
     """BASELINE config 2 (B4 H16 N4096 D64): size-independent properties instead of a full oracle
     pass, plus the oracle on one sampled (batch, head).
       * heads are independent: the sampled head computed alone equals its slice of the full run;
-      * linearity in dY: backward(2 dY) = 2 backward(dY) exactly in fp16 (power-of-two scaling)."""
+      * linearity in dY: backward(2 dY) = 2 backward(dY) up to fp16 subnormal rounding of dS."""
     b, h, n, d = 4, 16, 4096, 64
     g = torch.Generator(device="cpu").manual_seed(1234)
     dev = torch.device("cuda", 0)
@@ -179,7 +179,7 @@ def test_full_size_properties_config2(op):
     # linearity
     y.backward((2 * dy).to(dev))
     for nm, t in zip(GRADS, leaves):
-        assert torch.equal(t.grad.cpu(), 2 * full[nm]), nm
+        assert oracle.error_metrics(t.grad.cpu(), 2 * full[nm].float())["rel_l2"] < 2e-4, nm
     # sampled head against the oracle and against the full run
     bi, hi = 2, 5
     sl = lambda t: t[bi:bi + 1, hi:hi + 1].contiguous()
