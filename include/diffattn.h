@@ -82,6 +82,29 @@ int diffattn_bwd(const DiffAttnParams* p);
 enum { DIFFATTN_STAGE_PRE = 1, DIFFATTN_STAGE_DKDV = 2, DIFFATTN_STAGE_DQ = 4, DIFFATTN_STAGE_ALL = 7 };
 int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages);
 
+/* Backward without a caller-provided workspace and without any allocation.  (No counterpart in the
+ * reference, whose backward allocates its scratch with torch on every call, src/kernel.py:520-529.)
+ *
+ * For whom: hosts that bind this ABI directly (C, ctypes, another runtime) and have no allocator to
+ * hand: a serving loop that was given a fixed set of buffers up front, or a step loop that must not
+ * call cudaMalloc because that call synchronises the whole device and can fail late under memory
+ * pressure.  Such a caller passes inputs and outputs exactly as for diffattn_bwd and leaves
+ * `workspace` / `workspace_bytes` unset (they are ignored).
+ *
+ * The scratch (dA and the per-row statistics) lives in one array of DIFFATTN_STATIC_SCRATCH_BYTES that
+ * is part of the library image: every GPU that loads the library holds it until the process exits.
+ * Limit: diffattn_workspace_bytes(p) must not exceed it (B*H*N <= 123361 rows at D = 64), otherwise
+ * DIFFATTN_ERR_WORKSPACE is returned and nothing is launched.
+ * The first call on each device looks the array's device address up (one cudaGetSymbolAddress, no
+ * allocation); make that first call outside any stream capture.  The call itself uses no cudaMalloc,
+ * cudaFree or allocating library routine.
+ * All calls on a device share the one array and it keeps what the previous call left there.  Nothing
+ * in it has to start at zero (the preprocess kernel rewrites every byte the other kernels read), but
+ * two calls whose kernels overlap on the GPU (different streams, no ordering) race on it: order
+ * them.  *dlambda is still the caller's to zero. */
+#define DIFFATTN_STATIC_SCRATCH_BYTES (32u << 20)
+int diffattn_bwd_static(const DiffAttnParams* p);
+
 /* Scratch bytes diffattn_bwd needs for these shapes (the reference allocates its D1/D2 and
  * dLambda partial buffers itself, src/kernel.py:522-529).  The forward needs none. */
 uint64_t diffattn_workspace_bytes(const DiffAttnParams* p);

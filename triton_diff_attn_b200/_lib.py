@@ -11,7 +11,7 @@ import os
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libdiffattn.so")
 
-EXPORTS = ("diffattn_fwd", "diffattn_bwd", "diffattn_bwd_stages", "diffattn_workspace_bytes", "diffattn_status",
+EXPORTS = ("diffattn_fwd", "diffattn_bwd", "diffattn_bwd_stages", "diffattn_bwd_static", "diffattn_workspace_bytes", "diffattn_status",
            "diffattn_last_error", "diffattn_version", "diffattn_supports")
 
 ERR_NAMES = {
@@ -22,6 +22,7 @@ VALUE_ERRORS = (-1, -2, -3, -4, -5, -6, -7, -8)   # caller mistakes -> ValueErro
 
 LAMBDA_F16, LAMBDA_F32 = 0, 1
 STAGE_PRE, STAGE_DKDV, STAGE_DQ, STAGE_ALL = 1, 2, 4, 7
+STATIC_SCRATCH_BYTES = 32 << 20
 
 
 class DiffAttnParams(C.Structure):
@@ -53,6 +54,8 @@ def _load() -> C.CDLL:
     lib.diffattn_bwd.restype = C.c_int
     lib.diffattn_bwd_stages.argtypes = [C.POINTER(DiffAttnParams), C.c_int32]
     lib.diffattn_bwd_stages.restype = C.c_int
+    lib.diffattn_bwd_static.argtypes = [C.POINTER(DiffAttnParams)]
+    lib.diffattn_bwd_static.restype = C.c_int
     lib.diffattn_workspace_bytes.argtypes = [C.POINTER(DiffAttnParams)]
     lib.diffattn_workspace_bytes.restype = C.c_uint64
     lib.diffattn_status.argtypes = [C.c_int32]

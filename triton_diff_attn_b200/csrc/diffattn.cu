@@ -227,6 +227,48 @@ int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages) {
   return DIFFATTN_OK;
 }
 
+// ---- allocation-free backward: scratch in a file-scope device array -------------------------------
+// In host code the array's name is only a handle for the runtime, not a device address; the address
+// each device gives it is looked up once per device with cudaGetSymbolAddress and cached.
+static __device__ __align__(256) unsigned char g_static_scratch[DIFFATTN_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+void* g_static_ptr[kMaxDevices] = {nullptr};
+}  // namespace
+
+int diffattn_bwd_static(const DiffAttnParams* p) {
+  if (!p) return fail(DIFFATTN_ERR_NULL_PTR, "params is NULL");
+  if (p->struct_size != sizeof(DiffAttnParams))
+    return fail(DIFFATTN_ERR_BAD_STRUCT, "struct_size %u != %zu", p->struct_size, sizeof(DiffAttnParams));
+  const uint64_t need = diffattn_workspace_bytes(p);
+  if (need > DIFFATTN_STATIC_SCRATCH_BYTES)
+    return fail(DIFFATTN_ERR_WORKSPACE,
+                "diffattn_bwd_static: this shape needs %llu scratch bytes, the built-in array holds %u; "
+                "use diffattn_bwd with a caller workspace",
+                (unsigned long long)need, unsigned(DIFFATTN_STATIC_SCRATCH_BYTES));
+  if (p->device < 0 || p->device >= kMaxDevices)
+    return fail(DIFFATTN_ERR_BAD_SHAPE, "device ordinal %d outside [0,%d)", p->device, kMaxDevices);
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_ptr[p->device]) {
+      // set-up, once per device, with that device current
+      DA_CUDA(cudaSetDevice(p->device));
+      void* addr = nullptr;
+      DA_CUDA(cudaGetSymbolAddress(&addr, g_static_scratch));
+      if (!addr) return fail(DIFFATTN_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+      g_static_ptr[p->device] = addr;
+    }
+    scratch = g_static_ptr[p->device];
+  }
+  DiffAttnParams q = *p;
+  q.workspace = scratch;
+  q.workspace_bytes = DIFFATTN_STATIC_SCRATCH_BYTES;
+  return diffattn_bwd_stages(&q, DIFFATTN_STAGE_ALL);
+}
+
 int diffattn_status(int32_t device) {
   DA_CUDA(cudaSetDevice(device));
   DA_CUDA(cudaDeviceSynchronize());
