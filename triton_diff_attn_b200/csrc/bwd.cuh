@@ -124,10 +124,12 @@ __global__ void __launch_bounds__(256) diffattn_bwd_pre_kernel(const BwdArgs arg
 
 // ------------------------------------------------------------------------------------------------
 // 2. dK1, dK2, dV: one CTA = 128 key/value rows of one (batch, head); query tiles of 64 stream by.
-// TMEM: dV [0,128) dK1 [128,192) dK2 [192,256) S1^T [256,320) S2^T [320,384) dP^T [384,448).
-// Thread = key row.  Warpgroup g handles query columns [32g, 32g+32) of the three score tiles and
-// writes the fp16 A-operands back in place: (P1 - lam P2)^T over dP^T, dS_b^T over S_b^T, each at
-// column offset 32g (16 packed columns).
+// TMEM: dV [0,128) dK1 [128,192) dK2 [192,256) | scores S1^T [256,320) S2^T [320,384) dP^T [384,448) |
+// fp16 A-operands dS1^T [448,480) dS2^T [480,512).  Thread = key row; warpgroup g handles query columns
+// [32g, 32g+32).  The warpgroups pull their scores into registers and release the score columns at once,
+// so the MMAs of tile i+1 run under the elementwise work of tile i.  dS_b^T goes back to TMEM (A-operand of
+// dK_b += dS_b^T Q_b); (P1 - lam P2)^T goes to a double-buffered K-major shared-memory tile (A-operand of
+// dV += Pc^T dA) because TMEM has no columns left for it.
 // ------------------------------------------------------------------------------------------------
 namespace dkdv64 {
 constexpr int BKV = 128, BQ = 64, HD = 64, DV = 128, ST = 3;
@@ -137,17 +139,23 @@ constexpr int Q_BYTES = BQ * HD * 2;        // 8 KB
 constexpr int DA_BYTES = BQ * DV * 2;       // 16 KB, two boxes of 8 KB
 constexpr int STAT_BYTES = BQ * 16;         // 1 KB
 constexpr int STAGE_BYTES = 2 * Q_BYTES + DA_BYTES + STAT_BYTES;   // 33 KB
+constexpr int PC_BYTES = BKV * BQ * 2;      // 16 KB per buffer
 constexpr int OFF_K1 = 0, OFF_K2 = K_BYTES, OFF_V = 2 * K_BYTES;
-constexpr int OFF_STAGE = OFF_V + V_BYTES;                         // 64 KB
-constexpr int OFF_MISC = OFF_STAGE + ST * STAGE_BYTES;
+constexpr int OFF_PC = OFF_V + V_BYTES;                            // 64 KB
+constexpr int OFF_STAGE = OFF_PC + 2 * PC_BYTES;                   // 96 KB
+constexpr int OFF_MISC = OFF_STAGE + ST * STAGE_BYTES;             // 195 KB
 constexpr int MISC_BYTES = 1024;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
 constexpr int NUM_THREADS = 320;
-constexpr int T_DV = 0, T_DK1 = 128, T_DK2 = 192, T_S1 = 256, T_S2 = 320, T_DP = 384;
+constexpr int T_DV = 0, T_DK1 = 128, T_DK2 = 192, T_S1 = 256, T_S2 = 320, T_DP = 384, T_DS1 = 448, T_DS2 = 480;
 struct Misc {
   uint64_t bar_kv;
   uint64_t full[ST], empty[ST];
-  uint64_t s_full, e_done, acc_full;
+  uint64_t s_full;      // scores of a tile written (MMA -> warpgroups)
+  uint64_t s_free;      // scores of a tile are in registers (256 arrivals)
+  uint64_t e_done;      // dS^T in TMEM and Pc in shared memory written (256 arrivals)
+  uint64_t mma_done;    // dV/dK MMAs of a tile completed (operand buffers reusable)
+  uint64_t acc_full;
   uint32_t tmem_slot;
   int abort_flag;
 };
@@ -172,7 +180,9 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
     mbar_init(&misc->bar_kv, 1);
     for (int i = 0; i < ST; ++i) { mbar_init(&misc->full[i], 1); mbar_init(&misc->empty[i], 1); }
     mbar_init(&misc->s_full, 1);
+    mbar_init(&misc->s_free, 256);
     mbar_init(&misc->e_done, 256);
+    mbar_init(&misc->mma_done, 1);
     mbar_init(&misc->acc_full, 1);
     misc->abort_flag = 0;
     mbar_init_fence();
@@ -206,16 +216,12 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
   } else if (warp == 9) {
     if (lane == 0) {
       constexpr uint32_t IDESC_S = make_idesc(BKV, BQ, 0, 0);     // S^T = K Q^T, dP^T = V dA^T
-      constexpr uint32_t IDESC_DV = make_idesc(BKV, DV, 0, 1);    // dV += Pc^T dA   (dA MN-major)
-      constexpr uint32_t IDESC_DK = make_idesc(BKV, HD, 0, 1);    // dK += dS^T Q    (Q MN-major)
+      constexpr uint32_t IDESC_DV = make_idesc(BKV, DV, 0, 1);    // dV += Pc^T dA   (Pc K-major smem, dA MN-major)
+      constexpr uint32_t IDESC_DK = make_idesc(BKV, HD, 0, 1);    // dK += dS^T Q    (dS^T in TMEM, Q MN-major)
       const uint32_t k1a = smem_u32(smem + OFF_K1), k2a = smem_u32(smem + OFF_K2), va = smem_u32(smem + OFF_V);
-      bool ok = mbar_wait(&misc->bar_kv, 0, abort_flag, 501);
-      for (int i = 0; ok && i < nq; ++i) {
-        const int st = i % ST;
-        const uint32_t sp = smem_u32(smem + OFF_STAGE + st * STAGE_BYTES);
+      auto issue_scores = [&](int i) {
+        const uint32_t sp = smem_u32(smem + OFF_STAGE + (i % ST) * STAGE_BYTES);
         const uint32_t q1a = sp, q2a = sp + Q_BYTES, daa = sp + 2 * Q_BYTES;
-        if (!mbar_wait(&misc->full[st], (i / ST) & 1, abort_flag, 502, i)) break;
-        tc_fence_after();
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
           mma_ss(tmem_base + T_S1, sdesc_kmajor(k1a + k * 32), sdesc_kmajor(q1a + k * 32), IDESC_S, k > 0);
@@ -227,29 +233,42 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
           mma_ss(tmem_base + T_DP, sdesc_kmajor(va + (k / 4) * (V_BYTES / 2) + (k % 4) * 32),
                  sdesc_kmajor(daa + (k / 4) * (DA_BYTES / 2) + (k % 4) * 32), IDESC_S, k > 0);
         mma_commit(&misc->s_full);
-        if (!mbar_wait(&misc->e_done, i & 1, abort_flag, 503, i)) break;
+      };
+      bool ok = mbar_wait(&misc->bar_kv, 0, abort_flag, 501);
+      ok = ok && mbar_wait(&misc->full[0], 0, abort_flag, 502);
+      if (ok) {
         tc_fence_after();
+        issue_scores(0);
+        for (int i = 0; i < nq; ++i) {
+          const int st = i % ST;
+          const uint32_t sp = smem_u32(smem + OFF_STAGE + st * STAGE_BYTES);
+          const uint32_t q1a = sp, q2a = sp + Q_BYTES, daa = sp + 2 * Q_BYTES;
+          const uint32_t pca = smem_u32(smem + OFF_PC + (i & 1) * PC_BYTES);
+          if (i + 1 < nq) {
+            if (!mbar_wait(&misc->full[(i + 1) % ST], ((i + 1) / ST) & 1, abort_flag, 503, i)) break;
+            if (!mbar_wait(&misc->s_free, i & 1, abort_flag, 504, i)) break;    // scores(i) are in registers
+            tc_fence_after();
+            issue_scores(i + 1);
+          }
+          if (!mbar_wait(&misc->e_done, i & 1, abort_flag, 505, i)) break;
+          tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < BQ / 16; ++k) {
-          const uint32_t a_col = (k / 2) * 32 + (k % 2) * 8;   // warpgroup k/2 wrote these 16 query columns
-          mma_ts(tmem_base + T_DV, tmem_base + T_DP + a_col, make_sdesc(daa + k * 2048, DA_BYTES / 2, 1024), IDESC_DV,
-                 (i > 0 || k > 0));
-        }
+          for (int k = 0; k < BQ / 16; ++k)
+            mma_ss(tmem_base + T_DV, sdesc_kmajor(pca + k * 32), make_sdesc(daa + k * 2048, DA_BYTES / 2, 1024), IDESC_DV,
+                   (i > 0 || k > 0));
 #pragma unroll
-        for (int k = 0; k < BQ / 16; ++k) {
-          const uint32_t a_col = (k / 2) * 32 + (k % 2) * 8;
-          mma_ts(tmem_base + T_DK1, tmem_base + T_S1 + a_col, make_sdesc(q1a + k * 2048, 16, 1024), IDESC_DK,
-                 (i > 0 || k > 0));
-        }
+          for (int k = 0; k < BQ / 16; ++k)
+            mma_ts(tmem_base + T_DK1, tmem_base + T_DS1 + k * 8, make_sdesc(q1a + k * 2048, 16, 1024), IDESC_DK,
+                   (i > 0 || k > 0));
 #pragma unroll
-        for (int k = 0; k < BQ / 16; ++k) {
-          const uint32_t a_col = (k / 2) * 32 + (k % 2) * 8;
-          mma_ts(tmem_base + T_DK2, tmem_base + T_S2 + a_col, make_sdesc(q2a + k * 2048, 16, 1024), IDESC_DK,
-                 (i > 0 || k > 0));
+          for (int k = 0; k < BQ / 16; ++k)
+            mma_ts(tmem_base + T_DK2, tmem_base + T_DS2 + k * 8, make_sdesc(q2a + k * 2048, 16, 1024), IDESC_DK,
+                   (i > 0 || k > 0));
+          mma_commit(&misc->mma_done);
+          mma_commit(&misc->empty[st]);
         }
-        mma_commit(&misc->empty[st]);
+        mma_commit(&misc->acc_full);
       }
-      mma_commit(&misc->acc_full);
     }
   } else {
     const int g = warp >> 2;
@@ -269,6 +288,8 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
       tmem_ld32(tb + T_S2 + g * 32, s2);
       tmem_ld32(tb + T_DP + g * 32, dp);
       tc_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&misc->s_free);
       uint32_t pc[16], d1[16], d2[16];
 #pragma unroll
       for (int jj = 0; jj < 16; ++jj) {
@@ -288,9 +309,23 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
         d1[jj] = pack_half2(d1v[0], d1v[1]);
         d2[jj] = pack_half2(d2v[0], d2v[1]);
       }
-      tmem_st16(tb + T_DP + g * 32, pc);
-      tmem_st16(tb + T_S1 + g * 32, d1);
-      tmem_st16(tb + T_S2 + g * 32, d2);
+      // operand buffers of tile i-1 (dS^T columns, and Pc buffer of tile i-2) must have been consumed
+      if (i > 0) {
+        if (!mbar_wait(&misc->mma_done, (i - 1) & 1, abort_flag, 605 + g, i)) { ok = false; break; }
+        tc_fence_after();
+      }
+      tmem_st16(tb + T_DS1 + g * 16, d1);
+      tmem_st16(tb + T_DS2 + g * 16, d2);
+      // Pc tile [128 key rows][64 query columns] fp16, 128-byte rows, 16-byte chunks XOR-swizzled by row
+      {
+        uint8_t* prow = smem + OFF_PC + (i & 1) * PC_BYTES + row * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int chunk = (g * 4 + c) ^ (row & 7);
+          *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(pc[4 * c], pc[4 * c + 1], pc[4 * c + 2], pc[4 * c + 3]);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&misc->e_done);
@@ -341,12 +376,14 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
 }
 
 // ------------------------------------------------------------------------------------------------
-// 3. dQ1, dQ2: one CTA = 128 query rows; key/value tiles of 128 stream by.
-// TMEM: S1 [0,128) S2 [128,256) dP [256,384) dQ1 [384,448) dQ2 [448,512).  Thread = query row;
-// warpgroup b forms dS_b = +-P_b (dP - E_b) and writes it as fp16 over S_b (TMEM A-operand of dS_b K_b).
+// 3. dQ1, dQ2: one CTA = 128 query rows; key/value tiles of 128 rows stream by and are consumed in
+// sub-tiles of 64 rows.  TMEM: S1 two 64-column buffers [0,128), S2 [128,256), dP [256,384),
+// dQ1 [384,448), dQ2 [448,512).  Thread = query row; warpgroup b forms dS_b = +-P_b (dP - E_b) and writes
+// it as fp16 over its S buffer (TMEM A-operand of dS_b K_b).  The MMAs of sub-tile t+1 are issued before
+// the issuer waits for dS(t), so the warpgroups always find their next scores ready.
 // ------------------------------------------------------------------------------------------------
 namespace dq64 {
-constexpr int BM = 128, BN = 128, HD = 64, DV = 128, ST = 2;
+constexpr int BM = 128, BN = 128, SUB = 64, HD = 64, DV = 128, ST = 2;
 constexpr int Q_BYTES = BM * HD * 2;        // 16 KB
 constexpr int DA_BYTES = BM * DV * 2;       // 32 KB
 constexpr int K_BYTES = BN * HD * 2;        // 16 KB
@@ -362,7 +399,7 @@ constexpr int T_S1 = 0, T_S2 = 128, T_DP = 256, T_DQ1 = 384, T_DQ2 = 448;
 struct Misc {
   uint64_t bar_q;
   uint64_t full[ST], empty[ST];
-  uint64_t s_full[2], ds_full[2], acc_full;
+  uint64_t s_full[2][2], ds_full[2][2], acc_full;   // [branch][buffer]
   uint32_t tmem_slot;
   int abort_flag;
 };
@@ -382,11 +419,13 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
   const int q_tile = blockIdx.x, bh = blockIdx.y;
   const int b_idx = bh / args.h, h_idx = bh % args.h;
   const int nkv = args.n / BN;
+  const int nsub = 2 * nkv;
 
   if (warp == 8 && lane == 0) {
     mbar_init(&misc->bar_q, 1);
     for (int i = 0; i < ST; ++i) { mbar_init(&misc->full[i], 1); mbar_init(&misc->empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&misc->s_full[i], 1); mbar_init(&misc->ds_full[i], 128); }
+    for (int b = 0; b < 2; ++b)
+      for (int u = 0; u < 2; ++u) { mbar_init(&misc->s_full[b][u], 1); mbar_init(&misc->ds_full[b][u], 128); }
     mbar_init(&misc->acc_full, 1);
     misc->abort_flag = 0;
     mbar_init_fence();
@@ -417,50 +456,66 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
     }
   } else if (warp == 9) {
     if (lane == 0) {
-      constexpr uint32_t IDESC_S = make_idesc(BM, BN, 0, 0);     // S = Q K^T, dP = dA V^T
+      constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0);    // S = Q K^T, dP = dA V^T
       constexpr uint32_t IDESC_DQ = make_idesc(BM, HD, 0, 1);    // dQ += dS K   (K MN-major)
       const uint32_t q1a = smem_u32(smem + OFF_Q1), q2a = smem_u32(smem + OFF_Q2), daa = smem_u32(smem + OFF_DA);
-      bool ok = mbar_wait(&misc->bar_q, 0, abort_flag, 801);
-      for (int j = 0; ok && j < nkv; ++j) {
-        const int st = j % ST;
-        const uint32_t sp = smem_u32(smem + OFF_STAGE + st * STAGE_BYTES);
+      // scores of sub-tile t into buffer t&1: S1 and dP (commit -> branch 1), then S2 (commit -> branch 2)
+      auto issue_scores = [&](int t) {
+        const int j = t >> 1, u = t & 1;
+        const uint32_t sp = smem_u32(smem + OFF_STAGE + (j % ST) * STAGE_BYTES) + u * (SUB * 128);
         const uint32_t k1a = sp, k2a = sp + K_BYTES, va = sp + 2 * K_BYTES;
-        if (!mbar_wait(&misc->full[st], (j / ST) & 1, abort_flag, 802, j)) break;
-        tc_fence_after();
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          mma_ss(tmem_base + T_S1, sdesc_kmajor(q1a + k * 32), sdesc_kmajor(k1a + k * 32), IDESC_S, k > 0);
+          mma_ss(tmem_base + T_S1 + u * SUB, sdesc_kmajor(q1a + k * 32), sdesc_kmajor(k1a + k * 32), IDESC_S, k > 0);
 #pragma unroll
         for (int k = 0; k < DV / 16; ++k)
-          mma_ss(tmem_base + T_DP, sdesc_kmajor(daa + (k / 4) * (DA_BYTES / 2) + (k % 4) * 32),
+          mma_ss(tmem_base + T_DP + u * SUB, sdesc_kmajor(daa + (k / 4) * (DA_BYTES / 2) + (k % 4) * 32),
                  sdesc_kmajor(va + (k / 4) * (V_BYTES / 2) + (k % 4) * 32), IDESC_S, k > 0);
-        mma_commit(&misc->s_full[0]);
+        mma_commit(&misc->s_full[0][u]);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          mma_ss(tmem_base + T_S2, sdesc_kmajor(q2a + k * 32), sdesc_kmajor(k2a + k * 32), IDESC_S, k > 0);
-        mma_commit(&misc->s_full[1]);
-        if (!mbar_wait(&misc->ds_full[0], j & 1, abort_flag, 803, j)) break;
+          mma_ss(tmem_base + T_S2 + u * SUB, sdesc_kmajor(q2a + k * 32), sdesc_kmajor(k2a + k * 32), IDESC_S, k > 0);
+        mma_commit(&misc->s_full[1][u]);
+      };
+      bool ok = mbar_wait(&misc->bar_q, 0, abort_flag, 801);
+      ok = ok && mbar_wait(&misc->full[0], 0, abort_flag, 802);
+      if (ok) {
         tc_fence_after();
+        issue_scores(0);
+        for (int t = 0; t < nsub; ++t) {
+          const int j = t >> 1, u = t & 1;
+          const uint32_t sp = smem_u32(smem + OFF_STAGE + (j % ST) * STAGE_BYTES) + u * (SUB * 128);
+          const uint32_t k1a = sp, k2a = sp + K_BYTES;
+          if (t + 1 < nsub) {
+            const int jn = (t + 1) >> 1;
+            if (((t + 1) & 1) == 0) {
+              if (!mbar_wait(&misc->full[jn % ST], (jn / ST) & 1, abort_flag, 803, t)) break;
+              tc_fence_after();
+            }
+            issue_scores(t + 1);
+          }
+          if (!mbar_wait(&misc->ds_full[0][u], (t >> 1) & 1, abort_flag, 804, t)) break;
+          tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < BN / 16; ++k)
-          mma_ts(tmem_base + T_DQ1, tmem_base + T_S1 + k * 8, make_sdesc(k1a + k * 2048, 16, 1024), IDESC_DQ,
-                 (j > 0 || k > 0));
-        if (!mbar_wait(&misc->ds_full[1], j & 1, abort_flag, 804, j)) break;
-        tc_fence_after();
+          for (int k = 0; k < SUB / 16; ++k)
+            mma_ts(tmem_base + T_DQ1, tmem_base + T_S1 + u * SUB + k * 8, make_sdesc(k1a + k * 2048, 16, 1024), IDESC_DQ,
+                   (t > 0 || k > 0));
+          if (!mbar_wait(&misc->ds_full[1][u], (t >> 1) & 1, abort_flag, 805, t)) break;
+          tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < BN / 16; ++k)
-          mma_ts(tmem_base + T_DQ2, tmem_base + T_S2 + k * 8, make_sdesc(k2a + k * 2048, 16, 1024), IDESC_DQ,
-                 (j > 0 || k > 0));
-        mma_commit(&misc->empty[st]);
+          for (int k = 0; k < SUB / 16; ++k)
+            mma_ts(tmem_base + T_DQ2, tmem_base + T_S2 + u * SUB + k * 8, make_sdesc(k2a + k * 2048, 16, 1024), IDESC_DQ,
+                   (t > 0 || k > 0));
+          if (u) mma_commit(&misc->empty[j % ST]);
+        }
+        mma_commit(&misc->acc_full);
       }
-      mma_commit(&misc->acc_full);
     }
   } else {
     const int br = warp >> 2;
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
     const uint32_t tb = tmem_base + lane_base;
-    const uint32_t t_s = tb + (br ? T_S2 : T_S1);
     const float sl2 = args.sm_scale * 1.4426950408889634f;
     const float lam = load_lambda(args.lambda_ptr, args.lambda_dtype);
     const size_t grow = size_t(bh) * args.n + size_t(q_tile) * BM + row;
@@ -469,26 +524,28 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
     const float e = br ? sv.w : sv.z;
     const float coef = br ? -lam : 1.f;
     bool ok = true;
-    for (int j = 0; j < nkv; ++j) {
-      if (!mbar_wait(&misc->s_full[br], j & 1, abort_flag, 901 + br, j)) { ok = false; break; }
+    for (int t = 0; t < nsub; ++t) {
+      const int u = t & 1;
+      const uint32_t t_s = tb + (br ? T_S2 : T_S1) + u * SUB;
+      const uint32_t t_dp = tb + T_DP + u * SUB;
+      if (!mbar_wait(&misc->s_full[br][u], (t >> 1) & 1, abort_flag, 901 + br, t)) { ok = false; break; }
       tc_fence_after();
+      uint32_t s[SUB], dp[SUB];
+      tmem_ld32(t_s, s);
+      tmem_ld32(t_dp, dp);
+      tmem_ld32(t_s + 32, s + 32);
+      tmem_ld32(t_dp + 32, dp + 32);
+      tc_wait_ld();
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32], dp[32], ds[16];
-        tmem_ld32(t_s + c * 32, s);
-        tmem_ld32(tb + T_DP + c * 32, dp);
-        tc_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = coef * ex2(fmaf(__uint_as_float(s[2 * i]), sl2, neg_l));
-          const float p1 = coef * ex2(fmaf(__uint_as_float(s[2 * i + 1]), sl2, neg_l));
-          ds[i] = pack_half2(p0 * (__uint_as_float(dp[2 * i]) - e), p1 * (__uint_as_float(dp[2 * i + 1]) - e));
-        }
-        tmem_st16(t_s + c * 16, ds);
+      for (int i = 0; i < SUB / 2; ++i) {
+        const float p0 = coef * ex2(fmaf(__uint_as_float(s[2 * i]), sl2, neg_l));
+        const float p1 = coef * ex2(fmaf(__uint_as_float(s[2 * i + 1]), sl2, neg_l));
+        s[i] = pack_half2(p0 * (__uint_as_float(dp[2 * i]) - e), p1 * (__uint_as_float(dp[2 * i + 1]) - e));
       }
+      tmem_st32(t_s, s);
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(&misc->ds_full[br]);
+      mbar_arrive(&misc->ds_full[br][u]);
     }
     ok = ok && mbar_wait(&misc->acc_full, 0, abort_flag, 911 + br);
     tc_fence_after();

@@ -5,8 +5,10 @@
 //   warps 4-7  softmax of branch 2
 //   warp  8    TMA producer: Q1,Q2 once; K1,K2 and V tiles through two mbarrier rings
 //   warp  9    tcgen05.mma issuer (one elected thread) and TMEM owner
-// TMEM (512 columns of 128 lanes x 32 bit): S1 [0,128) S2 [128,256) O1 [256,384) O2 [384,512);
-// P_b (fp16, two per column) overwrites the first 64 columns of S_b and is the TMEM A-operand of P_b V.
+// TMEM (512 columns of 128 lanes x 32 bit): S1 two 64-column buffers [0,128), S2 likewise [128,256),
+// O1 [256,384), O2 [384,512).  Scores are produced in sub-tiles of 64 key rows into alternating buffers, so
+// the MMA for sub-tile t+1 runs while the softmax warpgroup works on sub-tile t.  P_b (fp16, two per
+// column) overwrites the first 32 columns of its S buffer and is the TMEM A-operand of P_b V.
 // Replaces the reference's Triton forward (src/kernel.py:21-207): same math (two online softmaxes,
 // O = O1/l1 - lambda O2/l2, RMSNorm * (1 - lambda_init)), but saves lse1, lse2, rstd and A2 = P2 V
 // instead of O1/O2.
@@ -37,7 +39,8 @@ __device__ __forceinline__ float load_lambda(const void* p, int dtype) {
 
 namespace fwd64 {
 constexpr int BM = 128;            // query rows per CTA
-constexpr int BN = 128;            // key/value rows per iteration
+constexpr int BN = 128;            // key/value rows per shared-memory tile
+constexpr int SUB = 64;            // key/value rows per MMA sub-tile (one S buffer in TMEM)
 constexpr int HD = 64;
 constexpr int DV = 128;
 constexpr int KS = 3;              // K ring depth
@@ -53,14 +56,17 @@ constexpr int OFF_MISC = OFF_V + VS * V_BYTES;           // barriers, coefficien
 constexpr int MISC_BYTES = 4096;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024; // +1024 for manual alignment
 constexpr int NUM_THREADS = 320;
+// TMEM columns: S_b buffer u at 128*b + 64*u; O1 at 256, O2 at 384
+constexpr int T_O = 256;
 
 struct Misc {
   uint64_t bar_q;
   uint64_t k_full[KS], k_empty[KS];
   uint64_t v_full[VS], v_empty[VS];
-  uint64_t s_full[2];
-  uint64_t p_full[2];
-  uint64_t o_full;
+  uint64_t s_full[2][2];     // [branch][buffer]: S sub-tile written by the MMA
+  uint64_t p_full[2][2];     // [branch][buffer]: P written by the softmax warpgroup (128 arrivals)
+  uint64_t o_done[2];        // [branch]: one phase per P V sub-tile MMA
+  uint64_t o_full;           // everything accumulated
   uint32_t tmem_slot;
   int abort_flag;
   float coef1[BM];     // 1 / l1
@@ -69,6 +75,8 @@ struct Misc {
 };
 static_assert(sizeof(Misc) <= MISC_BYTES, "misc area too small");
 }  // namespace fwd64
+
+__device__ __forceinline__ float max3(float a, float b, float c) { return fmaxf(fmaxf(a, b), c); }
 
 __global__ void __launch_bounds__(fwd64::NUM_THREADS, 1)
 diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
@@ -87,12 +95,16 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
   const int b_idx = bh / args.h;
   const int h_idx = bh % args.h;
   const int nkv = args.n / BN;
+  const int nsub = 2 * nkv;          // 64-row sub-tiles
 
   if (warp == 8 && lane == 0) {
     mbar_init(&misc->bar_q, 1);
     for (int i = 0; i < KS; ++i) { mbar_init(&misc->k_full[i], 1); mbar_init(&misc->k_empty[i], 1); }
     for (int i = 0; i < VS; ++i) { mbar_init(&misc->v_full[i], 1); mbar_init(&misc->v_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&misc->s_full[i], 1); mbar_init(&misc->p_full[i], 128); }
+    for (int b = 0; b < 2; ++b) {
+      for (int u = 0; u < 2; ++u) { mbar_init(&misc->s_full[b][u], 1); mbar_init(&misc->p_full[b][u], 128); }
+      mbar_init(&misc->o_done[b], 1);
+    }
     mbar_init(&misc->o_full, 1);
     misc->abort_flag = 0;
     mbar_init_fence();
@@ -127,23 +139,29 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     }
   } else if (warp == 9) {
     // -------------------------------- MMA issuer --------------------------------
+    // Sub-tile t covers key rows [64t, 64t+64).  S_b(t+1) is issued before waiting for P_b(t), so the
+    // softmax warpgroups always find their next scores ready.
     if (lane == 0) {
-      constexpr uint32_t IDESC_S = make_idesc(BM, BN, 0, 0);    // S = Q K^T, both K-major
+      constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0);   // S = Q K^T, both K-major
       constexpr uint32_t IDESC_O = make_idesc(BM, DV, 0, 1);    // O += P V, V is MN-major
       const uint32_t q_addr[2] = {smem_u32(smem + OFF_Q1), smem_u32(smem + OFF_Q2)};
-      auto issue_s = [&](int br, int j) {
-        const uint32_t k_addr = smem_u32(smem + OFF_K + (j % KS) * 2 * K_BYTES + br * K_BYTES);
+      auto issue_s = [&](int br, int t) {
+        const int j = t >> 1, half = t & 1;
+        const uint32_t k_addr = smem_u32(smem + OFF_K + (j % KS) * 2 * K_BYTES + br * K_BYTES) + half * (SUB * 128);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          mma_ss(tmem_base + br * 128, sdesc_kmajor(q_addr[br] + k * 32), sdesc_kmajor(k_addr + k * 32), IDESC_S, k > 0);
-        mma_commit(&misc->s_full[br]);
+          mma_ss(tmem_base + br * 128 + (t & 1) * SUB, sdesc_kmajor(q_addr[br] + k * 32), sdesc_kmajor(k_addr + k * 32),
+                 IDESC_S, k > 0);
+        mma_commit(&misc->s_full[br][t & 1]);
       };
-      auto issue_pv = [&](int br, int j) {
-        const uint32_t v_addr = smem_u32(smem + OFF_V + (j % VS) * V_BYTES);
+      auto issue_pv = [&](int br, int t) {
+        const int j = t >> 1, half = t & 1;
+        const uint32_t v_addr = smem_u32(smem + OFF_V + (j % VS) * V_BYTES) + half * (SUB * 128);
 #pragma unroll
-        for (int k = 0; k < BN / 16; ++k)
-          mma_ts(tmem_base + 256 + br * 128, tmem_base + br * 128 + k * 8,
-                 make_sdesc(v_addr + k * 2048, V_BYTES / 2, 1024), IDESC_O, (j > 0 || k > 0));
+        for (int k = 0; k < SUB / 16; ++k)
+          mma_ts(tmem_base + T_O + br * 128, tmem_base + br * 128 + (t & 1) * SUB + k * 8,
+                 make_sdesc(v_addr + k * 2048, V_BYTES / 2, 1024), IDESC_O, (t > 0 || k > 0));
+        mma_commit(&misc->o_done[br]);
       };
       bool ok = mbar_wait(&misc->bar_q, 0, abort_flag, 201);
       ok = ok && mbar_wait(&misc->k_full[0], 0, abort_flag, 202);
@@ -151,26 +169,28 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
         tc_fence_after();
         issue_s(0, 0);
         issue_s(1, 0);
-        mma_commit(&misc->k_empty[0]);
-        for (int j = 0; j < nkv; ++j) {
-          const int vs = j % VS;
-          if (!mbar_wait(&misc->v_full[vs], (j / VS) & 1, abort_flag, 203, j)) break;
-          if (!mbar_wait(&misc->p_full[0], j & 1, abort_flag, 204, j)) break;
-          tc_fence_after();
-          issue_pv(0, j);
-          if (j + 1 < nkv) {
-            if (!mbar_wait(&misc->k_full[(j + 1) % KS], ((j + 1) / KS) & 1, abort_flag, 205, j)) break;
-            tc_fence_after();
-            issue_s(0, j + 1);
+        for (int t = 0; t < nsub; ++t) {
+          const int j = t >> 1;
+          if (t + 1 < nsub) {
+            const int jn = (t + 1) >> 1;
+            if (((t + 1) & 1) == 0) {
+              if (!mbar_wait(&misc->k_full[jn % KS], (jn / KS) & 1, abort_flag, 205, t)) break;
+              tc_fence_after();
+            }
+            issue_s(0, t + 1);
+            issue_s(1, t + 1);
+            if ((t + 1) & 1) mma_commit(&misc->k_empty[jn % KS]);   // both halves of K tile jn consumed
           }
-          if (!mbar_wait(&misc->p_full[1], j & 1, abort_flag, 206, j)) break;
-          tc_fence_after();
-          issue_pv(1, j);
-          mma_commit(&misc->v_empty[vs]);
-          if (j + 1 < nkv) {
-            issue_s(1, j + 1);
-            mma_commit(&misc->k_empty[(j + 1) % KS]);
+          if ((t & 1) == 0) {
+            if (!mbar_wait(&misc->v_full[j % VS], (j / VS) & 1, abort_flag, 203, t)) break;
           }
+          if (!mbar_wait(&misc->p_full[0][t & 1], (t >> 1) & 1, abort_flag, 204, t)) break;
+          tc_fence_after();
+          issue_pv(0, t);
+          if (!mbar_wait(&misc->p_full[1][t & 1], (t >> 1) & 1, abort_flag, 206, t)) break;
+          tc_fence_after();
+          issue_pv(1, t);
+          if (t & 1) mma_commit(&misc->v_empty[j % VS]);
         }
         mma_commit(&misc->o_full);
       }
@@ -180,32 +200,42 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     const int br = warp >> 2;                       // branch handled by this warpgroup
     const int row = (warp & 3) * 32 + lane;         // query row inside the tile = TMEM lane
     const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
-    const uint32_t t_s = tmem_base + lane_base + br * 128;
-    const uint32_t t_o = tmem_base + lane_base + 256 + br * 128;
+    const uint32_t t_s0 = tmem_base + lane_base + br * 128;
+    const uint32_t t_o = tmem_base + lane_base + T_O + br * 128;
     const float sl2 = args.sm_scale * 1.4426950408889634f;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
 
-    for (int j = 0; j < nkv; ++j) {
-      if (!mbar_wait(&misc->s_full[br], j & 1, abort_flag, 301 + br, j)) { ok = false; break; }
+    for (int t = 0; t < nsub; ++t) {
+      const uint32_t t_s = t_s0 + (t & 1) * SUB;
+      if (!mbar_wait(&misc->s_full[br][t & 1], (t >> 1) & 1, abort_flag, 301 + br, t)) { ok = false; break; }
       tc_fence_after();
-      uint32_t sr[128];
+      uint32_t sr[SUB];
       tmem_ld32(t_s + 0, sr);
       tmem_ld32(t_s + 32, sr + 32);
-      tmem_ld32(t_s + 64, sr + 64);
-      tmem_ld32(t_s + 96, sr + 96);
       tc_wait_ld();
-      float mx = __uint_as_float(sr[0]);
+      // row maximum as 8 independent chains of 3-input maxima
+      float mx[8];
 #pragma unroll
-      for (int i = 1; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(sr[i]));
-      const float m_new = fmaxf(m_run, mx);
-      if (j == 0) {
+      for (int i = 0; i < 8; ++i) mx[i] = __uint_as_float(sr[i]);
+#pragma unroll
+      for (int i = 8; i < SUB; i += 16) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          mx[c] = max3(mx[c], __uint_as_float(sr[i + c]), __uint_as_float(sr[i + 8 + c < SUB ? i + 8 + c : i + c]));
+      }
+      const float mxa = max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7]));
+      const float m_new = fmaxf(m_run, mxa);
+      if (t == 0) {
         m_run = m_new;
       } else {
         // Rescale only when the running maximum moved by more than 2^8; otherwise keep the stale
         // maximum (P stays below 256, exact in the final normalisation).
         const bool need = (m_new - m_run) * sl2 > 8.f;
         if (__any_sync(0xffffffffu, need)) {
+          // O_b must be quiescent: wait for P_b V of the previous sub-tile
+          if (!mbar_wait(&misc->o_done[br], (t - 1) & 1, abort_flag, 305 + br, t)) { ok = false; break; }
+          tc_fence_after();
           const float scale = need ? ex2((m_run - m_new) * sl2) : 1.f;
           if (need) m_run = m_new;
           l_run *= scale;
@@ -221,21 +251,20 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
         }
       }
       const float neg = -m_run * sl2;
-      float sum0 = 0.f, sum1 = 0.f;
+      float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
+      for (int i = 0; i < SUB / 2; ++i) {
         const float p0 = ex2(fmaf(__uint_as_float(sr[2 * i]), sl2, neg));
         const float p1 = ex2(fmaf(__uint_as_float(sr[2 * i + 1]), sl2, neg));
-        sum0 += p0;
-        sum1 += p1;
+        sum[(2 * i) & 3] += p0;
+        sum[(2 * i + 1) & 3] += p1;
         sr[i] = pack_half2(p0, p1);
       }
-      l_run += sum0 + sum1;
-      tmem_st32(t_s + 0, sr);
-      tmem_st32(t_s + 32, sr + 32);
+      l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+      tmem_st32(t_s, sr);
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(&misc->p_full[br]);
+      mbar_arrive(&misc->p_full[br][t & 1]);
     }
 
     // ---- epilogue: every thread runs every barrier; only the global writes depend on `ok`
@@ -248,8 +277,8 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     const float c1 = misc->coef1[row];
     const float c2 = misc->coef2[row];
     // this warpgroup owns value columns [64*br, 64*br+64) of both accumulators
-    const uint32_t t_o1 = tmem_base + lane_base + 256 + br * 64;
-    const uint32_t t_o2 = tmem_base + lane_base + 384 + br * 64;
+    const uint32_t t_o1 = tmem_base + lane_base + T_O + br * 64;
+    const uint32_t t_o2 = tmem_base + lane_base + T_O + 128 + br * 64;
     uint32_t o1[64], o2[64];
     tmem_ld32(t_o1, o1);
     tmem_ld32(t_o1 + 32, o1 + 32);
