@@ -194,7 +194,7 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&misc->tmem_slot);
 
   if (warp == 8) {
-    if (lane == 0) {
+    if (elect_one()) {
       mbar_expect_tx(&misc->bar_kv, 2 * K_BYTES + V_BYTES);
       tma_load_4d(smem + OFF_K1, &tm_k1, &misc->bar_kv, 0, kv_tile * BKV, h_idx, b_idx);
       tma_load_4d(smem + OFF_K2, &tm_k2, &misc->bar_kv, 0, kv_tile * BKV, h_idx, b_idx);
@@ -214,58 +214,66 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
       }
     }
   } else if (warp == 9) {
-    if (lane == 0) {
+    // One elected thread issues every MMA; descriptors advance by 32-bit adds (see sm100.cuh).
+    if (elect_one()) {
       constexpr uint32_t IDESC_S = make_idesc(BKV, BQ, 0, 0);     // S^T = K Q^T, dP^T = V dA^T
       constexpr uint32_t IDESC_DV = make_idesc(BKV, DV, 0, 1);    // dV += Pc^T dA   (Pc K-major smem, dA MN-major)
       constexpr uint32_t IDESC_DK = make_idesc(BKV, HD, 0, 1);    // dK += dS^T Q    (dS^T in TMEM, Q MN-major)
-      const uint32_t k1a = smem_u32(smem + OFF_K1), k2a = smem_u32(smem + OFF_K2), va = smem_u32(smem + OFF_V);
-      auto issue_scores = [&](int i) {
-        const uint32_t sp = smem_u32(smem + OFF_STAGE + (i % ST) * STAGE_BYTES);
-        const uint32_t q1a = sp, q2a = sp + Q_BYTES, daa = sp + 2 * Q_BYTES;
+      const uint32_t k1_lo = sdesc_lo(smem_u32(smem + OFF_K1)), k2_lo = sdesc_lo(smem_u32(smem + OFF_K2));
+      const uint32_t v_lo = sdesc_lo(smem_u32(smem + OFF_V));
+      const uint32_t pc_lo0 = sdesc_lo(smem_u32(smem + OFF_PC));
+      const uint32_t st_lo0 = sdesc_lo(smem_u32(smem + OFF_STAGE));
+      constexpr uint32_t DA_MN_LBO = ((DA_BYTES / 2) >> 4) << 16;   // dA as MN-major B: 64-column atoms 8 KB apart
+      const uint32_t tb = tmem_base;
+      auto issue_scores = [&](uint32_t sp_lo) {
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) mma_ss_lo(tb + T_S1, k1_lo + k * 2, sp_lo + k * 2, IDESC_S, k > 0);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          mma_ss(tmem_base + T_S1, sdesc_kmajor(k1a + k * 32), sdesc_kmajor(q1a + k * 32), IDESC_S, k > 0);
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
-          mma_ss(tmem_base + T_S2, sdesc_kmajor(k2a + k * 32), sdesc_kmajor(q2a + k * 32), IDESC_S, k > 0);
+          mma_ss_lo(tb + T_S2, k2_lo + k * 2, sp_lo + (Q_BYTES >> 4) + k * 2, IDESC_S, k > 0);
 #pragma unroll
         for (int k = 0; k < DV / 16; ++k)
-          mma_ss(tmem_base + T_DP, sdesc_kmajor(va + (k / 4) * (V_BYTES / 2) + (k % 4) * 32),
-                 sdesc_kmajor(daa + (k / 4) * (DA_BYTES / 2) + (k % 4) * 32), IDESC_S, k > 0);
+          mma_ss_lo(tb + T_DP, v_lo + (k / 4) * ((V_BYTES / 2) >> 4) + (k % 4) * 2,
+                    sp_lo + ((2 * Q_BYTES) >> 4) + (k / 4) * ((DA_BYTES / 2) >> 4) + (k % 4) * 2, IDESC_S, k > 0);
         mma_commit(&misc->s_full);
       };
       bool ok = mbar_wait(&misc->bar_kv, 0, abort_flag, 501);
       ok = ok && mbar_wait(&misc->full[0], 0, abort_flag, 502);
       if (ok) {
         tc_fence_after();
-        issue_scores(0);
+        issue_scores(st_lo0);
+        int st = 0;
+        uint32_t st_par = 0;
         for (int i = 0; i < nq; ++i) {
-          const int st = i % ST;
-          const uint32_t sp = smem_u32(smem + OFF_STAGE + st * STAGE_BYTES);
-          const uint32_t q1a = sp, q2a = sp + Q_BYTES, daa = sp + 2 * Q_BYTES;
-          const uint32_t pca = smem_u32(smem + OFF_PC + (i & 1) * PC_BYTES);
+          const uint32_t sp_lo = st_lo0 + st * (STAGE_BYTES >> 4);
+          const uint32_t pc_lo = pc_lo0 + (i & 1) * (PC_BYTES >> 4);
+          const uint32_t ph = i & 1;
+          int st_n = st + 1;
+          uint32_t par_n = st_par;
+          if (st_n == ST) { st_n = 0; par_n ^= 1; }
           if (i + 1 < nq) {
-            if (!mbar_wait(&misc->full[(i + 1) % ST], ((i + 1) / ST) & 1, abort_flag, 503, i)) break;
-            if (!mbar_wait(&misc->s_free, i & 1, abort_flag, 504, i)) break;    // scores(i) are in registers
+            if (!mbar_wait(&misc->full[st_n], par_n, abort_flag, 503, i)) break;
+            if (!mbar_wait(&misc->s_free, ph, abort_flag, 504, i)) break;    // scores(i) are in registers
             tc_fence_after();
-            issue_scores(i + 1);
+            issue_scores(st_lo0 + st_n * (STAGE_BYTES >> 4));
           }
-          if (!mbar_wait(&misc->e_done, i & 1, abort_flag, 505, i)) break;
+          if (!mbar_wait(&misc->e_done, ph, abort_flag, 505, i)) break;
           tc_fence_after();
+          const uint32_t first = i > 0;
 #pragma unroll
           for (int k = 0; k < BQ / 16; ++k)
-            mma_ss(tmem_base + T_DV, sdesc_kmajor(pca + k * 32), make_sdesc(daa + k * 2048, DA_BYTES / 2, 1024), IDESC_DV,
-                   (i > 0 || k > 0));
+            mma_ss_lo(tb + T_DV, pc_lo + k * 2, sp_lo + ((2 * Q_BYTES) >> 4) + DA_MN_LBO - (1u << 16) + k * (2048 >> 4), IDESC_DV,
+                      k > 0 ? 1u : first);
 #pragma unroll
           for (int k = 0; k < BQ / 16; ++k)
-            mma_ts(tmem_base + T_DK1, tmem_base + T_DS1 + k * 8, make_sdesc(q1a + k * 2048, 16, 1024), IDESC_DK,
-                   (i > 0 || k > 0));
+            mma_ts_lo(tb + T_DK1, tb + T_DS1 + k * 8, sp_lo + k * (2048 >> 4), IDESC_DK, k > 0 ? 1u : first);
 #pragma unroll
           for (int k = 0; k < BQ / 16; ++k)
-            mma_ts(tmem_base + T_DK2, tmem_base + T_DS2 + k * 8, make_sdesc(q2a + k * 2048, 16, 1024), IDESC_DK,
-                   (i > 0 || k > 0));
+            mma_ts_lo(tb + T_DK2, tb + T_DS2 + k * 8, sp_lo + (Q_BYTES >> 4) + k * (2048 >> 4), IDESC_DK, k > 0 ? 1u : first);
           mma_commit(&misc->mma_done);
           mma_commit(&misc->empty[st]);
+          st = st_n;
+          st_par = par_n;
         }
         mma_commit(&misc->acc_full);
       }
@@ -437,7 +445,7 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&misc->tmem_slot);
 
   if (warp == 8) {
-    if (lane == 0) {
+    if (elect_one()) {
       mbar_expect_tx(&misc->bar_q, 2 * Q_BYTES + DA_BYTES);
       tma_load_4d(smem + OFF_Q1, &tm_q1, &misc->bar_q, 0, q_tile * BM, h_idx, b_idx);
       tma_load_4d(smem + OFF_Q2, &tm_q2, &misc->bar_q, 0, q_tile * BM, h_idx, b_idx);
@@ -455,58 +463,72 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
       }
     }
   } else if (warp == 9) {
-    if (lane == 0) {
+    // One elected thread issues every MMA; descriptors advance by 32-bit adds (see sm100.cuh).
+    if (elect_one()) {
       constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0);    // S = Q K^T, dP = dA V^T
       constexpr uint32_t IDESC_DQ = make_idesc(BM, HD, 0, 1);    // dQ += dS K   (K MN-major)
-      const uint32_t q1a = smem_u32(smem + OFF_Q1), q2a = smem_u32(smem + OFF_Q2), daa = smem_u32(smem + OFF_DA);
-      // scores of sub-tile t into buffer t&1: S1 and dP (commit -> branch 1), then S2 (commit -> branch 2)
-      auto issue_scores = [&](int t) {
-        const int j = t >> 1, u = t & 1;
-        const uint32_t sp = smem_u32(smem + OFF_STAGE + (j % ST) * STAGE_BYTES) + u * (SUB * 128);
-        const uint32_t k1a = sp, k2a = sp + K_BYTES, va = sp + 2 * K_BYTES;
+      constexpr uint32_t HALF = (SUB * 128) >> 4;
+      const uint32_t q1_lo = sdesc_lo(smem_u32(smem + OFF_Q1)), q2_lo = sdesc_lo(smem_u32(smem + OFF_Q2));
+      const uint32_t da_lo = sdesc_lo(smem_u32(smem + OFF_DA));
+      const uint32_t st_lo0 = sdesc_lo(smem_u32(smem + OFF_STAGE));
+      const uint32_t tb = tmem_base;
+      // scores of a 64-row sub-tile into buffer u: S1 and dP (commit -> branch 1), then S2 (commit -> branch 2)
+      auto issue_scores = [&](uint32_t sp_lo, int u) {
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          mma_ss(tmem_base + T_S1 + u * SUB, sdesc_kmajor(q1a + k * 32), sdesc_kmajor(k1a + k * 32), IDESC_S, k > 0);
+          mma_ss_lo(tb + T_S1 + u * SUB, q1_lo + k * 2, sp_lo + u * HALF + k * 2, IDESC_S, k > 0);
 #pragma unroll
         for (int k = 0; k < DV / 16; ++k)
-          mma_ss(tmem_base + T_DP + u * SUB, sdesc_kmajor(daa + (k / 4) * (DA_BYTES / 2) + (k % 4) * 32),
-                 sdesc_kmajor(va + (k / 4) * (V_BYTES / 2) + (k % 4) * 32), IDESC_S, k > 0);
+          mma_ss_lo(tb + T_DP + u * SUB, da_lo + (k / 4) * ((DA_BYTES / 2) >> 4) + (k % 4) * 2,
+                    sp_lo + ((2 * K_BYTES) >> 4) + (k / 4) * ((V_BYTES / 2) >> 4) + u * HALF + (k % 4) * 2, IDESC_S, k > 0);
         mma_commit(&misc->s_full[0][u]);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          mma_ss(tmem_base + T_S2 + u * SUB, sdesc_kmajor(q2a + k * 32), sdesc_kmajor(k2a + k * 32), IDESC_S, k > 0);
+          mma_ss_lo(tb + T_S2 + u * SUB, q2_lo + k * 2, sp_lo + (K_BYTES >> 4) + u * HALF + k * 2, IDESC_S, k > 0);
         mma_commit(&misc->s_full[1][u]);
+      };
+      auto issue_dq = [&](int br, uint32_t sp_lo, int u, uint32_t first) {
+#pragma unroll
+        for (int k = 0; k < SUB / 16; ++k)
+          mma_ts_lo(tb + (br ? T_DQ2 : T_DQ1), tb + (br ? T_S2 : T_S1) + u * SUB + k * 8,
+                    sp_lo + br * (K_BYTES >> 4) + u * HALF + k * (2048 >> 4), IDESC_DQ, k > 0 ? 1u : first);
       };
       bool ok = mbar_wait(&misc->bar_q, 0, abort_flag, 801);
       ok = ok && mbar_wait(&misc->full[0], 0, abort_flag, 802);
       if (ok) {
         tc_fence_after();
-        issue_scores(0);
-        for (int t = 0; t < nsub; ++t) {
-          const int j = t >> 1, u = t & 1;
-          const uint32_t sp = smem_u32(smem + OFF_STAGE + (j % ST) * STAGE_BYTES) + u * (SUB * 128);
-          const uint32_t k1a = sp, k2a = sp + K_BYTES;
-          if (t + 1 < nsub) {
-            const int jn = (t + 1) >> 1;
-            if (((t + 1) & 1) == 0) {
-              if (!mbar_wait(&misc->full[jn % ST], (jn / ST) & 1, abort_flag, 803, t)) break;
-              tc_fence_after();
-            }
-            issue_scores(t + 1);
+        issue_scores(st_lo0, 0);
+        int st = 0;
+        uint32_t st_par = 0;
+        for (int j = 0; j < nkv; ++j) {
+          const uint32_t sp_lo = st_lo0 + st * (STAGE_BYTES >> 4);
+          const uint32_t ph = j & 1;
+          int st_n = st + 1;
+          uint32_t par_n = st_par;
+          if (st_n == ST) { st_n = 0; par_n ^= 1; }
+          // ---- sub-tile 2j (buffer 0): scores of 2j+1 first
+          issue_scores(sp_lo, 1);
+          if (!mbar_wait(&misc->ds_full[0][0], ph, abort_flag, 804, j)) break;
+          tc_fence_after();
+          issue_dq(0, sp_lo, 0, j > 0);
+          if (!mbar_wait(&misc->ds_full[1][0], ph, abort_flag, 805, j)) break;
+          tc_fence_after();
+          issue_dq(1, sp_lo, 0, j > 0);
+          // ---- sub-tile 2j+1 (buffer 1): scores of 2j+2 (next tile) first
+          if (j + 1 < nkv) {
+            if (!mbar_wait(&misc->full[st_n], par_n, abort_flag, 803, j)) break;
+            tc_fence_after();
+            issue_scores(st_lo0 + st_n * (STAGE_BYTES >> 4), 0);
           }
-          if (!mbar_wait(&misc->ds_full[0][u], (t >> 1) & 1, abort_flag, 804, t)) break;
+          if (!mbar_wait(&misc->ds_full[0][1], ph, abort_flag, 806, j)) break;
           tc_fence_after();
-#pragma unroll
-          for (int k = 0; k < SUB / 16; ++k)
-            mma_ts(tmem_base + T_DQ1, tmem_base + T_S1 + u * SUB + k * 8, make_sdesc(k1a + k * 2048, 16, 1024), IDESC_DQ,
-                   (t > 0 || k > 0));
-          if (!mbar_wait(&misc->ds_full[1][u], (t >> 1) & 1, abort_flag, 805, t)) break;
+          issue_dq(0, sp_lo, 1, 1);
+          if (!mbar_wait(&misc->ds_full[1][1], ph, abort_flag, 807, j)) break;
           tc_fence_after();
-#pragma unroll
-          for (int k = 0; k < SUB / 16; ++k)
-            mma_ts(tmem_base + T_DQ2, tmem_base + T_S2 + u * SUB + k * 8, make_sdesc(k2a + k * 2048, 16, 1024), IDESC_DQ,
-                   (t > 0 || k > 0));
-          if (u) mma_commit(&misc->empty[j % ST]);
+          issue_dq(1, sp_lo, 1, 1);
+          mma_commit(&misc->empty[st]);
+          st = st_n;
+          st_par = par_n;
         }
         mma_commit(&misc->acc_full);
       }

@@ -269,6 +269,14 @@ int diffattn_bwd_static(const DiffAttnParams* p) {
   return diffattn_bwd_stages(&q, DIFFATTN_STAGE_ALL);
 }
 
+#ifdef DA_TIMING
+int diffattn_debug_timing(long long* out, int n) {
+  DA_CUDA(cudaDeviceSynchronize());
+  DA_CUDA(cudaMemcpyFromSymbol(out, da::g_timing, sizeof(long long) * n));
+  return 0;
+}
+#endif
+
 int diffattn_status(int32_t device) {
   DA_CUDA(cudaSetDevice(device));
   DA_CUDA(cudaDeviceSynchronize());

@@ -37,6 +37,13 @@ __device__ __forceinline__ float load_lambda(const void* p, int dtype) {
   return dtype == 0 ? __half2float(*reinterpret_cast<const __half*>(p)) : *reinterpret_cast<const float*>(p);
 }
 
+#ifdef DA_TIMING
+__device__ long long g_timing[4096];
+#define DA_TS(slot) do { if (tm_on) g_timing[tm_base + (slot)] = clock64(); } while (0)
+#else
+#define DA_TS(slot) do { } while (0)
+#endif
+
 namespace fwd64 {
 constexpr int BM = 128;            // query rows per CTA
 constexpr int BN = 128;            // key/value rows per shared-memory tile
@@ -121,7 +128,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
 
   if (warp == 8) {
     // ------------------------------- TMA producer -------------------------------
-    if (lane == 0) {
+    if (elect_one()) {
       mbar_expect_tx(&misc->bar_q, 2 * Q_BYTES);
       tma_load_4d(smem + OFF_Q1, &tm_q1, &misc->bar_q, 0, q_tile * BM, h_idx, b_idx);
       tma_load_4d(smem + OFF_Q2, &tm_q2, &misc->bar_q, 0, q_tile * BM, h_idx, b_idx);
@@ -139,58 +146,75 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     }
   } else if (warp == 9) {
     // -------------------------------- MMA issuer --------------------------------
-    // Sub-tile t covers key rows [64t, 64t+64).  S_b(t+1) is issued before waiting for P_b(t), so the
-    // softmax warpgroups always find their next scores ready.
-    if (lane == 0) {
+    // One thread, chosen by elect.sync, runs the whole loop.  (A thread picked by comparing the lane id
+    // issues tcgen05.mma about three times slower: 152 against 48 clocks per instruction, measured.)
+    // Each K/V tile of 128 rows is two sub-tiles of 64; S_b of the next sub-tile is issued before the
+    // wait for P_b of the current one, so the softmax warpgroups always find their next scores ready.
+    // The loop body is kept to a few integer instructions per MMA: this thread shares its scheduler with
+    // two busy softmax warps.
+    if (elect_one()) {
       constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0);   // S = Q K^T, both K-major
       constexpr uint32_t IDESC_O = make_idesc(BM, DV, 0, 1);    // O += P V, V is MN-major
-      const uint32_t q_addr[2] = {smem_u32(smem + OFF_Q1), smem_u32(smem + OFF_Q2)};
-      auto issue_s = [&](int br, int t) {
-        const int j = t >> 1, half = t & 1;
-        const uint32_t k_addr = smem_u32(smem + OFF_K + (j % KS) * 2 * K_BYTES + br * K_BYTES) + half * (SUB * 128);
+      constexpr uint32_t HALF = (SUB * 128) >> 4;               // 64 rows of 128 bytes, in descriptor units
+      const uint32_t q1_lo = sdesc_lo(smem_u32(smem + OFF_Q1)), q2_lo = sdesc_lo(smem_u32(smem + OFF_Q2));
+      const uint32_t k_lo0 = sdesc_lo(smem_u32(smem + OFF_K));
+      const uint32_t v_lo0 = sdesc_lo(smem_u32(smem + OFF_V), V_BYTES / 2);
+      const uint32_t t_s1 = tmem_base, t_s2 = tmem_base + 128, t_o1 = tmem_base + T_O, t_o2 = tmem_base + T_O + 128;
+      // S_b(buffer u) = Q_b K_b(tile at k_lo, half u)^T
+      auto issue_s = [&](uint32_t k_lo, int u) {
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          mma_ss(tmem_base + br * 128 + (t & 1) * SUB, sdesc_kmajor(q_addr[br] + k * 32), sdesc_kmajor(k_addr + k * 32),
-                 IDESC_S, k > 0);
-        mma_commit(&misc->s_full[br][t & 1]);
+          mma_ss_lo(t_s1 + u * SUB, q1_lo + k * 2, k_lo + u * HALF + k * 2, IDESC_S, k > 0);
+        mma_commit(&misc->s_full[0][u]);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          mma_ss_lo(t_s2 + u * SUB, q2_lo + k * 2, k_lo + (K_BYTES >> 4) + u * HALF + k * 2, IDESC_S, k > 0);
+        mma_commit(&misc->s_full[1][u]);
       };
-      auto issue_pv = [&](int br, int t) {
-        const int j = t >> 1, half = t & 1;
-        const uint32_t v_addr = smem_u32(smem + OFF_V + (j % VS) * V_BYTES) + half * (SUB * 128);
+      // O_b += P_b(buffer u) V(tile at v_lo, half u)
+      auto issue_pv = [&](int br, uint32_t v_lo, int u, uint32_t first) {
+        const uint32_t t_o = br ? t_o2 : t_o1, t_p = (br ? t_s2 : t_s1) + u * SUB;
 #pragma unroll
         for (int k = 0; k < SUB / 16; ++k)
-          mma_ts(tmem_base + T_O + br * 128, tmem_base + br * 128 + (t & 1) * SUB + k * 8,
-                 make_sdesc(v_addr + k * 2048, V_BYTES / 2, 1024), IDESC_O, (t > 0 || k > 0));
+          mma_ts_lo(t_o, t_p + k * 8, v_lo + u * HALF + k * (2048 >> 4), IDESC_O, k > 0 ? 1u : first);
         mma_commit(&misc->o_done[br]);
       };
       bool ok = mbar_wait(&misc->bar_q, 0, abort_flag, 201);
       ok = ok && mbar_wait(&misc->k_full[0], 0, abort_flag, 202);
       if (ok) {
         tc_fence_after();
-        issue_s(0, 0);
-        issue_s(1, 0);
-        for (int t = 0; t < nsub; ++t) {
-          const int j = t >> 1;
-          if (t + 1 < nsub) {
-            const int jn = (t + 1) >> 1;
-            if (((t + 1) & 1) == 0) {
-              if (!mbar_wait(&misc->k_full[jn % KS], (jn / KS) & 1, abort_flag, 205, t)) break;
-              tc_fence_after();
-            }
-            issue_s(0, t + 1);
-            issue_s(1, t + 1);
-            if ((t + 1) & 1) mma_commit(&misc->k_empty[jn % KS]);   // both halves of K tile jn consumed
-          }
-          if ((t & 1) == 0) {
-            if (!mbar_wait(&misc->v_full[j % VS], (j / VS) & 1, abort_flag, 203, t)) break;
-          }
-          if (!mbar_wait(&misc->p_full[0][t & 1], (t >> 1) & 1, abort_flag, 204, t)) break;
+        int ks = 0, vs = 0;
+        uint32_t k_par = 0, v_par = 0;
+        issue_s(k_lo0, 0);
+        for (int j = 0; j < nkv; ++j) {
+          const uint32_t k_lo = k_lo0 + ks * ((2 * K_BYTES) >> 4);
+          const uint32_t v_lo = v_lo0 + vs * (V_BYTES >> 4);
+          const uint32_t ph = j & 1;
+          // ---- sub-tile 2j (buffer 0): first issue the scores of sub-tile 2j+1 (same K tile, upper half)
+          issue_s(k_lo, 1);
+          mma_commit(&misc->k_empty[ks]);
+          if (!mbar_wait(&misc->v_full[vs], v_par, abort_flag, 203, j)) break;
+          if (!mbar_wait(&misc->p_full[0][0], ph, abort_flag, 204, j)) break;
           tc_fence_after();
-          issue_pv(0, t);
-          if (!mbar_wait(&misc->p_full[1][t & 1], (t >> 1) & 1, abort_flag, 206, t)) break;
+          issue_pv(0, v_lo, 0, j > 0);
+          if (!mbar_wait(&misc->p_full[1][0], ph, abort_flag, 206, j)) break;
           tc_fence_after();
-          issue_pv(1, t);
-          if (t & 1) mma_commit(&misc->v_empty[j % VS]);
+          issue_pv(1, v_lo, 0, j > 0);
+          // ---- sub-tile 2j+1 (buffer 1): first issue the scores of sub-tile 2j+2 (next K tile, lower half)
+          if (++ks == KS) { ks = 0; k_par ^= 1; }
+          if (j + 1 < nkv) {
+            if (!mbar_wait(&misc->k_full[ks], k_par, abort_flag, 205, j)) break;
+            tc_fence_after();
+            issue_s(k_lo0 + ks * ((2 * K_BYTES) >> 4), 0);
+          }
+          if (!mbar_wait(&misc->p_full[0][1], ph, abort_flag, 207, j)) break;
+          tc_fence_after();
+          issue_pv(0, v_lo, 1, 1);
+          if (!mbar_wait(&misc->p_full[1][1], ph, abort_flag, 208, j)) break;
+          tc_fence_after();
+          issue_pv(1, v_lo, 1, 1);
+          mma_commit(&misc->v_empty[vs]);
+          if (++vs == VS) { vs = 0; v_par ^= 1; }
         }
         mma_commit(&misc->o_full);
       }
@@ -205,15 +229,25 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     const float sl2 = args.sm_scale * 1.4426950408889634f;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
+#ifdef DA_TIMING
+    const bool tm_warp = (blockIdx.x == 3 && blockIdx.y == 1 && lane == 0 && (warp & 3) == 0);
+#endif
 
     for (int t = 0; t < nsub; ++t) {
       const uint32_t t_s = t_s0 + (t & 1) * SUB;
+#ifdef DA_TIMING
+      const bool tm_on = tm_warp && t >= 16 && t < 32;
+      const int tm_base = br * 256 + (t - 16) * 8;
+#endif
+      DA_TS(0);
       if (!mbar_wait(&misc->s_full[br][t & 1], (t >> 1) & 1, abort_flag, 301 + br, t)) { ok = false; break; }
       tc_fence_after();
+      DA_TS(1);
       uint32_t sr[SUB];
       tmem_ld32(t_s + 0, sr);
       tmem_ld32(t_s + 32, sr + 32);
       tc_wait_ld();
+      DA_TS(2);
       // row maximum as 8 independent chains of 3-input maxima
       float mx[8];
 #pragma unroll
@@ -251,6 +285,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
         }
       }
       const float neg = -m_run * sl2;
+      DA_TS(3);
       float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < SUB / 2; ++i) {
@@ -261,10 +296,13 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
         sr[i] = pack_half2(p0, p1);
       }
       l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+      DA_TS(4);
       tmem_st32(t_s, sr);
       tc_wait_st();
+      DA_TS(5);
       tc_fence_before();
       mbar_arrive(&misc->p_full[br][t & 1]);
+      DA_TS(6);
     }
 
     // ---- epilogue: every thread runs every barrier; only the global writes depend on `ok`

@@ -86,6 +86,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// Same wait executed by a whole converged warp; the result is made warp-uniform so that the warp
+// stays converged (elect.sync below needs all 32 lanes) even when a wait gives up.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int site,
+                                               int iter = 0) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, site, iter));
+}
+
 // named barrier among `nthreads` threads of the CTA (id 1..15; 0 is __syncthreads)
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
@@ -170,6 +177,30 @@ __device__ __forceinline__ uint64_t make_sdesc(uint32_t smem_addr, uint32_t lbo_
   return d;
 }
 __device__ __forceinline__ uint64_t sdesc_kmajor(uint32_t smem_addr) { return make_sdesc(smem_addr, 16, 1024); }
+
+// Lean forms for issuer loops.  Every descriptor used by this library has SBO = 1024, version 1 and
+// SWIZZLE_128B, so the upper 32 bits are one constant and only the lower word (start address and LBO)
+// changes: advancing an operand is a 32-bit add of (bytes >> 4).
+static constexpr uint32_t kSdescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t sdesc_lo(uint32_t smem_addr, uint32_t lbo_bytes = 16) {
+  return ((smem_addr & 0x3ffffu) >> 4) | ((lbo_bytes >> 4) << 16);
+}
+__device__ __forceinline__ void mma_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accum), "r"(kSdescHi)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n\t}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(accum), "r"(kSdescHi)
+      : "memory");
+}
 
 // ---- TMEM <-> registers, shape 32x32b: thread t of warp w touches lane 32*(w%4)+t, one column per register
 #define DA_R4(r, i) "=r"(r[i]), "=r"(r[i + 1]), "=r"(r[i + 2]), "=r"(r[i + 3])
