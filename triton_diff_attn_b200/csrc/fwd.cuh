@@ -190,16 +190,30 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
           const uint32_t k_lo = k_lo0 + ks * ((2 * K_BYTES) >> 4);
           const uint32_t v_lo = v_lo0 + vs * (V_BYTES >> 4);
           const uint32_t ph = j & 1;
+#ifdef DA_TIMING
+          const bool tm_on = (blockIdx.x == 3 && blockIdx.y == 1) && j >= 8 && j < 16;
+          const int tm_base = 512 + (j - 8) * 16;
+#endif
+          DA_TS(0);
           // ---- sub-tile 2j (buffer 0): first issue the scores of sub-tile 2j+1 (same K tile, upper half)
           issue_s(k_lo, 1);
+          DA_TS(1);
           mma_commit(&misc->k_empty[ks]);
           if (!mbar_wait(&misc->v_full[vs], v_par, abort_flag, 203, j)) break;
+#ifndef DA_NOPWAIT
           if (!mbar_wait(&misc->p_full[0][0], ph, abort_flag, 204, j)) break;
+#endif
           tc_fence_after();
+          DA_TS(2);
           issue_pv(0, v_lo, 0, j > 0);
+          DA_TS(3);
+#ifndef DA_NOPWAIT
           if (!mbar_wait(&misc->p_full[1][0], ph, abort_flag, 206, j)) break;
+#endif
           tc_fence_after();
+          DA_TS(4);
           issue_pv(1, v_lo, 0, j > 0);
+          DA_TS(5);
           // ---- sub-tile 2j+1 (buffer 1): first issue the scores of sub-tile 2j+2 (next K tile, lower half)
           if (++ks == KS) { ks = 0; k_par ^= 1; }
           if (j + 1 < nkv) {
@@ -207,12 +221,21 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
             tc_fence_after();
             issue_s(k_lo0 + ks * ((2 * K_BYTES) >> 4), 0);
           }
+          DA_TS(6);
+#ifndef DA_NOPWAIT
           if (!mbar_wait(&misc->p_full[0][1], ph, abort_flag, 207, j)) break;
+#endif
           tc_fence_after();
+          DA_TS(7);
           issue_pv(0, v_lo, 1, 1);
+          DA_TS(8);
+#ifndef DA_NOPWAIT
           if (!mbar_wait(&misc->p_full[1][1], ph, abort_flag, 208, j)) break;
+#endif
           tc_fence_after();
+          DA_TS(9);
           issue_pv(1, v_lo, 1, 1);
+          DA_TS(10);
           mma_commit(&misc->v_empty[vs]);
           if (++vs == VS) { vs = 0; v_par ^= 1; }
         }
@@ -229,6 +252,9 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     const float sl2 = args.sm_scale * 1.4426950408889634f;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
+#ifdef DA_DEPHASE
+    if (br == 1) { const long long c0 = clock64(); while (clock64() - c0 < DA_DEPHASE) { } }
+#endif
 #ifdef DA_TIMING
     const bool tm_warp = (blockIdx.x == 3 && blockIdx.y == 1 && lane == 0 && (warp & 3) == 0);
 #endif
@@ -243,35 +269,63 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
       if (!mbar_wait(&misc->s_full[br][t & 1], (t >> 1) & 1, abort_flag, 301 + br, t)) { ok = false; break; }
       tc_fence_after();
       DA_TS(1);
+#ifdef DA_NOSOFTMAX
+      tc_fence_before();
+      mbar_arrive(&misc->p_full[br][t & 1]);
+      continue;
+#endif
       uint32_t sr[SUB];
       tmem_ld32(t_s + 0, sr);
       tmem_ld32(t_s + 32, sr + 32);
       tc_wait_ld();
       DA_TS(2);
-      // row maximum as 8 independent chains of 3-input maxima
-      float mx[8];
+#ifdef DA_LDSTONLY
+      tmem_st32(t_s, sr + 32);
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&misc->p_full[br][t & 1]);
+      continue;
+#endif
+      // One pass: exponentials against the running maximum m_run of the earlier sub-tiles, the row
+      // maximum of this sub-tile alongside (independent chains, hidden under the exp unit's latency).
+      // If the new maximum exceeds m_run by more than 2^8 (rare; always at t = 0) the pass is redone
+      // with the updated maximum after rescaling O_b and l, so P never leaves fp16 range and the final
+      // normalisation stays exact.
+      float neg = -m_run * sl2;
+      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+      float mx[4];
+      uint32_t pk[SUB / 2];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) mx[i] = __uint_as_float(sr[i]);
+      for (int c = 0; c < 4; ++c) mx[c] = __uint_as_float(sr[c]);
+      if (t > 0) {
 #pragma unroll
-      for (int i = 8; i < SUB; i += 16) {
-#pragma unroll
-        for (int c = 0; c < 8; ++c)
-          mx[c] = max3(mx[c], __uint_as_float(sr[i + c]), __uint_as_float(sr[i + 8 + c < SUB ? i + 8 + c : i + c]));
-      }
-      const float mxa = max3(max3(mx[0], mx[1], mx[2]), max3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7]));
-      const float m_new = fmaxf(m_run, mxa);
-      if (t == 0) {
-        m_run = m_new;
+        for (int i = 0; i < SUB / 2; ++i) {
+#ifdef DA_NOEXP
+          const float p0 = fmaf(__uint_as_float(sr[2 * i]), sl2, neg);
+          const float p1 = fmaf(__uint_as_float(sr[2 * i + 1]), sl2, neg);
+#else
+          const float p0 = ex2(fmaf(__uint_as_float(sr[2 * i]), sl2, neg));
+          const float p1 = ex2(fmaf(__uint_as_float(sr[2 * i + 1]), sl2, neg));
+#endif
+          sum[(2 * i) & 3] += p0;
+          sum[(2 * i + 1) & 3] += p1;
+          pk[i] = pack_half2(p0, p1);
+          mx[i & 3] = max3(mx[i & 3], __uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]));
+        }
       } else {
-        // Rescale only when the running maximum moved by more than 2^8; otherwise keep the stale
-        // maximum (P stays below 256, exact in the final normalisation).
-        const bool need = (m_new - m_run) * sl2 > 8.f;
-        if (__any_sync(0xffffffffu, need)) {
-          // O_b must be quiescent: wait for P_b V of the previous sub-tile
+#pragma unroll
+        for (int i = 0; i < SUB / 2; ++i)
+          mx[i & 3] = max3(mx[i & 3], __uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]));
+      }
+      DA_TS(3);
+      const float m_new = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      const bool need = (t == 0) || ((m_new - m_run) * sl2 > 8.f);
+      if (__any_sync(0xffffffffu, need)) {
+        if (t > 0) {
+          // O_b must be quiescent: wait for P_b V of the previous sub-tile, then rescale it
           if (!mbar_wait(&misc->o_done[br], (t - 1) & 1, abort_flag, 305 + br, t)) { ok = false; break; }
           tc_fence_after();
           const float scale = need ? ex2((m_run - m_new) * sl2) : 1.f;
-          if (need) m_run = m_new;
           l_run *= scale;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
@@ -283,22 +337,27 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
             tmem_st32(t_o + c * 32, o);
           }
         }
-      }
-      const float neg = -m_run * sl2;
-      DA_TS(3);
-      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+        if (need) m_run = m_new;
+        neg = -m_run * sl2;
 #pragma unroll
-      for (int i = 0; i < SUB / 2; ++i) {
-        const float p0 = ex2(fmaf(__uint_as_float(sr[2 * i]), sl2, neg));
-        const float p1 = ex2(fmaf(__uint_as_float(sr[2 * i + 1]), sl2, neg));
-        sum[(2 * i) & 3] += p0;
-        sum[(2 * i + 1) & 3] += p1;
-        sr[i] = pack_half2(p0, p1);
+        for (int c = 0; c < 4; ++c) sum[c] = 0.f;
+#pragma unroll
+        for (int i = 0; i < SUB / 2; ++i) {
+          const float p0 = ex2(fmaf(__uint_as_float(sr[2 * i]), sl2, neg));
+          const float p1 = ex2(fmaf(__uint_as_float(sr[2 * i + 1]), sl2, neg));
+          sum[(2 * i) & 3] += p0;
+          sum[(2 * i + 1) & 3] += p1;
+          pk[i] = pack_half2(p0, p1);
+        }
       }
       l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
       DA_TS(4);
-      tmem_st32(t_s, sr);
+#ifndef DA_NOST
+      tmem_st32(t_s, pk);
       tc_wait_st();
+#else
+      if (l_run == 12345.f) { tmem_st32(t_s, pk); tc_wait_st(); }
+#endif
       DA_TS(5);
       tc_fence_before();
       mbar_arrive(&misc->p_full[br][t & 1]);
