@@ -125,8 +125,8 @@ __global__ void __launch_bounds__(256) diffattn_bwd_pre_kernel(const BwdArgs arg
 // ------------------------------------------------------------------------------------------------
 // 2. dK1, dK2, dV: one CTA = 128 key/value rows of one (batch, head); query tiles of 64 stream by.
 // TMEM: dV [0,128) dK1 [128,192) dK2 [192,256) | scores S1^T [256,320) S2^T [320,384) dP^T [384,448) |
-// fp16 A-operands dS1^T [448,480) dS2^T [480,512).  Thread = key row; warpgroup g handles query columns
-// [32g, 32g+32).  The warpgroups pull their scores into registers and release the score columns at once,
+// fp16 A-operands dS1^T [448,480) dS2^T [480,512).  Thread = key row; four warpgroups, warpgroup g handles
+// query columns [16g, 16g+16) (more resident warps per scheduler hide the exp-unit and TMEM latencies).  The warpgroups pull their scores into registers and release the score columns at once,
 // so the MMAs of tile i+1 run under the elementwise work of tile i.  dS_b^T goes back to TMEM (A-operand of
 // dK_b += dS_b^T Q_b); (P1 - lam P2)^T goes to a double-buffered K-major shared-memory tile (A-operand of
 // dV += Pc^T dA) because TMEM has no columns left for it.
@@ -146,7 +146,9 @@ constexpr int OFF_STAGE = OFF_PC + 2 * PC_BYTES;                   // 96 KB
 constexpr int OFF_MISC = OFF_STAGE + ST * STAGE_BYTES;             // 195 KB
 constexpr int MISC_BYTES = 1024;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
-constexpr int NUM_THREADS = 320;
+constexpr int NWG = 4;                      // elementwise warpgroups; warpgroup g owns query columns [16g, 16g+16)
+constexpr int NUM_THREADS = NWG * 128 + 64;
+constexpr int WARP_TMA = NWG * 4, WARP_MMA = NWG * 4 + 1;
 constexpr int T_DV = 0, T_DK1 = 128, T_DK2 = 192, T_S1 = 256, T_S2 = 320, T_DP = 384, T_DS1 = 448, T_DS2 = 480;
 struct Misc {
   uint64_t bar_kv;
@@ -176,24 +178,24 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
   const int b_idx = bh / args.h, h_idx = bh % args.h;
   const int nq = args.n / BQ;
 
-  if (warp == 8 && lane == 0) {
+  if (warp == WARP_TMA && lane == 0) {
     mbar_init(&misc->bar_kv, 1);
     for (int i = 0; i < ST; ++i) { mbar_init(&misc->full[i], 1); mbar_init(&misc->empty[i], 1); }
     mbar_init(&misc->s_full, 1);
-    mbar_init(&misc->s_free, 256);
-    mbar_init(&misc->e_done, 256);
+    mbar_init(&misc->s_free, NWG * 128);
+    mbar_init(&misc->e_done, NWG * 128);
     mbar_init(&misc->mma_done, 1);
     mbar_init(&misc->acc_full, 1);
     misc->abort_flag = 0;
     mbar_init_fence();
   }
-  if (warp == 9) tmem_alloc(&misc->tmem_slot, 512);
+  if (warp == WARP_MMA) tmem_alloc(&misc->tmem_slot, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&misc->tmem_slot);
 
-  if (warp == 8) {
+  if (warp == WARP_TMA) {
     if (elect_one()) {
       mbar_expect_tx(&misc->bar_kv, 2 * K_BYTES + V_BYTES);
       tma_load_4d(smem + OFF_K1, &tm_k1, &misc->bar_kv, 0, kv_tile * BKV, h_idx, b_idx);
@@ -213,7 +215,7 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
                      &misc->full[st]);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == WARP_MMA) {
     // One elected thread issues every MMA; descriptors advance by 32-bit adds (see sm100.cuh).
     if (elect_one()) {
       constexpr uint32_t IDESC_S = make_idesc(BKV, BQ, 0, 0);     // S^T = K Q^T, dP^T = V dA^T
@@ -251,14 +253,23 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
           int st_n = st + 1;
           uint32_t par_n = st_par;
           if (st_n == ST) { st_n = 0; par_n ^= 1; }
+#ifdef DA_TIMING
+          const bool tm_on = (blockIdx.x == 3 && blockIdx.y == 1) && i >= 16 && i < 32;
+          const int tm_base = 1024 + 512 + (i - 16) * 8;
+#endif
+          DA_TS(0);
           if (i + 1 < nq) {
             if (!mbar_wait(&misc->full[st_n], par_n, abort_flag, 503, i)) break;
+            DA_TS(1);
             if (!mbar_wait(&misc->s_free, ph, abort_flag, 504, i)) break;    // scores(i) are in registers
             tc_fence_after();
+            DA_TS(2);
             issue_scores(st_lo0 + st_n * (STAGE_BYTES >> 4));
+            DA_TS(3);
           }
           if (!mbar_wait(&misc->e_done, ph, abort_flag, 505, i)) break;
           tc_fence_after();
+          DA_TS(4);
           const uint32_t first = i > 0;
 #pragma unroll
           for (int k = 0; k < BQ / 16; ++k)
@@ -272,6 +283,7 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
             mma_ts_lo(tb + T_DK2, tb + T_DS2 + k * 8, sp_lo + (Q_BYTES >> 4) + k * (2048 >> 4), IDESC_DK, k > 0 ? 1u : first);
           mma_commit(&misc->mma_done);
           mma_commit(&misc->empty[st]);
+          DA_TS(5);
           st = st_n;
           st_par = par_n;
         }
@@ -279,7 +291,7 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
       }
     }
   } else {
-    const int g = warp >> 2;
+    const int g = warp >> 2;                       // warpgroup: query columns [16g, 16g+16) of every tile
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
     const uint32_t tb = tmem_base + lane_base;
@@ -288,19 +300,26 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
     bool ok = true;
     for (int i = 0; i < nq; ++i) {
       const int st = i % ST;
-      const float4* stats = reinterpret_cast<const float4*>(smem + OFF_STAGE + st * STAGE_BYTES + 2 * Q_BYTES + DA_BYTES) + g * 32;
+      const float4* stats = reinterpret_cast<const float4*>(smem + OFF_STAGE + st * STAGE_BYTES + 2 * Q_BYTES + DA_BYTES) + g * 16;
+#ifdef DA_TIMING
+      const bool tm_on = (blockIdx.x == 3 && blockIdx.y == 1 && lane == 0 && (warp & 3) == 0 && g < 2) && i >= 16 && i < 32;
+      const int tm_base = 1024 + g * 256 + (i - 16) * 8;
+#endif
+      DA_TS(0);
       if (!mbar_wait(&misc->s_full, i & 1, abort_flag, 601 + g, i)) { ok = false; break; }
       tc_fence_after();
-      uint32_t s1[32], s2[32], dp[32];
-      tmem_ld32(tb + T_S1 + g * 32, s1);
-      tmem_ld32(tb + T_S2 + g * 32, s2);
-      tmem_ld32(tb + T_DP + g * 32, dp);
+      DA_TS(1);
+      uint32_t s1[16], s2[16], dp[16];
+      tmem_ld16(tb + T_S1 + g * 16, s1);
+      tmem_ld16(tb + T_S2 + g * 16, s2);
+      tmem_ld16(tb + T_DP + g * 16, dp);
       tc_wait_ld();
       tc_fence_before();
       mbar_arrive(&misc->s_free);
-      uint32_t pc[16], d1[16], d2[16];
+      DA_TS(2);
+      uint32_t pc[8], d1[8], d2[8];
 #pragma unroll
-      for (int jj = 0; jj < 16; ++jj) {
+      for (int jj = 0; jj < 8; ++jj) {
         float pcv[2], d1v[2], d2v[2];
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
@@ -317,19 +336,24 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
         d1[jj] = pack_half2(d1v[0], d1v[1]);
         d2[jj] = pack_half2(d2v[0], d2v[1]);
       }
+      DA_TS(3);
       // operand buffers of tile i-1 (dS^T columns, and Pc buffer of tile i-2) must have been consumed
       if (i > 0) {
         if (!mbar_wait(&misc->mma_done, (i - 1) & 1, abort_flag, 605 + g, i)) { ok = false; break; }
         tc_fence_after();
       }
-      tmem_st16(tb + T_DS1 + g * 16, d1);
-      tmem_st16(tb + T_DS2 + g * 16, d2);
+      DA_TS(4);
+      // 8 packed columns per warpgroup: the 32x32b.x8 shape
+      asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                   ::"r"(tb + T_DS1 + g * 8), "r"(d1[0]), "r"(d1[1]), "r"(d1[2]), "r"(d1[3]), "r"(d1[4]), "r"(d1[5]), "r"(d1[6]), "r"(d1[7]) : "memory");
+      asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                   ::"r"(tb + T_DS2 + g * 8), "r"(d2[0]), "r"(d2[1]), "r"(d2[2]), "r"(d2[3]), "r"(d2[4]), "r"(d2[5]), "r"(d2[6]), "r"(d2[7]) : "memory");
       // Pc tile [128 key rows][64 query columns] fp16, 128-byte rows, 16-byte chunks XOR-swizzled by row
       {
         uint8_t* prow = smem + OFF_PC + (i & 1) * PC_BYTES + row * 128;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const int chunk = (g * 4 + c) ^ (row & 7);
+        for (int c = 0; c < 2; ++c) {
+          const int chunk = (g * 2 + c) ^ (row & 7);
           *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(pc[4 * c], pc[4 * c + 1], pc[4 * c + 2], pc[4 * c + 3]);
         }
       }
@@ -337,33 +361,20 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&misc->e_done);
+      DA_TS(5);
     }
     ok = ok && mbar_wait(&misc->acc_full, 0, abort_flag, 611 + g);
     tc_fence_after();
-    // warpgroup g: dV columns [64g, 64g+64) and dK_{g+1}
+    // warpgroup g reads accumulator columns [64g, 64g+64): g = 0,1 -> the two halves of dV, g = 2 -> dK1, g = 3 -> dK2
     uint32_t acc[64];
     const size_t grow = size_t(bh) * args.n + size_t(kv_tile) * BKV + row;
-    tmem_ld32(tb + T_DV + g * 64, acc);
-    tmem_ld32(tb + T_DV + g * 64 + 32, acc + 32);
+    tmem_ld32(tb + g * 64, acc);
+    tmem_ld32(tb + g * 64 + 32, acc + 32);
     tc_wait_ld();
     if (ok && !*abort_flag) {
-      uint4* p = reinterpret_cast<uint4*>(args.dv + grow * DV + g * 64);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        uint4 v;
-        v.x = pack_half2(__uint_as_float(acc[8 * i + 0]), __uint_as_float(acc[8 * i + 1]));
-        v.y = pack_half2(__uint_as_float(acc[8 * i + 2]), __uint_as_float(acc[8 * i + 3]));
-        v.z = pack_half2(__uint_as_float(acc[8 * i + 4]), __uint_as_float(acc[8 * i + 5]));
-        v.w = pack_half2(__uint_as_float(acc[8 * i + 6]), __uint_as_float(acc[8 * i + 7]));
-        p[i] = v;
-      }
-    }
-    tmem_ld32(tb + (g ? T_DK2 : T_DK1), acc);
-    tmem_ld32(tb + (g ? T_DK2 : T_DK1) + 32, acc + 32);
-    tc_wait_ld();
-    if (ok && !*abort_flag) {
-      const float s = args.sm_scale;
-      uint4* p = reinterpret_cast<uint4*>((g ? args.dk2 : args.dk1) + grow * HD);
+      const float s = g < 2 ? 1.f : args.sm_scale;
+      __half* base = g < 2 ? args.dv + grow * DV + g * 64 : (g == 2 ? args.dk1 : args.dk2) + grow * HD;
+      uint4* p = reinterpret_cast<uint4*>(base);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         uint4 v;
@@ -377,7 +388,7 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == WARP_MMA) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
@@ -386,8 +397,9 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
 // ------------------------------------------------------------------------------------------------
 // 3. dQ1, dQ2: one CTA = 128 query rows; key/value tiles of 128 rows stream by and are consumed in
 // sub-tiles of 64 rows.  TMEM: S1 two 64-column buffers [0,128), S2 [128,256), dP [256,384),
-// dQ1 [384,448), dQ2 [448,512).  Thread = query row; warpgroup b forms dS_b = +-P_b (dP - E_b) and writes
-// it as fp16 over its S buffer (TMEM A-operand of dS_b K_b).  The MMAs of sub-tile t+1 are issued before
+// dQ1 [384,448), dQ2 [448,512).  Thread = query row; four warpgroups: two per branch, each forming
+// dS_b = +-P_b (dP - E_b) for 32 of the 64 columns of a sub-tile and writing it as fp16 over the first 16 of its
+// own columns (TMEM A-operand of dS_b K_b).  The MMAs of sub-tile t+1 are issued before
 // the issuer waits for dS(t), so the warpgroups always find their next scores ready.
 // ------------------------------------------------------------------------------------------------
 namespace dq64 {
@@ -402,7 +414,9 @@ constexpr int OFF_STAGE = OFF_DA + DA_BYTES;         // 64 KB
 constexpr int OFF_MISC = OFF_STAGE + ST * STAGE_BYTES;
 constexpr int MISC_BYTES = 1024;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
-constexpr int NUM_THREADS = 320;
+constexpr int NWG = 4;                      // warpgroup w: branch w>>1, columns [32(w&1), 32(w&1)+32) of each sub-tile
+constexpr int NUM_THREADS = NWG * 128 + 64;
+constexpr int WARP_TMA = NWG * 4, WARP_MMA = NWG * 4 + 1;
 constexpr int T_S1 = 0, T_S2 = 128, T_DP = 256, T_DQ1 = 384, T_DQ2 = 448;
 struct Misc {
   uint64_t bar_q;
@@ -429,22 +443,22 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
   const int nkv = args.n / BN;
   const int nsub = 2 * nkv;
 
-  if (warp == 8 && lane == 0) {
+  if (warp == WARP_TMA && lane == 0) {
     mbar_init(&misc->bar_q, 1);
     for (int i = 0; i < ST; ++i) { mbar_init(&misc->full[i], 1); mbar_init(&misc->empty[i], 1); }
     for (int b = 0; b < 2; ++b)
-      for (int u = 0; u < 2; ++u) { mbar_init(&misc->s_full[b][u], 1); mbar_init(&misc->ds_full[b][u], 128); }
+      for (int u = 0; u < 2; ++u) { mbar_init(&misc->s_full[b][u], 1); mbar_init(&misc->ds_full[b][u], 256); }
     mbar_init(&misc->acc_full, 1);
     misc->abort_flag = 0;
     mbar_init_fence();
   }
-  if (warp == 9) tmem_alloc(&misc->tmem_slot, 512);
+  if (warp == WARP_MMA) tmem_alloc(&misc->tmem_slot, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&misc->tmem_slot);
 
-  if (warp == 8) {
+  if (warp == WARP_TMA) {
     if (elect_one()) {
       mbar_expect_tx(&misc->bar_q, 2 * Q_BYTES + DA_BYTES);
       tma_load_4d(smem + OFF_Q1, &tm_q1, &misc->bar_q, 0, q_tile * BM, h_idx, b_idx);
@@ -462,7 +476,7 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
         tma_load_4d(sp + 2 * K_BYTES + V_BYTES / 2, &tm_v, &misc->full[st], 64, j * BN, h_idx, b_idx);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == WARP_MMA) {
     // One elected thread issues every MMA; descriptors advance by 32-bit adds (see sm100.cuh).
     if (elect_one()) {
       constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0);    // S = Q K^T, dP = dA V^T
@@ -490,7 +504,7 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
       auto issue_dq = [&](int br, uint32_t sp_lo, int u, uint32_t first) {
 #pragma unroll
         for (int k = 0; k < SUB / 16; ++k)
-          mma_ts_lo(tb + (br ? T_DQ2 : T_DQ1), tb + (br ? T_S2 : T_S1) + u * SUB + k * 8,
+          mma_ts_lo(tb + (br ? T_DQ2 : T_DQ1), tb + (br ? T_S2 : T_S1) + u * SUB + (k / 2) * 32 + (k % 2) * 8,
                     sp_lo + br * (K_BYTES >> 4) + u * HALF + k * (2048 >> 4), IDESC_DQ, k > 0 ? 1u : first);
       };
       bool ok = mbar_wait(&misc->bar_q, 0, abort_flag, 801);
@@ -506,14 +520,24 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
           int st_n = st + 1;
           uint32_t par_n = st_par;
           if (st_n == ST) { st_n = 0; par_n ^= 1; }
+#ifdef DA_TIMING
+          const bool tm_on = (blockIdx.x == 3 && blockIdx.y == 1) && j >= 8 && j < 16;
+          const int tm_base = 2048 + 512 + (j - 8) * 16;
+#endif
+          DA_TS(0);
           // ---- sub-tile 2j (buffer 0): scores of 2j+1 first
           issue_scores(sp_lo, 1);
+          DA_TS(1);
           if (!mbar_wait(&misc->ds_full[0][0], ph, abort_flag, 804, j)) break;
           tc_fence_after();
+          DA_TS(2);
           issue_dq(0, sp_lo, 0, j > 0);
+          DA_TS(3);
           if (!mbar_wait(&misc->ds_full[1][0], ph, abort_flag, 805, j)) break;
           tc_fence_after();
+          DA_TS(4);
           issue_dq(1, sp_lo, 0, j > 0);
+          DA_TS(5);
           // ---- sub-tile 2j+1 (buffer 1): scores of 2j+2 (next tile) first
           if (j + 1 < nkv) {
             if (!mbar_wait(&misc->full[st_n], par_n, abort_flag, 803, j)) break;
@@ -534,7 +558,8 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
       }
     }
   } else {
-    const int br = warp >> 2;
+    const int br = warp >> 3;                      // branch
+    const int half = (warp >> 2) & 1;              // which 32 of the 64 columns of a sub-tile
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
     const uint32_t tb = tmem_base + lane_base;
@@ -548,50 +573,57 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
     bool ok = true;
     for (int t = 0; t < nsub; ++t) {
       const int u = t & 1;
-      const uint32_t t_s = tb + (br ? T_S2 : T_S1) + u * SUB;
-      const uint32_t t_dp = tb + T_DP + u * SUB;
+      // own 32 columns; the fp16 result goes to the first 16 of them (the other warpgroup's columns are untouched)
+      const uint32_t t_s = tb + (br ? T_S2 : T_S1) + u * SUB + half * 32;
+      const uint32_t t_dp = tb + T_DP + u * SUB + half * 32;
+#ifdef DA_TIMING
+      const bool tm_on = (blockIdx.x == 3 && blockIdx.y == 1 && lane == 0) && t >= 18 && t < 20;
+      const int tm_base = 2048 + warp * 16 + (t - 18) * 8;
+#endif
+      DA_TS(0);
       if (!mbar_wait(&misc->s_full[br][u], (t >> 1) & 1, abort_flag, 901 + br, t)) { ok = false; break; }
       tc_fence_after();
-      uint32_t s[SUB], dp[SUB];
+      DA_TS(1);
+      uint32_t s[32], dp[32];
       tmem_ld32(t_s, s);
       tmem_ld32(t_dp, dp);
-      tmem_ld32(t_s + 32, s + 32);
-      tmem_ld32(t_dp + 32, dp + 32);
       tc_wait_ld();
+      DA_TS(2);
 #pragma unroll
-      for (int i = 0; i < SUB / 2; ++i) {
+      for (int i = 0; i < 16; ++i) {
         const float p0 = coef * ex2(fmaf(__uint_as_float(s[2 * i]), sl2, neg_l));
         const float p1 = coef * ex2(fmaf(__uint_as_float(s[2 * i + 1]), sl2, neg_l));
         s[i] = pack_half2(p0 * (__uint_as_float(dp[2 * i]) - e), p1 * (__uint_as_float(dp[2 * i + 1]) - e));
       }
-      tmem_st32(t_s, s);
+      DA_TS(3);
+      tmem_st16(t_s, s);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&misc->ds_full[br][u]);
+      DA_TS(4);
     }
     ok = ok && mbar_wait(&misc->acc_full, 0, abort_flag, 911 + br);
     tc_fence_after();
-    uint32_t acc[64];
-    tmem_ld32(tb + (br ? T_DQ2 : T_DQ1), acc);
-    tmem_ld32(tb + (br ? T_DQ2 : T_DQ1) + 32, acc + 32);
+    uint32_t acc[32];
+    tmem_ld32(tb + (br ? T_DQ2 : T_DQ1) + half * 32, acc);
     tc_wait_ld();
     if (ok && !*abort_flag) {
-      const float s = args.sm_scale;
-      uint4* p = reinterpret_cast<uint4*>((br ? args.dq2 : args.dq1) + grow * HD);
+      const float sc = args.sm_scale;
+      uint4* p = reinterpret_cast<uint4*>((br ? args.dq2 : args.dq1) + grow * HD + half * 32);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < 4; ++i) {
         uint4 v;
-        v.x = pack_half2(__uint_as_float(acc[8 * i + 0]) * s, __uint_as_float(acc[8 * i + 1]) * s);
-        v.y = pack_half2(__uint_as_float(acc[8 * i + 2]) * s, __uint_as_float(acc[8 * i + 3]) * s);
-        v.z = pack_half2(__uint_as_float(acc[8 * i + 4]) * s, __uint_as_float(acc[8 * i + 5]) * s);
-        v.w = pack_half2(__uint_as_float(acc[8 * i + 6]) * s, __uint_as_float(acc[8 * i + 7]) * s);
+        v.x = pack_half2(__uint_as_float(acc[8 * i + 0]) * sc, __uint_as_float(acc[8 * i + 1]) * sc);
+        v.y = pack_half2(__uint_as_float(acc[8 * i + 2]) * sc, __uint_as_float(acc[8 * i + 3]) * sc);
+        v.z = pack_half2(__uint_as_float(acc[8 * i + 4]) * sc, __uint_as_float(acc[8 * i + 5]) * sc);
+        v.w = pack_half2(__uint_as_float(acc[8 * i + 6]) * sc, __uint_as_float(acc[8 * i + 7]) * sc);
         p[i] = v;
       }
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == WARP_MMA) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
