@@ -32,21 +32,25 @@ import torch
 EPS = 1e-5  # src/kernel.py:50
 
 
-def _lam(lambda_scale, dtype) -> torch.Tensor:
+def _lam(lambda_scale, dtype, device="cpu") -> torch.Tensor:
     if not torch.is_tensor(lambda_scale):
         lambda_scale = torch.tensor([float(lambda_scale)])
-    return lambda_scale.detach().reshape(-1)[0].to(dtype=dtype, device="cpu")
+    return lambda_scale.detach().reshape(-1)[0].to(dtype=dtype, device=device)
 
 
 def forward(q1, q2, k1, k2, v, lambda_scale, lambda_init: float = 0.8, rms_norm: bool = False,
-            dtype=torch.float32, round_p_half: bool = False, eps: float = EPS) -> Dict[str, torch.Tensor]:
+            dtype=torch.float32, round_p_half: bool = False, eps: float = EPS, device="cpu") -> Dict[str, torch.Tensor]:
     """Forward pass; returns Y and the intermediates the backward kernels save (src/layers.py:60-80).
 
     Keys: y, a (pre-norm), a1, a2 (per-branch P_b V), lse1, lse2 (natural-log logsumexp of S_b,
     the quantity the reference kernel stores as M1/M2, src/kernel.py:188-189), rstd.
+
+    `device` selects where torch evaluates the same restatement (default CPU).  Tests of sequence lengths
+    whose N x N matrices are too slow on the host pass a CUDA device and get the identical fp32 arithmetic
+    there (TF32 off); the baseline timing always uses the CPU.
     """
-    q1, q2, k1, k2, v = (t.detach().to("cpu", dtype) for t in (q1, q2, k1, k2, v))
-    lam = _lam(lambda_scale, dtype)
+    q1, q2, k1, k2, v = (t.detach().to(device, dtype) for t in (q1, q2, k1, k2, v))
+    lam = _lam(lambda_scale, dtype, device)
     d = q1.shape[-1]
     s = 1.0 / math.sqrt(d)                                             # layers.py:60-62
     s1 = torch.matmul(q1, k1.transpose(2, 3)) * s                      # layers.py:64
@@ -72,7 +76,7 @@ def forward(q1, q2, k1, k2, v, lambda_scale, lambda_init: float = 0.8, rms_norm:
 
 def backward_closed_form(q1, q2, k1, k2, v, lambda_scale, dy, lambda_init: float = 0.8,
                          rms_norm: bool = False, dtype=torch.float32,
-                         eps: float = EPS) -> Dict[str, torch.Tensor]:
+                         eps: float = EPS, device="cpu") -> Dict[str, torch.Tensor]:
     """Closed-form gradients (no autograd).  Same quantities the reference's backward kernel forms
     (src/kernel.py:283-299 preprocess, :410-436 main loop), with the division-free d(lambda).
 
@@ -84,9 +88,9 @@ def backward_closed_form(q1, q2, k1, k2, v, lambda_scale, dy, lambda_init: float
         dQ_b = s dS_b K_b,  dK_b = s dS_b^T Q_b                       (kernel.py:423-424,435-436)
         dlam = - sum E_2
     """
-    f = forward(q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, dtype=dtype, eps=eps)
-    q1, q2, k1, k2, v, dy = (t.detach().to("cpu", dtype) for t in (q1, q2, k1, k2, v, dy))
-    lam = _lam(lambda_scale, dtype)
+    f = forward(q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, dtype=dtype, eps=eps, device=device)
+    q1, q2, k1, k2, v, dy = (t.detach().to(device, dtype) for t in (q1, q2, k1, k2, v, dy))
+    lam = _lam(lambda_scale, dtype, device)
     d = q1.shape[-1]
     dv_dim = v.shape[-1]
     s = 1.0 / math.sqrt(d)

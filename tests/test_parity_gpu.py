@@ -192,6 +192,56 @@ def test_full_size_properties_config2(op):
         assert torch.equal(alone[k], sl(full[k])), k
 
 
+def _full_size_case(op, b, h, n, d, scale, lam, lam_init, rms, seed, bi, hi):
+    """Run the operator at a BASELINE size; check one sampled (batch, head) against the fp32 restatement
+    evaluated by torch on the GPU (TF32 off; the N x N matrices are too slow on the host at these N),
+    head independence bit for bit, and d(lambda) of the sampled head alone."""
+    dev = torch.device("cuda", 0)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    g = torch.Generator(device=dev).manual_seed(seed)
+    def draw(*s_):
+        return (torch.randn(*s_, generator=g, device=dev, dtype=torch.float32) * scale).to(torch.float16)
+    q1, q2, k1, k2 = (draw(b, h, n, d) for _ in range(4))
+    v = draw(b, h, n, 2 * d)
+    dy = torch.randn(b, h, n, 2 * d, generator=g, device=dev, dtype=torch.float32).to(torch.float16)
+    leaves = [t.clone().requires_grad_(True) for t in (q1, q2, k1, k2, v)]
+    lam_t = torch.tensor([lam], device=dev, requires_grad=True)
+    y = op.MultiheadDiffAttnKernel(*leaves, lam_t, lam_init, rms)
+    y.backward(dy)
+    op.device_status(0)
+    sl = lambda t: t[bi:bi + 1, hi:hi + 1].contiguous()
+    full = {"y": sl(y.detach())}
+    for nm, t in zip(GRADS, leaves):
+        full[nm] = sl(t.grad)
+    del leaves, y
+    want = oracle.backward_closed_form(sl(q1), sl(q2), sl(k1), sl(k2), sl(v), torch.tensor([lam]), sl(dy), lam_init, rms,
+                                       device=dev)
+    for k in ("y",) + GRADS:
+        m = oracle.error_metrics(full[k], want[k])
+        bound = MAX_ABS * max(1.0, float(want[k].abs().max()))
+        assert m["max_abs"] <= bound and m["rel_l2"] <= REL_L2, (k, m)
+    alone = [t.clone().requires_grad_(True) for t in (sl(q1), sl(q2), sl(k1), sl(k2), sl(v))]
+    lam1 = torch.tensor([lam], device=dev, requires_grad=True)
+    y1 = op.MultiheadDiffAttnKernel(*alone, lam1, lam_init, rms)
+    y1.backward(sl(dy))
+    assert torch.equal(y1.detach(), full["y"])
+    for nm, t in zip(GRADS, alone):
+        assert torch.equal(t.grad, full[nm]), nm
+    dl = float(op.DiffAttnFunction.last_dlambda_fp32.cpu())
+    tol = 1e-2 * max(abs(float(want["dlambda"])), 1e-3 * float(want["e2"].abs().sum()))
+    assert abs(dl - float(want["dlambda"])) <= tol, (dl, float(want["dlambda"]))
+
+
+def test_full_size_config3_long_sequence(op):
+    """BASELINE config 3: B=1 H=32 N=16384 D=64, inputs scaled by 0.5, lambda 0.3, rms_norm on."""
+    _full_size_case(op, 1, 32, 16384, 64, 0.5, 0.3, 0.8, True, seed=333, bi=0, hi=17)
+
+
+def test_full_size_config5_one_gpu_share(op):
+    """BASELINE config 5 as one of 8 GPUs sees it: B=8 H=32 N=4096 D=64 (B*H = 256 of the 2048 heads)."""
+    _full_size_case(op, 8, 32, 4096, 64, 1.0, 0.5, 0.8, True, seed=555, bi=5, hi=9)
+
+
 def test_errors_raise_without_launch(op):
     dev = torch.device("cuda", 0)
     q = torch.zeros(1, 1, 100, 64, dtype=torch.float16, device=dev)
