@@ -65,6 +65,10 @@ CASES = [
     (1, 2, 256, 64, 1.0, -0.5, 0.2, True, 16),      # negative lambda
     (1, 1, 256, 64, 2.5, 0.7, 0.2, False, 17),      # peaky softmax: exercises the rescale path
     (1, 1, 1024, 64, 0.5, 0.3, 0.8, True, 18),
+    # head dim 32: the reference's own test and benchmark shapes (src/kernel.py:581-584, src/benchmark.py:19-25)
+    (2, 2, 256, 32, 0.5, 0.5, 0.8, True, 31),
+    (2, 16, 512, 32, 1.0, 0.5, 0.8, True, 32),      # BASELINE config 1 / README.md example shape
+    (1, 2, 384, 32, 1.0, -0.4, 0.2, False, 33),
 ]
 
 
@@ -153,6 +157,22 @@ def test_reference_golden_selfcheck_tolerance(op, golden_dir):
     for k in ("y",) + GRADS:
         assert torch.allclose(got[k][:, :, ::step, :].float(), torch.from_numpy(z[k]), atol=1e-2, rtol=0), k
     assert abs(got["dlambda_fp32"] - float(z["dlambda"][0])) <= 1e-2 * abs(float(z["dlambda"][0]))
+
+
+@pytest.mark.parametrize("name", ["selftest_b2h2n256d32", "c1_b2h16n512d32"])
+def test_reference_golden_d32(op, golden_dir, name):
+    """Head dim 32 against the vectors produced by the reference's own PyTorch path at the reference's
+    self-test shape (src/kernel.py:581-596: N(0, 0.5^2) inputs, uniform dY) and at BASELINE config 1, with the
+    reference's acceptance test allclose(atol=1e-2, rtol=0) (src/kernel.py:624-635, src/benchmark.py:293)."""
+    z = np.load(os.path.join(golden_dir, name + ".npz"))
+    b, h, n, d, seed = (int(x) for x in z["meta"])
+    scale, lam, lam_init, rms, dyu = (float(x) for x in z["fmeta"])
+    step = int(z["row_step"][0])
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(b, h, n, d, seed, scale, torch.float16, bool(dyu))
+    got = run_gpu(op, q1, q2, k1, k2, v, dy, lam, lam_init, bool(rms))
+    for k in ("y",) + GRADS:
+        assert torch.allclose(got[k][:, :, ::step, :].float(), torch.from_numpy(z[k]), atol=1e-2, rtol=0), k
+    assert abs(got["dlambda_fp32"] - float(z["dlambda"][0])) <= 1e-2 * max(abs(float(z["dlambda"][0])), 1.0)
 
 
 def test_full_size_properties_config2(op):
@@ -249,7 +269,7 @@ def test_errors_raise_without_launch(op):
     lam = torch.tensor([0.5], device=dev)
     with pytest.raises(ValueError, match="multiple of 128"):
         op.MultiheadDiffAttnKernel(q, q, q, q, v, lam)
-    q = torch.zeros(1, 1, 128, 48, dtype=torch.float16, device=dev)
+    q = torch.zeros(1, 1, 128, 48, dtype=torch.float16, device=dev)     # 48 and 128 are not compiled in
     v = torch.zeros(1, 1, 128, 96, dtype=torch.float16, device=dev)
     with pytest.raises(ValueError, match="UNSUPPORTED_D"):
         op.MultiheadDiffAttnKernel(q, q, q, q, v, lam)

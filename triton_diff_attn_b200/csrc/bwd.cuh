@@ -33,6 +33,7 @@ struct BwdArgs {
   int rms_norm;
   int n;
   int h;
+  int d;                // real head dim (64, or 32 with zero-filled padding in the 64-wide tiles)
   long long rows;       // B*H*N
 };
 
@@ -371,12 +372,16 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
     tmem_ld32(tb + g * 64, acc);
     tmem_ld32(tb + g * 64 + 32, acc + 32);
     tc_wait_ld();
-    if (ok && !*abort_flag) {
+    const int d_real = args.d, dv_real = 2 * args.d;
+    // real columns among this warpgroup's 64: dV half g holds columns [64g, 64g+64) of dv_real; dK holds d_real
+    const int ncols = g < 2 ? (dv_real - g * 64 < 64 ? dv_real - g * 64 : 64) : d_real;
+    if (ok && !*abort_flag && ncols > 0) {
       const float s = g < 2 ? 1.f : args.sm_scale;
-      __half* base = g < 2 ? args.dv + grow * DV + g * 64 : (g == 2 ? args.dk1 : args.dk2) + grow * HD;
+      __half* base = g < 2 ? args.dv + grow * dv_real + g * 64 : (g == 2 ? args.dk1 : args.dk2) + grow * d_real;
       uint4* p = reinterpret_cast<uint4*>(base);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
+        if (8 * i >= ncols) break;
         uint4 v;
         v.x = pack_half2(__uint_as_float(acc[8 * i + 0]) * s, __uint_as_float(acc[8 * i + 1]) * s);
         v.y = pack_half2(__uint_as_float(acc[8 * i + 2]) * s, __uint_as_float(acc[8 * i + 3]) * s);
@@ -607,9 +612,9 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
     uint32_t acc[32];
     tmem_ld32(tb + (br ? T_DQ2 : T_DQ1) + half * 32, acc);
     tc_wait_ld();
-    if (ok && !*abort_flag) {
+    if (ok && !*abort_flag && half * 32 < args.d) {
       const float sc = args.sm_scale;
-      uint4* p = reinterpret_cast<uint4*>((br ? args.dq2 : args.dq1) + grow * HD + half * 32);
+      uint4* p = reinterpret_cast<uint4*>((br ? args.dq2 : args.dq1) + grow * args.d + half * 32);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         uint4 v;

@@ -57,9 +57,12 @@ int make_map(CUtensorMap* map, const void* base, int cols, int rows, int d2, int
   // a size-1 dimension's stride is never used, but the encoder still wants a legal value
   if (d2 == 1) strides[1] = strides[0] * cuuint64_t(rows);
   if (d3 == 1) strides[2] = strides[1] * cuuint64_t(d2);
-  cuuint32_t box[4] = {cuuint32_t(cols < 64 ? cols : 64), cuuint32_t(box_rows), 1, 1};
+  // The box is always 64 columns (128 bytes, one swizzle row).  A tensor narrower than that (head dim 32)
+  // is padded by the TMA engine: out-of-range elements arrive as zeros.
+  cuuint32_t box[4] = {64, cuuint32_t(box_rows), 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
-  const CUtensorMapSwizzle sw = cols >= 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B;
+  (void)cols;
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -76,7 +79,7 @@ int check_common(const DiffAttnParams* p, bool bwd) {
   if (p->B < 0 || p->H < 0 || p->N < 0 || p->D <= 0)
     return fail(DIFFATTN_ERR_BAD_SHAPE, "negative size: B=%d H=%d N=%d D=%d", p->B, p->H, p->N, p->D);
   if (!diffattn_supports(p->D, bwd ? 1 : 0))
-    return fail(DIFFATTN_ERR_UNSUPPORTED_D, "head dim %d is not compiled in (supported: 64)", p->D);
+    return fail(DIFFATTN_ERR_UNSUPPORTED_D, "head dim %d is not compiled in (supported: 32, 64)", p->D);
   if (p->N % 128 != 0)
     return fail(DIFFATTN_ERR_BAD_SHAPE, "N=%d must be a multiple of 128 (no masking, as the reference)", p->N);
   if (p->lambda_dtype != DIFFATTN_LAMBDA_F16 && p->lambda_dtype != DIFFATTN_LAMBDA_F32)
@@ -129,7 +132,7 @@ const char* diffattn_last_error(void) { return g_err; }
 int diffattn_version(void) { return DIFFATTN_VERSION; }
 int diffattn_supports(int32_t d, int32_t dir) {
   (void)dir;
-  return d == 64 ? 1 : 0;
+  return (d == 64 || d == 32) ? 1 : 0;
 }
 
 uint64_t diffattn_workspace_bytes(const DiffAttnParams* p) {
@@ -157,7 +160,7 @@ int diffattn_fwd(const DiffAttnParams* p) {
   a.lse1 = p->lse1; a.lse2 = p->lse2; a.rstd = p->rstd;
   a.lambda_ptr = p->lambda_scale; a.lambda_dtype = p->lambda_dtype;
   a.sm_scale = p->sm_scale; a.out_scale = 1.f - p->lambda_init; a.eps = p->eps;
-  a.rms_norm = p->rms_norm; a.n = p->N; a.h = p->H;
+  a.rms_norm = p->rms_norm; a.n = p->N; a.h = p->H; a.d = p->D;
   if ((rc = set_smem(da::diffattn_fwd64_kernel, da::fwd64::SMEM_BYTES))) return rc;
   dim3 grid(p->N / da::fwd64::BM, p->B * p->H);
   da::diffattn_fwd64_kernel<<<grid, da::fwd64::NUM_THREADS, da::fwd64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, a);
@@ -189,7 +192,7 @@ int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages) {
   a.dlambda = p->dlambda;
   a.lambda_ptr = p->lambda_scale; a.lambda_dtype = p->lambda_dtype;
   a.sm_scale = p->sm_scale; a.out_scale = 1.f - p->lambda_init; a.rms_norm = p->rms_norm;
-  a.n = p->N; a.h = p->H; a.rows = (long long)rows;
+  a.n = p->N; a.h = p->H; a.d = p->D; a.rows = (long long)rows;
 
   // 1. preprocess (grid-stride; one atomic per CTA for d(lambda))
   if (stages & DIFFATTN_STAGE_PRE) {
@@ -197,7 +200,8 @@ int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages) {
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p->device);
     long long blocks = (long long)((rows + 7) / 8);
     if (blocks > (long long)sms * 8) blocks = (long long)sms * 8;
-    da::diffattn_bwd_pre_kernel<4><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    if (D == 64) da::diffattn_bwd_pre_kernel<4><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    else da::diffattn_bwd_pre_kernel<2><<<(unsigned)blocks, 256, 0, stream>>>(a);
     DA_CUDA(cudaGetLastError());
   }
   CUtensorMap mq1, mq2, mk1, mk2, mv, mda;

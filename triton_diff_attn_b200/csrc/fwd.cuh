@@ -31,6 +31,7 @@ struct FwdArgs {
   int rms_norm;
   int n;              // sequence length
   int h;              // heads
+  int d;              // real head dim: 64, or 32 (then the 64-wide tiles are zero-filled by TMA beyond column 32 / 64)
 };
 
 __device__ __forceinline__ float load_lambda(const void* p, int dtype) {
@@ -393,12 +394,13 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     }
     misc->ssq[br][row] = ssq;
     named_bar_sync(1, 256);
-    const float rstd = rsqrtf((misc->ssq[0][row] + misc->ssq[1][row]) * (1.f / DV) + args.eps);
+    const int dv_real = 2 * args.d;                      // 128, or 64 when the head dim is 32 (upper columns are padding)
+    const float rstd = rsqrtf((misc->ssq[0][row] + misc->ssq[1][row]) / float(dv_real) + args.eps);
     const float yscale = args.rms_norm ? args.out_scale * rstd : 1.f;
-    if (ok && !*abort_flag) {
-      const size_t grow = size_t(bh) * args.n + size_t(q_tile) * BM + row;
-      uint4* yp = reinterpret_cast<uint4*>(args.y + grow * DV + br * 64);
-      uint4* ap = reinterpret_cast<uint4*>(args.a2 + grow * DV + br * 64);
+    const size_t grow = size_t(bh) * args.n + size_t(q_tile) * BM + row;
+    if (ok && !*abort_flag && br * 64 < dv_real) {
+      uint4* yp = reinterpret_cast<uint4*>(args.y + grow * dv_real + br * 64);
+      uint4* ap = reinterpret_cast<uint4*>(args.a2 + grow * dv_real + br * 64);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         uint4 yv, av;
@@ -413,6 +415,8 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
         yp[i] = yv;
         ap[i] = av;
       }
+    }
+    if (ok && !*abort_flag) {
       const float lse = m_run * args.sm_scale + logf(l_run);
       if (br == 0) {
         args.lse1[grow] = lse;
