@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the differential-attention hot path (forward + backward) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3|c5shard]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3|c4|c5shard|ref_d32]
 
 A step is one forward + backward over one batch of synthetic fp16 input.  At N=1 the workload is
 BASELINE config 2 (B=4, H=16, N=4096, D=64).  With N>1 every rank runs the same shape on its own
@@ -33,7 +33,9 @@ WORKLOADS = {
     # name: (B, H, N, D, input scale, lambda, lambda_init, rms_norm)
     "c2": (4, 16, 4096, 64, 1.0, 0.5, 0.8, True),        # BASELINE config 2 (headline)
     "c3": (1, 32, 16384, 64, 0.5, 0.3, 0.8, True),       # BASELINE config 3
+    "c4": (8, 8, 8192, 128, 1.0, 0.7, 0.2, False),       # BASELINE config 4 (wide head, RMSNorm off)
     "c5shard": (8, 32, 4096, 64, 1.0, 0.5, 0.8, True),   # BASELINE config 5 split over 8 GPUs
+    "ref_d32": (4, 16, 4096, 32, 0.5, 0.5, 0.8, True),   # the reference's benchmark point H=16 D=32 N=4096 (src/benchmark.py:19-25)
 }
 METRIC = "diff-attn fwd+bwd TFLOP/s (credited 28*B*H*N^2*D), fp16"
 NOMINAL_TFLOPS = 2250.0
@@ -177,6 +179,7 @@ def main():
     import torch.distributed as dist
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ["NCCL_DEBUG"] = "WARN"      # keep NCCL's version banner off stdout: rank 0 prints ONE JSON line
         dist.init_process_group("nccl", device_id=dev)
 
     from triton_diff_attn_b200 import _lib, layers, MultiheadDiffAttnKernel, sum_dlambda_on_host, device_status
@@ -292,11 +295,18 @@ def main():
         return
 
     peaks = measured_peaks()
+    # executed MMA flops per unit B*H*N^2*D: D<=64: fwd 12 (S 4 + two P V 8), dK/dV 16, dQ 12 (S and dP recomputed);
+    # D=128: fwd 16 (S in both value-column passes), dV + dK kernels 24, dQ kernel 16
+    unit = f_fwd / 8.0
+    ex = {"fwd": 16.0, "dkdv": 24.0, "dq": 16.0} if d == 128 else {"fwd": 12.0, "dkdv": 16.0, "dq": 12.0}
+    tag = "128" if d == 128 else "64"
+    dkdv_name = "diffattn_bwd_dv128_kernel + diffattn_bwd_side128_kernel<K side>" if d == 128 else "diffattn_bwd_dkdv64_kernel"
+    dq_name = "diffattn_bwd_side128_kernel<Q side>" if d == 128 else "diffattn_bwd_dq64_kernel"
     kernels = {
-        "diffattn_fwd64_kernel": {"ms": ms_fwd, "credited_flops": f_fwd, "executed_mma_flops": f_fwd * 12 / 8},
+        f"diffattn_fwd{tag}_kernel": {"ms": ms_fwd, "credited_flops": f_fwd, "executed_mma_flops": unit * ex["fwd"]},
         "diffattn_bwd_pre_kernel": {"ms": ms_pre, "credited_flops": 0.0, "executed_mma_flops": 0.0},
-        "diffattn_bwd_dkdv64_kernel": {"ms": ms_dkdv, "credited_flops": f_bwd * 16 / 20, "executed_mma_flops": f_bwd * 16 / 20},
-        "diffattn_bwd_dq64_kernel": {"ms": ms_dq, "credited_flops": f_bwd * 4 / 20, "executed_mma_flops": f_bwd * 12 / 20},
+        dkdv_name: {"ms": ms_dkdv, "credited_flops": f_bwd * 16 / 20, "executed_mma_flops": unit * ex["dkdv"]},
+        dq_name: {"ms": ms_dq, "credited_flops": f_bwd * 4 / 20, "executed_mma_flops": unit * ex["dq"]},
     }
     for kinfo in kernels.values():
         kinfo["credited_tflops"] = kinfo["credited_flops"] / (kinfo["ms"] * 1e-3) / 1e12
@@ -322,7 +332,7 @@ def main():
         "fwd": {"ms": ms_fwd, "tflops": f_fwd / (ms_fwd * 1e-3) / 1e12, "frac_nominal": f_fwd / (ms_fwd * 1e-3) / 1e12 / NOMINAL_TFLOPS},
         "bwd": {"ms": ms_bwd, "tflops": f_bwd / (ms_bwd * 1e-3) / 1e12, "frac_nominal": f_bwd / (ms_bwd * 1e-3) / 1e12 / NOMINAL_TFLOPS},
         "fwd_bwd_frac_nominal": value / world / NOMINAL_TFLOPS,
-        "kernels": kernels, "roofline": roofline, "clocks": clocks, "gpu_launches": 4 * args.steps,
+        "kernels": kernels, "roofline": roofline, "clocks": clocks, "gpu_launches": (6 if d == 128 else 4) * args.steps,
         "dlambda_host_sum": dl_total,
     }
     if e2e:

@@ -45,7 +45,8 @@ def test_exports_match_header(L):
 def test_supports(L):
     assert L.lib.diffattn_supports(64, 0) == 1 and L.lib.diffattn_supports(64, 1) == 1
     assert L.lib.diffattn_supports(32, 0) == 1 and L.lib.diffattn_supports(32, 1) == 1
-    assert L.lib.diffattn_supports(48, 0) == 0 and L.lib.diffattn_supports(128, 0) == 0
+    assert L.lib.diffattn_supports(128, 0) == 1 and L.lib.diffattn_supports(128, 1) == 1
+    assert L.lib.diffattn_supports(48, 0) == 0 and L.lib.diffattn_supports(256, 0) == 0
 
 
 def test_null_and_struct(L):

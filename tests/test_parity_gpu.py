@@ -69,6 +69,10 @@ CASES = [
     (2, 2, 256, 32, 0.5, 0.5, 0.8, True, 31),
     (2, 16, 512, 32, 1.0, 0.5, 0.8, True, 32),      # BASELINE config 1 / README.md example shape
     (1, 2, 384, 32, 1.0, -0.4, 0.2, False, 33),
+    # head dim 128 (value width 256): BASELINE config 4 family (rms_norm off, lambda 0.7, lambda_init 0.2) and rms on
+    (1, 1, 256, 128, 1.0, 0.7, 0.2, False, 41),
+    (2, 2, 512, 128, 1.0, 0.7, 0.2, False, 42),
+    (1, 2, 384, 128, 1.0, 0.5, 0.8, True, 43),
 ]
 
 
@@ -262,6 +266,11 @@ def test_full_size_config5_one_gpu_share(op):
     _full_size_case(op, 8, 32, 4096, 64, 1.0, 0.5, 0.8, True, seed=555, bi=5, hi=9)
 
 
+def test_full_size_config4_wide_head(op):
+    """BASELINE config 4: B=8 H=8 N=8192 D=128 (v width 256), rms_norm off, lambda 0.7, lambda_init 0.2."""
+    _full_size_case(op, 8, 8, 8192, 128, 1.0, 0.7, 0.2, False, seed=444, bi=3, hi=6)
+
+
 def test_errors_raise_without_launch(op):
     dev = torch.device("cuda", 0)
     q = torch.zeros(1, 1, 100, 64, dtype=torch.float16, device=dev)
@@ -269,7 +278,7 @@ def test_errors_raise_without_launch(op):
     lam = torch.tensor([0.5], device=dev)
     with pytest.raises(ValueError, match="multiple of 128"):
         op.MultiheadDiffAttnKernel(q, q, q, q, v, lam)
-    q = torch.zeros(1, 1, 128, 48, dtype=torch.float16, device=dev)     # 48 and 128 are not compiled in
+    q = torch.zeros(1, 1, 128, 48, dtype=torch.float16, device=dev)     # 48 is not compiled in
     v = torch.zeros(1, 1, 128, 96, dtype=torch.float16, device=dev)
     with pytest.raises(ValueError, match="UNSUPPORTED_D"):
         op.MultiheadDiffAttnKernel(q, q, q, q, v, lam)

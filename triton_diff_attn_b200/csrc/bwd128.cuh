@@ -1,0 +1,431 @@
+// Differential-attention backward for head dim D = 128 (value width 256), sm_100a.
+//
+// At this width the accumulators of the D = 64 design (dV, dK1, dK2 in one CTA) need all 512 TMEM
+// columns, so the work is cut differently (same math as src/kernel.py:410-436 of the reference):
+//   * diffattn_bwd_side128_kernel<QSIDE>  one branch b per CTA (blockIdx.z).  With X the stationary
+//       operand of the branch and Z the streamed one:  S = X Z^T,  T = Y W^T,  dS = +-P (T - E),
+//       OUT += dS Z.   QSIDE:  X = Q_b, Y = dA, Z = K_b, W = V   -> OUT = dQ_b  (thread = query row)
+//                      !QSIDE: X = K_b, Y = V,  Z = Q_b, W = dA  -> OUT = dK_b  (thread = key row; S, T transposed)
+//   * diffattn_bwd_dv128_kernel           dV += (P1 - lam P2)^T dA, key/value-stationary, both branches.
+// TMEM and shared-memory conventions are those of bwd.cuh; streamed tiles are 64 rows.
+#pragma once
+#include "bwd.cuh"
+#include "sm100.cuh"
+
+namespace da {
+
+namespace side128 {
+constexpr int BM = 128, SUB = 64, HD = 128, DV = 256, ST = 2, NWG = 4;
+constexpr int X_BYTES = BM * HD * 2;        // 32 KB: two boxes [128 x 64]
+constexpr int Y_BYTES = BM * DV * 2;        // 64 KB: four boxes [128 x 64]
+constexpr int Z_BYTES = SUB * HD * 2;       // 16 KB: two boxes [64 x 64]
+constexpr int W_BYTES = SUB * DV * 2;       // 32 KB: four boxes [64 x 64]
+constexpr int STAT_BYTES = SUB * 16;        // 1 KB
+constexpr int STAGE_BYTES = Z_BYTES + W_BYTES + STAT_BYTES;   // 49 KB
+constexpr int OFF_X = 0, OFF_Y = X_BYTES, OFF_STAGE = X_BYTES + Y_BYTES;   // 96 KB
+constexpr int OFF_MISC = OFF_STAGE + ST * STAGE_BYTES;                     // 194 KB
+constexpr int MISC_BYTES = 1024;
+constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
+constexpr int NUM_THREADS = NWG * 128 + 64;
+constexpr int WARP_TMA = NWG * 4, WARP_MMA = NWG * 4 + 1;
+constexpr int T_S = 0, T_T = 128, T_OUT = 256;
+struct Misc {
+  uint64_t bar_xy;
+  uint64_t full[ST], empty[ST];
+  uint64_t s_full[2], ds_full[2], acc_full;
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+}  // namespace side128
+
+// tm_x, tm_z: the branch's stationary / streamed [N, 128] operand (box rows 128 / 64);
+// tm_y, tm_w: the [N, 256] operands.  dA lives in the dense workspace and is addressed (col, row, b*h, 0).
+template <bool QSIDE>
+__global__ void __launch_bounds__(side128::NUM_THREADS, 1)
+diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__ CUtensorMap tm_x1,
+                            const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ CUtensorMap tm_z0,
+                            const __grid_constant__ CUtensorMap tm_z1, const __grid_constant__ CUtensorMap tm_w,
+                            const BwdArgs args) {
+  using namespace side128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Misc* misc = reinterpret_cast<Misc*>(smem + OFF_MISC);
+  volatile int* abort_flag = &misc->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x, bh = blockIdx.y, br = blockIdx.z;
+  const int b_idx = bh / args.h, h_idx = bh % args.h;
+  const int nsub = args.n / SUB;
+  const CUtensorMap* tm_x = br ? &tm_x1 : &tm_x0;
+  const CUtensorMap* tm_z = br ? &tm_z1 : &tm_z0;
+  // dA is the Y operand on the query side and the W operand on the key side
+  const int y_c2 = QSIDE ? bh : h_idx, y_c3 = QSIDE ? 0 : b_idx;
+  const int w_c2 = QSIDE ? h_idx : bh, w_c3 = QSIDE ? b_idx : 0;
+
+  if (warp == WARP_TMA && lane == 0) {
+    mbar_init(&misc->bar_xy, 1);
+    for (int i = 0; i < ST; ++i) { mbar_init(&misc->full[i], 1); mbar_init(&misc->empty[i], 1); }
+    for (int u = 0; u < 2; ++u) { mbar_init(&misc->s_full[u], 1); mbar_init(&misc->ds_full[u], NWG * 128); }
+    mbar_init(&misc->acc_full, 1);
+    misc->abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == WARP_MMA) tmem_alloc(&misc->tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&misc->tmem_slot);
+
+  if (warp == WARP_TMA) {
+    if (elect_one()) {
+      mbar_expect_tx(&misc->bar_xy, X_BYTES + Y_BYTES);
+      for (int c = 0; c < 2; ++c) tma_load_4d(smem + OFF_X + c * 16384, tm_x, &misc->bar_xy, c * 64, tile * BM, h_idx, b_idx);
+      for (int c = 0; c < 4; ++c) tma_load_4d(smem + OFF_Y + c * 16384, &tm_y, &misc->bar_xy, c * 64, tile * BM, y_c2, y_c3);
+      int st = 0;
+      uint32_t par = 1;
+      for (int t = 0; t < nsub; ++t) {
+        uint8_t* sp = smem + OFF_STAGE + st * STAGE_BYTES;
+        if (!mbar_wait(&misc->empty[st], par, abort_flag, 1101, t)) break;
+        mbar_expect_tx(&misc->full[st], QSIDE ? (Z_BYTES + W_BYTES) : STAGE_BYTES);
+        for (int c = 0; c < 2; ++c) tma_load_4d(sp + c * 8192, tm_z, &misc->full[st], c * 64, t * SUB, h_idx, b_idx);
+        for (int c = 0; c < 4; ++c) tma_load_4d(sp + Z_BYTES + c * 8192, &tm_w, &misc->full[st], c * 64, t * SUB, w_c2, w_c3);
+        if (!QSIDE)
+          bulk_load_1d(sp + Z_BYTES + W_BYTES, args.stats + (size_t(bh) * args.n + size_t(t) * SUB), STAT_BYTES, &misc->full[st]);
+        if (++st == ST) { st = 0; par ^= 1; }
+      }
+    }
+  } else if (warp == WARP_MMA) {
+    if (elect_one()) {
+      constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0);
+      constexpr uint32_t IDESC_OUT = make_idesc(BM, HD, 0, 1);     // OUT += dS Z, Z MN-major (two 64-column atoms)
+      const uint32_t x_lo = sdesc_lo(smem_u32(smem + OFF_X)), y_lo = sdesc_lo(smem_u32(smem + OFF_Y));
+      const uint32_t st_lo0 = sdesc_lo(smem_u32(smem + OFF_STAGE));
+      const uint32_t tb = tmem_base;
+      auto issue_scores = [&](uint32_t sp_lo, int u) {
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          mma_ss_lo(tb + T_S + u * SUB, x_lo + (k / 4) * (16384 >> 4) + (k % 4) * 2, sp_lo + (k / 4) * (8192 >> 4) + (k % 4) * 2,
+                    IDESC_S, k > 0);
+#pragma unroll
+        for (int k = 0; k < DV / 16; ++k)
+          mma_ss_lo(tb + T_T + u * SUB, y_lo + (k / 4) * (16384 >> 4) + (k % 4) * 2,
+                    sp_lo + (Z_BYTES >> 4) + (k / 4) * (8192 >> 4) + (k % 4) * 2, IDESC_S, k > 0);
+        mma_commit(&misc->s_full[u]);
+      };
+      bool ok = mbar_wait(&misc->bar_xy, 0, abort_flag, 1201);
+      ok = ok && mbar_wait(&misc->full[0], 0, abort_flag, 1202);
+      if (ok) {
+        tc_fence_after();
+        issue_scores(st_lo0, 0);
+        int st = 0;
+        uint32_t par = 0;
+        for (int t = 0; t < nsub; ++t) {
+          const int u = t & 1;
+          const uint32_t sp_lo = st_lo0 + st * (STAGE_BYTES >> 4);
+          int st_n = st + 1;
+          uint32_t par_n = par;
+          if (st_n == ST) { st_n = 0; par_n ^= 1; }
+          if (t + 1 < nsub) {
+            if (!mbar_wait(&misc->full[st_n], par_n, abort_flag, 1203, t)) break;
+            tc_fence_after();
+            issue_scores(st_lo0 + st_n * (STAGE_BYTES >> 4), u ^ 1);
+          }
+          if (!mbar_wait(&misc->ds_full[u], (t >> 1) & 1, abort_flag, 1204, t)) break;
+          tc_fence_after();
+          // Z as MN-major B: N = 128 columns = two atoms 8 KB apart, K = the 64 streamed rows
+#pragma unroll
+          for (int k = 0; k < SUB / 16; ++k)
+            mma_ts_lo(tb + T_OUT, tb + T_S + u * SUB + k * 16, sp_lo + ((8192u >> 4) << 16) - (1u << 16) + k * (2048 >> 4), IDESC_OUT,
+                      (t > 0 || k > 0));
+          mma_commit(&misc->empty[st]);
+          st = st_n;
+          par = par_n;
+        }
+        mma_commit(&misc->acc_full);
+      }
+    }
+  } else {
+    const int g = warp >> 2;                       // columns [16g, 16g+16) of every sub-tile
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
+    const uint32_t tb = tmem_base + lane_base;
+    const float sl2 = args.sm_scale * 1.4426950408889634f;
+    const float lam = load_lambda(args.lambda_ptr, args.lambda_dtype);
+    const float coef = br ? -lam : 1.f;
+    const size_t grow = size_t(bh) * args.n + size_t(tile) * BM + row;
+    float neg_l = 0.f, e = 0.f;
+    if (QSIDE) {
+      const float4 sv = args.stats[grow];
+      neg_l = br ? -sv.y : -sv.x;
+      e = br ? sv.w : sv.z;
+    }
+    bool ok = true;
+    int st = 0;
+    for (int t = 0; t < nsub; ++t) {
+      const int u = t & 1;
+      const uint32_t t_s = tb + T_S + u * SUB + g * 16, t_t = tb + T_T + u * SUB + g * 16;
+      const float4* stats = reinterpret_cast<const float4*>(smem + OFF_STAGE + st * STAGE_BYTES + Z_BYTES + W_BYTES) + g * 16;
+      if (!mbar_wait(&misc->s_full[u], (t >> 1) & 1, abort_flag, 1301 + g, t)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t s[16], tt[16], ds[8];
+      tmem_ld16(t_s, s);
+      tmem_ld16(t_t, tt);
+      tc_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float v[2];
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+          const int j = 2 * i + w;
+          float nl = neg_l, ee = e;
+          if (!QSIDE) {
+            const float4 sv = stats[j];
+            nl = br ? -sv.y : -sv.x;
+            ee = br ? sv.w : sv.z;
+          }
+          const float p = coef * ex2(fmaf(__uint_as_float(s[j]), sl2, nl));
+          v[w] = p * (__uint_as_float(tt[j]) - ee);
+        }
+        ds[i] = pack_half2(v[0], v[1]);
+      }
+      asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                   ::"r"(t_s), "r"(ds[0]), "r"(ds[1]), "r"(ds[2]), "r"(ds[3]), "r"(ds[4]), "r"(ds[5]), "r"(ds[6]), "r"(ds[7]) : "memory");
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&misc->ds_full[u]);
+      if (++st == ST) st = 0;
+    }
+    ok = ok && mbar_wait(&misc->acc_full, 0, abort_flag, 1311 + g);
+    tc_fence_after();
+    uint32_t acc[32];
+    tmem_ld32(tb + T_OUT + g * 32, acc);
+    tc_wait_ld();
+    if (ok && !*abort_flag) {
+      const float sc = args.sm_scale;
+      __half* out = QSIDE ? (br ? args.dq2 : args.dq1) : (br ? args.dk2 : args.dk1);
+      uint4* p = reinterpret_cast<uint4*>(out + grow * HD + g * 32);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 v;
+        v.x = pack_half2(__uint_as_float(acc[8 * i + 0]) * sc, __uint_as_float(acc[8 * i + 1]) * sc);
+        v.y = pack_half2(__uint_as_float(acc[8 * i + 2]) * sc, __uint_as_float(acc[8 * i + 3]) * sc);
+        v.z = pack_half2(__uint_as_float(acc[8 * i + 4]) * sc, __uint_as_float(acc[8 * i + 5]) * sc);
+        v.w = pack_half2(__uint_as_float(acc[8 * i + 6]) * sc, __uint_as_float(acc[8 * i + 7]) * sc);
+        p[i] = v;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == WARP_MMA) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// dV for D = 128: one CTA = 128 key/value rows; query tiles of 64 rows stream by.
+// TMEM: dV [0,256) | S1^T two 64-column buffers [256,384) | S2^T likewise [384,512).
+// (P1 - lam P2)^T goes through one K-major shared-memory tile (A operand of dV += Pc^T dA).
+// ------------------------------------------------------------------------------------------------
+namespace dv128 {
+constexpr int BKV = 128, BQ = 64, HD = 128, DV = 256, ST = 2, NWG = 4;
+constexpr int K_BYTES = BKV * HD * 2;       // 32 KB: two boxes [128 x 64]
+constexpr int Q_BYTES = BQ * HD * 2;        // 16 KB: two boxes [64 x 64]
+constexpr int DA_BYTES = BQ * DV * 2;       // 32 KB: four boxes [64 x 64]
+constexpr int STAT_BYTES = BQ * 16;
+constexpr int STAGE_BYTES = 2 * Q_BYTES + DA_BYTES + STAT_BYTES;   // 65 KB
+constexpr int PC_BYTES = BKV * BQ * 2;      // 16 KB
+constexpr int OFF_K1 = 0, OFF_K2 = K_BYTES, OFF_PC = 2 * K_BYTES, OFF_STAGE = OFF_PC + PC_BYTES;   // 80 KB
+constexpr int OFF_MISC = OFF_STAGE + ST * STAGE_BYTES;                                             // 210 KB
+constexpr int MISC_BYTES = 1024;
+constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
+constexpr int NUM_THREADS = NWG * 128 + 64;
+constexpr int WARP_TMA = NWG * 4, WARP_MMA = NWG * 4 + 1;
+constexpr int T_DV = 0, T_S1 = 256, T_S2 = 384;
+struct Misc {
+  uint64_t bar_kv;
+  uint64_t full[ST], empty[ST];
+  uint64_t s_full[2], e_done, mma_done, acc_full;
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+}  // namespace dv128
+
+__global__ void __launch_bounds__(dv128::NUM_THREADS, 1)
+diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
+                          const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k2,
+                          const __grid_constant__ CUtensorMap tm_da, const BwdArgs args) {
+  using namespace dv128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Misc* misc = reinterpret_cast<Misc*>(smem + OFF_MISC);
+  volatile int* abort_flag = &misc->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kv_tile = blockIdx.x, bh = blockIdx.y;
+  const int b_idx = bh / args.h, h_idx = bh % args.h;
+  const int nq = args.n / BQ;
+
+  if (warp == WARP_TMA && lane == 0) {
+    mbar_init(&misc->bar_kv, 1);
+    for (int i = 0; i < ST; ++i) { mbar_init(&misc->full[i], 1); mbar_init(&misc->empty[i], 1); }
+    for (int u = 0; u < 2; ++u) mbar_init(&misc->s_full[u], 1);
+    mbar_init(&misc->e_done, NWG * 128);
+    mbar_init(&misc->mma_done, 1);
+    mbar_init(&misc->acc_full, 1);
+    misc->abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == WARP_MMA) tmem_alloc(&misc->tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&misc->tmem_slot);
+
+  if (warp == WARP_TMA) {
+    if (elect_one()) {
+      mbar_expect_tx(&misc->bar_kv, 2 * K_BYTES);
+      for (int c = 0; c < 2; ++c) {
+        tma_load_4d(smem + OFF_K1 + c * 16384, &tm_k1, &misc->bar_kv, c * 64, kv_tile * BKV, h_idx, b_idx);
+        tma_load_4d(smem + OFF_K2 + c * 16384, &tm_k2, &misc->bar_kv, c * 64, kv_tile * BKV, h_idx, b_idx);
+      }
+      int st = 0;
+      uint32_t par = 1;
+      for (int i = 0; i < nq; ++i) {
+        uint8_t* sp = smem + OFF_STAGE + st * STAGE_BYTES;
+        if (!mbar_wait(&misc->empty[st], par, abort_flag, 1401, i)) break;
+        mbar_expect_tx(&misc->full[st], STAGE_BYTES);
+        for (int c = 0; c < 2; ++c) {
+          tma_load_4d(sp + c * 8192, &tm_q1, &misc->full[st], c * 64, i * BQ, h_idx, b_idx);
+          tma_load_4d(sp + Q_BYTES + c * 8192, &tm_q2, &misc->full[st], c * 64, i * BQ, h_idx, b_idx);
+        }
+        for (int c = 0; c < 4; ++c) tma_load_4d(sp + 2 * Q_BYTES + c * 8192, &tm_da, &misc->full[st], c * 64, i * BQ, bh, 0);
+        bulk_load_1d(sp + 2 * Q_BYTES + DA_BYTES, args.stats + (size_t(bh) * args.n + size_t(i) * BQ), STAT_BYTES, &misc->full[st]);
+        if (++st == ST) { st = 0; par ^= 1; }
+      }
+    }
+  } else if (warp == WARP_MMA) {
+    if (elect_one()) {
+      constexpr uint32_t IDESC_S = make_idesc(BKV, BQ, 0, 0);
+      constexpr uint32_t IDESC_DV = make_idesc(BKV, DV, 0, 1);     // N = 256: dA as MN-major B, four atoms 8 KB apart
+      const uint32_t k1_lo = sdesc_lo(smem_u32(smem + OFF_K1)), k2_lo = sdesc_lo(smem_u32(smem + OFF_K2));
+      const uint32_t pc_lo = sdesc_lo(smem_u32(smem + OFF_PC));
+      const uint32_t st_lo0 = sdesc_lo(smem_u32(smem + OFF_STAGE));
+      const uint32_t tb = tmem_base;
+      auto issue_scores = [&](uint32_t sp_lo, int u) {
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          mma_ss_lo(tb + T_S1 + u * BQ, k1_lo + (k / 4) * (16384 >> 4) + (k % 4) * 2, sp_lo + (k / 4) * (8192 >> 4) + (k % 4) * 2,
+                    IDESC_S, k > 0);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          mma_ss_lo(tb + T_S2 + u * BQ, k2_lo + (k / 4) * (16384 >> 4) + (k % 4) * 2,
+                    sp_lo + (Q_BYTES >> 4) + (k / 4) * (8192 >> 4) + (k % 4) * 2, IDESC_S, k > 0);
+        mma_commit(&misc->s_full[u]);
+      };
+      bool ok = mbar_wait(&misc->bar_kv, 0, abort_flag, 1501);
+      ok = ok && mbar_wait(&misc->full[0], 0, abort_flag, 1502);
+      if (ok) {
+        tc_fence_after();
+        issue_scores(st_lo0, 0);
+        int st = 0;
+        uint32_t par = 0;
+        for (int i = 0; i < nq; ++i) {
+          const int u = i & 1;
+          const uint32_t sp_lo = st_lo0 + st * (STAGE_BYTES >> 4);
+          int st_n = st + 1;
+          uint32_t par_n = par;
+          if (st_n == ST) { st_n = 0; par_n ^= 1; }
+          if (i + 1 < nq) {
+            if (!mbar_wait(&misc->full[st_n], par_n, abort_flag, 1503, i)) break;
+            tc_fence_after();
+            issue_scores(st_lo0 + st_n * (STAGE_BYTES >> 4), u ^ 1);
+          }
+          if (!mbar_wait(&misc->e_done, i & 1, abort_flag, 1504, i)) break;
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < BQ / 16; ++k)
+            mma_ss_lo(tb + T_DV, pc_lo + k * 2, sp_lo + ((2 * Q_BYTES) >> 4) + ((8192u >> 4) << 16) - (1u << 16) + k * (2048 >> 4),
+                      IDESC_DV, (i > 0 || k > 0));
+          mma_commit(&misc->mma_done);
+          mma_commit(&misc->empty[st]);
+          st = st_n;
+          par = par_n;
+        }
+        mma_commit(&misc->acc_full);
+      }
+    }
+  } else {
+    const int g = warp >> 2;                       // query columns [16g, 16g+16) of every tile
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
+    const uint32_t tb = tmem_base + lane_base;
+    const float sl2 = args.sm_scale * 1.4426950408889634f;
+    const float lam = load_lambda(args.lambda_ptr, args.lambda_dtype);
+    bool ok = true;
+    int st = 0;
+    for (int i = 0; i < nq; ++i) {
+      const int u = i & 1;
+      const float4* stats = reinterpret_cast<const float4*>(smem + OFF_STAGE + st * STAGE_BYTES + 2 * Q_BYTES + DA_BYTES) + g * 16;
+      if (!mbar_wait(&misc->s_full[u], (i >> 1) & 1, abort_flag, 1601 + g, i)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t s1[16], s2[16], pc[8];
+      tmem_ld16(tb + T_S1 + u * BQ + g * 16, s1);
+      tmem_ld16(tb + T_S2 + u * BQ + g * 16, s2);
+      tc_wait_ld();
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) {
+        float v[2];
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+          const int j = 2 * jj + w;
+          const float4 sv = stats[j];
+          v[w] = ex2(fmaf(__uint_as_float(s1[j]), sl2, -sv.x)) - lam * ex2(fmaf(__uint_as_float(s2[j]), sl2, -sv.y));
+        }
+        pc[jj] = pack_half2(v[0], v[1]);
+      }
+      // the single Pc tile is free once dV of the previous query tile has been accumulated
+      if (i > 0) {
+        if (!mbar_wait(&misc->mma_done, (i - 1) & 1, abort_flag, 1605 + g, i)) { ok = false; break; }
+      }
+      {
+        uint8_t* prow = smem + OFF_PC + row * 128;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int chunk = (g * 2 + c) ^ (row & 7);
+          *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(pc[4 * c], pc[4 * c + 1], pc[4 * c + 2], pc[4 * c + 3]);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_before();
+      mbar_arrive(&misc->e_done);
+      if (++st == ST) st = 0;
+    }
+    ok = ok && mbar_wait(&misc->acc_full, 0, abort_flag, 1611 + g);
+    tc_fence_after();
+    uint32_t acc[64];
+    const size_t grow = size_t(bh) * args.n + size_t(kv_tile) * BKV + row;
+    tmem_ld32(tb + T_DV + g * 64, acc);
+    tmem_ld32(tb + T_DV + g * 64 + 32, acc + 32);
+    tc_wait_ld();
+    if (ok && !*abort_flag) {
+      uint4* p = reinterpret_cast<uint4*>(args.dv + grow * DV + g * 64);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        uint4 v;
+        v.x = pack_half2(__uint_as_float(acc[8 * i + 0]), __uint_as_float(acc[8 * i + 1]));
+        v.y = pack_half2(__uint_as_float(acc[8 * i + 2]), __uint_as_float(acc[8 * i + 3]));
+        v.z = pack_half2(__uint_as_float(acc[8 * i + 4]), __uint_as_float(acc[8 * i + 5]));
+        v.w = pack_half2(__uint_as_float(acc[8 * i + 6]), __uint_as_float(acc[8 * i + 7]));
+        p[i] = v;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == WARP_MMA) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace da

@@ -12,7 +12,9 @@
 #include <mutex>
 
 #include "bwd.cuh"
+#include "bwd128.cuh"
 #include "fwd.cuh"
+#include "fwd128.cuh"
 #include "sm100.cuh"
 
 namespace {
@@ -79,7 +81,7 @@ int check_common(const DiffAttnParams* p, bool bwd) {
   if (p->B < 0 || p->H < 0 || p->N < 0 || p->D <= 0)
     return fail(DIFFATTN_ERR_BAD_SHAPE, "negative size: B=%d H=%d N=%d D=%d", p->B, p->H, p->N, p->D);
   if (!diffattn_supports(p->D, bwd ? 1 : 0))
-    return fail(DIFFATTN_ERR_UNSUPPORTED_D, "head dim %d is not compiled in (supported: 32, 64)", p->D);
+    return fail(DIFFATTN_ERR_UNSUPPORTED_D, "head dim %d is not compiled in (supported: 32, 64, 128)", p->D);
   if (p->N % 128 != 0)
     return fail(DIFFATTN_ERR_BAD_SHAPE, "N=%d must be a multiple of 128 (no masking, as the reference)", p->N);
   if (p->lambda_dtype != DIFFATTN_LAMBDA_F16 && p->lambda_dtype != DIFFATTN_LAMBDA_F32)
@@ -132,7 +134,7 @@ const char* diffattn_last_error(void) { return g_err; }
 int diffattn_version(void) { return DIFFATTN_VERSION; }
 int diffattn_supports(int32_t d, int32_t dir) {
   (void)dir;
-  return (d == 64 || d == 32) ? 1 : 0;
+  return (d == 64 || d == 32 || d == 128) ? 1 : 0;
 }
 
 uint64_t diffattn_workspace_bytes(const DiffAttnParams* p) {
@@ -149,11 +151,12 @@ int diffattn_fwd(const DiffAttnParams* p) {
   cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
   CUtensorMap mq1, mq2, mk1, mk2, mv;
   const int D = p->D, DV = 2 * p->D;
+  const int kv_rows = D == 128 ? 64 : 128;      // the D = 128 kernel streams 64-row tiles
   if ((rc = make_map(&mq1, p->q1, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "q1"))) return rc;
   if ((rc = make_map(&mq2, p->q2, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "q2"))) return rc;
-  if ((rc = make_map(&mk1, p->k1, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "k1"))) return rc;
-  if ((rc = make_map(&mk2, p->k2, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "k2"))) return rc;
-  if ((rc = make_map(&mv, p->v, DV, p->N, p->H, p->B, p->v_stride_n, p->v_stride_h, p->v_stride_b, 128, "v"))) return rc;
+  if ((rc = make_map(&mk1, p->k1, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, kv_rows, "k1"))) return rc;
+  if ((rc = make_map(&mk2, p->k2, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, kv_rows, "k2"))) return rc;
+  if ((rc = make_map(&mv, p->v, DV, p->N, p->H, p->B, p->v_stride_n, p->v_stride_h, p->v_stride_b, kv_rows, "v"))) return rc;
   da::FwdArgs a;
   a.y = static_cast<__half*>(p->y);
   a.a2 = static_cast<__half*>(p->a2);
@@ -161,6 +164,13 @@ int diffattn_fwd(const DiffAttnParams* p) {
   a.lambda_ptr = p->lambda_scale; a.lambda_dtype = p->lambda_dtype;
   a.sm_scale = p->sm_scale; a.out_scale = 1.f - p->lambda_init; a.eps = p->eps;
   a.rms_norm = p->rms_norm; a.n = p->N; a.h = p->H; a.d = p->D;
+  if (D == 128) {
+    if ((rc = set_smem(da::diffattn_fwd128_kernel, da::fwd128::SMEM_BYTES))) return rc;
+    dim3 grid128(p->N / da::fwd128::BM, p->B * p->H);
+    da::diffattn_fwd128_kernel<<<grid128, da::fwd128::NUM_THREADS, da::fwd128::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, a);
+    DA_CUDA(cudaGetLastError());
+    return DIFFATTN_OK;
+  }
   if ((rc = set_smem(da::diffattn_fwd64_kernel, da::fwd64::SMEM_BYTES))) return rc;
   dim3 grid(p->N / da::fwd64::BM, p->B * p->H);
   da::diffattn_fwd64_kernel<<<grid, da::fwd64::NUM_THREADS, da::fwd64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, a);
@@ -200,9 +210,48 @@ int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages) {
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p->device);
     long long blocks = (long long)((rows + 7) / 8);
     if (blocks > (long long)sms * 8) blocks = (long long)sms * 8;
-    if (D == 64) da::diffattn_bwd_pre_kernel<4><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    if (D == 128) da::diffattn_bwd_pre_kernel<8><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    else if (D == 64) da::diffattn_bwd_pre_kernel<4><<<(unsigned)blocks, 256, 0, stream>>>(a);
     else da::diffattn_bwd_pre_kernel<2><<<(unsigned)blocks, 256, 0, stream>>>(a);
     DA_CUDA(cudaGetLastError());
+  }
+  if (D == 128) {
+    // D = 128: dV kernel, then dK and dQ through the per-branch "side" kernel (bwd128.cuh)
+    auto qk = [&](CUtensorMap* m, const void* ptr, int rows, const char* nm) {
+      return make_map(m, ptr, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, rows, nm);
+    };
+    CUtensorMap q1_64, q2_64, k1_64, k2_64, q1_128, q2_128, k1_128, k2_128, v_64, v_128, da_64, da_128;
+    if ((rc = qk(&q1_64, p->q1, 64, "q1"))) return rc;
+    if ((rc = qk(&q2_64, p->q2, 64, "q2"))) return rc;
+    if ((rc = qk(&k1_64, p->k1, 64, "k1"))) return rc;
+    if ((rc = qk(&k2_64, p->k2, 64, "k2"))) return rc;
+    if ((rc = qk(&q1_128, p->q1, 128, "q1"))) return rc;
+    if ((rc = qk(&q2_128, p->q2, 128, "q2"))) return rc;
+    if ((rc = qk(&k1_128, p->k1, 128, "k1"))) return rc;
+    if ((rc = qk(&k2_128, p->k2, 128, "k2"))) return rc;
+    if ((rc = make_map(&v_64, p->v, DV, p->N, p->H, p->B, p->v_stride_n, p->v_stride_h, p->v_stride_b, 64, "v"))) return rc;
+    if ((rc = make_map(&v_128, p->v, DV, p->N, p->H, p->B, p->v_stride_n, p->v_stride_h, p->v_stride_b, 128, "v"))) return rc;
+    if ((rc = make_map(&da_64, a.da, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 64, "dA"))) return rc;
+    if ((rc = make_map(&da_128, a.da, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 128, "dA"))) return rc;
+    if (stages & DIFFATTN_STAGE_DKDV) {
+      if ((rc = set_smem(da::diffattn_bwd_dv128_kernel, da::dv128::SMEM_BYTES))) return rc;
+      dim3 g1(p->N / 128, (unsigned)bh);
+      da::diffattn_bwd_dv128_kernel<<<g1, da::dv128::NUM_THREADS, da::dv128::SMEM_BYTES, stream>>>(q1_64, q2_64, k1_128, k2_128, da_64, a);
+      DA_CUDA(cudaGetLastError());
+      if ((rc = set_smem(da::diffattn_bwd_side128_kernel<false>, da::side128::SMEM_BYTES))) return rc;
+      dim3 g2(p->N / 128, (unsigned)bh, 2);
+      da::diffattn_bwd_side128_kernel<false><<<g2, da::side128::NUM_THREADS, da::side128::SMEM_BYTES, stream>>>(
+          k1_128, k2_128, v_128, q1_64, q2_64, da_64, a);
+      DA_CUDA(cudaGetLastError());
+    }
+    if (stages & DIFFATTN_STAGE_DQ) {
+      if ((rc = set_smem(da::diffattn_bwd_side128_kernel<true>, da::side128::SMEM_BYTES))) return rc;
+      dim3 g3(p->N / 128, (unsigned)bh, 2);
+      da::diffattn_bwd_side128_kernel<true><<<g3, da::side128::NUM_THREADS, da::side128::SMEM_BYTES, stream>>>(
+          q1_128, q2_128, da_128, k1_64, k2_64, v_64, a);
+      DA_CUDA(cudaGetLastError());
+    }
+    return DIFFATTN_OK;
   }
   CUtensorMap mq1, mq2, mk1, mk2, mv, mda;
   // 2. dK, dV: key/value tiles of 128 rows resident, query-side tiles of 64 rows streamed

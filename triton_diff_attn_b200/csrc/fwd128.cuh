@@ -1,0 +1,342 @@
+// Differential-attention forward for head dim D = 128 (value width 256), sm_100a.
+//
+// Same roles and TMEM map as the D = 64 kernel (fwd.cuh): S1/S2 in two 64-column buffers each, O1 and O2
+// 128 columns each.  Two 256-wide accumulators do not fit in TMEM, so one CTA makes two passes over the
+// key/value sequence, one per 128-column half of V: the scores and probabilities are recomputed in the
+// second pass (same values), the row statistics are identical in both, and the RMSNorm sum of squares is
+// accumulated over the two passes.  With rms_norm the first half of A is parked as fp16 pairs in
+// registers until the second pass has produced rstd.  Streamed tiles are 64 rows: {K1, K2, V half}.
+#pragma once
+#include "fwd.cuh"
+#include "sm100.cuh"
+
+namespace da {
+
+namespace fwd128 {
+constexpr int BM = 128, SUB = 64, HD = 128, DV = 256, ST = 3;
+constexpr int Q_BYTES = BM * HD * 2;            // 32 KB: two boxes [128 x 64]
+constexpr int K_BYTES = SUB * HD * 2;           // 16 KB: two boxes [64 x 64]
+constexpr int V_BYTES = SUB * 128 * 2;          // 16 KB: the pass's 128 value columns, two boxes [64 x 64]
+constexpr int STAGE_BYTES = 2 * K_BYTES + V_BYTES;   // 48 KB
+constexpr int OFF_Q1 = 0, OFF_Q2 = Q_BYTES, OFF_STAGE = 2 * Q_BYTES;   // 64 KB
+constexpr int OFF_MISC = OFF_STAGE + ST * STAGE_BYTES;                 // 208 KB
+constexpr int MISC_BYTES = 4096;
+constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
+constexpr int NUM_THREADS = 320;
+constexpr int T_O = 256;
+
+struct Misc {
+  uint64_t bar_q;
+  uint64_t full[ST], empty[ST];
+  uint64_t s_full[2][2], p_full[2][2];
+  uint64_t o_done[2];
+  uint64_t o_full;
+  uint32_t tmem_slot;
+  int abort_flag;
+  float coef1[BM], coef2[BM];
+  float ssq[2][BM];
+};
+static_assert(sizeof(Misc) <= MISC_BYTES, "misc area too small");
+}  // namespace fwd128
+
+__global__ void __launch_bounds__(fwd128::NUM_THREADS, 1)
+diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
+                       const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k2,
+                       const __grid_constant__ CUtensorMap tm_v, const FwdArgs args) {
+  using namespace fwd128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Misc* misc = reinterpret_cast<Misc*>(smem + OFF_MISC);
+  volatile int* abort_flag = &misc->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_tile = blockIdx.x, bh = blockIdx.y;
+  const int b_idx = bh / args.h, h_idx = bh % args.h;
+  const int nsub = args.n / SUB;
+  const int ntot = 2 * nsub;          // sub-tiles over both passes
+
+  if (warp == 8 && lane == 0) {
+    mbar_init(&misc->bar_q, 1);
+    for (int i = 0; i < ST; ++i) { mbar_init(&misc->full[i], 1); mbar_init(&misc->empty[i], 1); }
+    for (int b = 0; b < 2; ++b) {
+      for (int u = 0; u < 2; ++u) { mbar_init(&misc->s_full[b][u], 1); mbar_init(&misc->p_full[b][u], 128); }
+      mbar_init(&misc->o_done[b], 1);
+    }
+    mbar_init(&misc->o_full, 1);
+    misc->abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == 9) tmem_alloc(&misc->tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&misc->tmem_slot);
+
+  if (warp == 8) {
+    if (elect_one()) {
+      mbar_expect_tx(&misc->bar_q, 2 * Q_BYTES);
+      for (int c = 0; c < 2; ++c) {
+        tma_load_4d(smem + OFF_Q1 + c * 16384, &tm_q1, &misc->bar_q, c * 64, q_tile * BM, h_idx, b_idx);
+        tma_load_4d(smem + OFF_Q2 + c * 16384, &tm_q2, &misc->bar_q, c * 64, q_tile * BM, h_idx, b_idx);
+      }
+      int st = 0;
+      uint32_t par = 1;
+      for (int gt = 0; gt < ntot; ++gt) {
+        const int pass = gt >= nsub, t = pass ? gt - nsub : gt;
+        uint8_t* sp = smem + OFF_STAGE + st * STAGE_BYTES;
+        if (!mbar_wait(&misc->empty[st], par, abort_flag, 2101, gt)) break;
+        mbar_expect_tx(&misc->full[st], STAGE_BYTES);
+        for (int c = 0; c < 2; ++c) {
+          tma_load_4d(sp + c * 8192, &tm_k1, &misc->full[st], c * 64, t * SUB, h_idx, b_idx);
+          tma_load_4d(sp + K_BYTES + c * 8192, &tm_k2, &misc->full[st], c * 64, t * SUB, h_idx, b_idx);
+          tma_load_4d(sp + 2 * K_BYTES + c * 8192, &tm_v, &misc->full[st], pass * 128 + c * 64, t * SUB, h_idx, b_idx);
+        }
+        if (++st == ST) { st = 0; par ^= 1; }
+      }
+    }
+  } else if (warp == 9) {
+    if (elect_one()) {
+      constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0);
+      constexpr uint32_t IDESC_O = make_idesc(BM, 128, 0, 1);
+      const uint32_t q1_lo = sdesc_lo(smem_u32(smem + OFF_Q1)), q2_lo = sdesc_lo(smem_u32(smem + OFF_Q2));
+      const uint32_t st_lo0 = sdesc_lo(smem_u32(smem + OFF_STAGE));
+      const uint32_t tb = tmem_base;
+      auto issue_s = [&](uint32_t sp_lo, int u) {
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          mma_ss_lo(tb + u * SUB, q1_lo + (k / 4) * (16384 >> 4) + (k % 4) * 2, sp_lo + (k / 4) * (8192 >> 4) + (k % 4) * 2, IDESC_S, k > 0);
+        mma_commit(&misc->s_full[0][u]);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          mma_ss_lo(tb + 128 + u * SUB, q2_lo + (k / 4) * (16384 >> 4) + (k % 4) * 2,
+                    sp_lo + (K_BYTES >> 4) + (k / 4) * (8192 >> 4) + (k % 4) * 2, IDESC_S, k > 0);
+        mma_commit(&misc->s_full[1][u]);
+      };
+      bool ok = mbar_wait(&misc->bar_q, 0, abort_flag, 2201);
+      ok = ok && mbar_wait(&misc->full[0], 0, abort_flag, 2202);
+      if (ok) {
+        tc_fence_after();
+        issue_s(st_lo0, 0);
+        int st = 0;
+        uint32_t par = 0;
+        for (int gt = 0; gt < ntot; ++gt) {
+          const int u = gt & 1;
+          const int t = gt >= nsub ? gt - nsub : gt;
+          const uint32_t sp_lo = st_lo0 + st * (STAGE_BYTES >> 4);
+          // V half-tile as MN-major B: 128 columns = two atoms 8 KB apart
+          const uint32_t v_lo = sp_lo + ((2 * K_BYTES) >> 4) + ((8192u >> 4) << 16) - (1u << 16);
+          int st_n = st + 1;
+          uint32_t par_n = par;
+          if (st_n == ST) { st_n = 0; par_n ^= 1; }
+          if (gt + 1 < ntot) {
+            if (!mbar_wait(&misc->full[st_n], par_n, abort_flag, 2203, gt)) break;
+            tc_fence_after();
+            issue_s(st_lo0 + st_n * (STAGE_BYTES >> 4), u ^ 1);
+          }
+          const uint32_t ph = (gt >> 1) & 1;
+          if (!mbar_wait(&misc->p_full[0][u], ph, abort_flag, 2204, gt)) break;
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < SUB / 16; ++k)
+            mma_ts_lo(tb + T_O, tb + u * SUB + k * 8, v_lo + k * (2048 >> 4), IDESC_O, (t > 0 || k > 0));
+          mma_commit(&misc->o_done[0]);
+          if (!mbar_wait(&misc->p_full[1][u], ph, abort_flag, 2205, gt)) break;
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < SUB / 16; ++k)
+            mma_ts_lo(tb + T_O + 128, tb + 128 + u * SUB + k * 8, v_lo + k * (2048 >> 4), IDESC_O, (t > 0 || k > 0));
+          mma_commit(&misc->o_done[1]);
+          mma_commit(&misc->empty[st]);
+          if (t == nsub - 1) mma_commit(&misc->o_full);
+          st = st_n;
+          par = par_n;
+        }
+      }
+    }
+  } else {
+    const int br = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
+    const uint32_t t_s0 = tmem_base + lane_base + br * 128;
+    const uint32_t t_o = tmem_base + lane_base + T_O + br * 128;
+    const float sl2 = args.sm_scale * 1.4426950408889634f;
+    const float lam = load_lambda(args.lambda_ptr, args.lambda_dtype);
+    const size_t grow = size_t(bh) * args.n + size_t(q_tile) * BM + row;
+    bool ok = true;
+    float ssq_total = 0.f;
+    uint32_t parked[32];            // first-pass A (this thread's 64 columns) as fp16 pairs, used with rms_norm
+#pragma unroll
+    for (int i = 0; i < 32; ++i) parked[i] = 0u;
+
+    for (int pass = 0; pass < 2; ++pass) {
+      float m_run = -INFINITY, l_run = 0.f;
+      for (int t = 0; t < nsub; ++t) {
+        const int gt = pass * nsub + t;
+        const uint32_t t_s = t_s0 + (gt & 1) * SUB;
+        if (!mbar_wait(&misc->s_full[br][gt & 1], (gt >> 1) & 1, abort_flag, 2301 + br, gt)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t sr[SUB];
+        tmem_ld32(t_s + 0, sr);
+        tmem_ld32(t_s + 32, sr + 32);
+        tc_wait_ld();
+        float neg = -m_run * sl2;
+        float sum[4] = {0.f, 0.f, 0.f, 0.f};
+        float mx[4];
+        uint32_t pk[SUB / 2];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) mx[c] = __uint_as_float(sr[c]);
+        if (t > 0) {
+#pragma unroll
+          for (int i = 0; i < SUB / 2; ++i) {
+            const float p0 = ex2(fmaf(__uint_as_float(sr[2 * i]), sl2, neg));
+            const float p1 = ex2(fmaf(__uint_as_float(sr[2 * i + 1]), sl2, neg));
+            sum[(2 * i) & 3] += p0;
+            sum[(2 * i + 1) & 3] += p1;
+            pk[i] = pack_half2(p0, p1);
+            mx[i & 3] = max3(mx[i & 3], __uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < SUB / 2; ++i)
+            mx[i & 3] = max3(mx[i & 3], __uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]));
+        }
+        const float m_new = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        const bool need = (t == 0) || ((m_new - m_run) * sl2 > 8.f);
+        if (__any_sync(0xffffffffu, need)) {
+          if (t > 0) {
+            if (!mbar_wait(&misc->o_done[br], (gt - 1) & 1, abort_flag, 2305 + br, gt)) { ok = false; break; }
+            tc_fence_after();
+            const float scale = need ? ex2((m_run - m_new) * sl2) : 1.f;
+            l_run *= scale;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t o[32];
+              tmem_ld32(t_o + c * 32, o);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * scale);
+              tmem_st32(t_o + c * 32, o);
+            }
+          }
+          if (need) m_run = m_new;
+          neg = -m_run * sl2;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) sum[c] = 0.f;
+#pragma unroll
+          for (int i = 0; i < SUB / 2; ++i) {
+            const float p0 = ex2(fmaf(__uint_as_float(sr[2 * i]), sl2, neg));
+            const float p1 = ex2(fmaf(__uint_as_float(sr[2 * i + 1]), sl2, neg));
+            sum[(2 * i) & 3] += p0;
+            sum[(2 * i + 1) & 3] += p1;
+            pk[i] = pack_half2(p0, p1);
+          }
+        }
+        l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+        tmem_st32(t_s, pk);
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(&misc->p_full[br][gt & 1]);
+      }
+
+      // ---- epilogue of this pass (value columns [128 pass, 128 pass + 128)); every thread runs every barrier
+      ok = ok && mbar_wait(&misc->o_full, pass & 1, abort_flag, 2311 + br, pass);
+      tc_fence_after();
+      const float inv_l = 1.f / l_run;
+      if (br == 0) misc->coef1[row] = inv_l; else misc->coef2[row] = inv_l;
+      named_bar_sync(1, 256);
+      const float c1 = misc->coef1[row], c2 = misc->coef2[row];
+      const uint32_t t_o1 = tmem_base + lane_base + T_O + br * 64;
+      const uint32_t t_o2 = tmem_base + lane_base + T_O + 128 + br * 64;
+      uint32_t o1[64], o2[64];
+      tmem_ld32(t_o1, o1);
+      tmem_ld32(t_o1 + 32, o1 + 32);
+      tmem_ld32(t_o2, o2);
+      tmem_ld32(t_o2 + 32, o2 + 32);
+      tc_wait_ld();
+      float ssq = 0.f;
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        const float a2v = __uint_as_float(o2[i]) * c2;
+        const float av = __uint_as_float(o1[i]) * c1 - lam * a2v;
+        ssq += av * av;
+        o1[i] = __float_as_uint(av);
+        o2[i] = __float_as_uint(a2v);
+      }
+      misc->ssq[br][row] = ssq;
+      tc_fence_before();
+      named_bar_sync(1, 256);          // all O reads are complete here: the next pass may overwrite O
+      ssq_total += misc->ssq[0][row] + misc->ssq[1][row];
+      const bool live = ok && !*abort_flag;
+      const int col0 = pass * 128 + br * 64;
+      if (live) {
+        uint4* ap = reinterpret_cast<uint4*>(args.a2 + grow * DV + col0);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          uint4 av;
+          av.x = pack_half2(__uint_as_float(o2[8 * i + 0]), __uint_as_float(o2[8 * i + 1]));
+          av.y = pack_half2(__uint_as_float(o2[8 * i + 2]), __uint_as_float(o2[8 * i + 3]));
+          av.z = pack_half2(__uint_as_float(o2[8 * i + 4]), __uint_as_float(o2[8 * i + 5]));
+          av.w = pack_half2(__uint_as_float(o2[8 * i + 6]), __uint_as_float(o2[8 * i + 7]));
+          ap[i] = av;
+        }
+      }
+      if (!args.rms_norm) {
+        if (live) {
+          uint4* yp = reinterpret_cast<uint4*>(args.y + grow * DV + col0);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            uint4 yv;
+            yv.x = pack_half2(__uint_as_float(o1[8 * i + 0]), __uint_as_float(o1[8 * i + 1]));
+            yv.y = pack_half2(__uint_as_float(o1[8 * i + 2]), __uint_as_float(o1[8 * i + 3]));
+            yv.z = pack_half2(__uint_as_float(o1[8 * i + 4]), __uint_as_float(o1[8 * i + 5]));
+            yv.w = pack_half2(__uint_as_float(o1[8 * i + 6]), __uint_as_float(o1[8 * i + 7]));
+            yp[i] = yv;
+          }
+        }
+      } else if (pass == 0) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) parked[i] = pack_half2(__uint_as_float(o1[2 * i]), __uint_as_float(o1[2 * i + 1]));
+      } else {
+        const float rstd = rsqrtf(ssq_total * (1.f / DV) + args.eps);
+        const float ys = args.out_scale * rstd;
+        if (live) {
+          uint4* y0 = reinterpret_cast<uint4*>(args.y + grow * DV + br * 64);
+          uint4* y1 = reinterpret_cast<uint4*>(args.y + grow * DV + col0);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            uint32_t w[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&parked[4 * i + c]));
+              w[c] = pack_half2(f.x * ys, f.y * ys);
+            }
+            y0[i] = make_uint4(w[0], w[1], w[2], w[3]);
+            uint4 yv;
+            yv.x = pack_half2(__uint_as_float(o1[8 * i + 0]) * ys, __uint_as_float(o1[8 * i + 1]) * ys);
+            yv.y = pack_half2(__uint_as_float(o1[8 * i + 2]) * ys, __uint_as_float(o1[8 * i + 3]) * ys);
+            yv.z = pack_half2(__uint_as_float(o1[8 * i + 4]) * ys, __uint_as_float(o1[8 * i + 5]) * ys);
+            yv.w = pack_half2(__uint_as_float(o1[8 * i + 6]) * ys, __uint_as_float(o1[8 * i + 7]) * ys);
+            y1[i] = yv;
+          }
+        }
+      }
+      if (pass == 1 && live) {
+        const float lse = m_run * args.sm_scale + logf(l_run);
+        if (br == 0) {
+          args.lse1[grow] = lse;
+          args.rstd[grow] = rsqrtf(ssq_total * (1.f / DV) + args.eps);
+        } else {
+          args.lse2[grow] = lse;
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace da
