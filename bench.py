@@ -37,6 +37,10 @@ WORKLOADS = {
     "c5shard": (8, 32, 4096, 64, 1.0, 0.5, 0.8, True),   # BASELINE config 5 split over 8 GPUs
     "ref_d32": (4, 16, 4096, 32, 0.5, 0.5, 0.8, True),   # the reference's benchmark point H=16 D=32 N=4096 (src/benchmark.py:19-25)
 }
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
+# profiles/c2_kernels_ncu_full.md (workload c2); other workloads report null.
+NCU_TRAFFIC_BYTES = {"c2": {"diffattn_fwd64_kernel": 309.5e6, "diffattn_bwd_pre_kernel": 257.0e6,
+                            "diffattn_bwd_dkdv64_kernel": 379.2e6, "diffattn_bwd_dq64_kernel": 325.3e6}}
 METRIC = "diff-attn fwd+bwd TFLOP/s (credited 28*B*H*N^2*D), fp16"
 NOMINAL_TFLOPS = 2250.0
 
@@ -317,7 +321,7 @@ def main():
         "bound": "tensor", "kernel": dom, "achieved": achieved, "peak": peaks["burst"], "unit": "TFLOP/s",
         "frac": achieved / peaks["burst"], "peak_kind": f"cuBLAS bf16 burst, {peaks['source']} (kernel timed alone)",
         "executed_tflops": kernels[dom]["executed_tflops"], "executed_frac": kernels[dom]["executed_tflops"] / peaks["burst"],
-        "traffic": None,
+        "traffic": NCU_TRAFFIC_BYTES.get(args.workload, {}).get(dom),
         "whole_step": {"achieved": value / world, "frac_of_measured_sustained": value / world / peaks["sustained"],
                        "frac_of_nominal_2250": value / world / NOMINAL_TFLOPS},
     }
