@@ -1,10 +1,11 @@
 // Differential-attention forward for sm_100a, head dim D = 64 (value width 128).
 //
-// One CTA owns one tile of 128 query rows of one (batch, head).  Roles (10 warps):
-//   warps 0-3  softmax of branch 1 (thread = query row; S1/P1/O1 in TMEM)
-//   warps 4-7  softmax of branch 2
-//   warp  8    TMA producer: Q1,Q2 once; K1,K2 and V tiles through two mbarrier rings
-//   warp  9    tcgen05.mma issuer (one elected thread) and TMEM owner
+// One CTA owns one tile of 128 query rows of one (batch, head).  Roles (12 warps):
+//   warps 0-3   softmax of branch 1 (thread = query row; S1/P1/O1 in TMEM)
+//   warps 4-7   softmax of branch 2
+//   warp  8     TMA producer: Q1,Q2 once; K1,K2 and V tiles through two mbarrier rings
+//   warp  9     tcgen05.mma issuer of S1, S2 (one elected thread; owns TMEM)
+//   warps 10,11 tcgen05.mma issuers of P1 V, P2 V
 // TMEM (512 columns of 128 lanes x 32 bit): S1 two 64-column buffers [0,128), S2 likewise [128,256),
 // O1 [256,384), O2 [384,512).  Scores are produced in sub-tiles of 64 key rows into alternating buffers, so
 // the MMA for sub-tile t+1 runs while the softmax warpgroup works on sub-tile t.  P_b (fp16, two per
@@ -63,7 +64,12 @@ constexpr int OFF_V = OFF_K + KS * 2 * K_BYTES;
 constexpr int OFF_MISC = OFF_V + VS * V_BYTES;           // barriers, coefficients
 constexpr int MISC_BYTES = 4096;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024; // +1024 for manual alignment
-constexpr int NUM_THREADS = 320;
+// warps 0-7 softmax; 8 TMA producer; 9 S issuer (both branches); 10, 11 P V issuers of branch 1, 2: one role
+// warp per scheduler (warp % 4).  A single warp issuing every MMA slows the row quarter that shares its
+// scheduler by about 30 %, and every barrier waits for that quarter.  Twelve warps keep three per scheduler,
+// which leaves 168 registers per thread (a thirteenth warp would cap them at 128).
+constexpr int NUM_THREADS = 384;
+constexpr int WARP_TMA = 8, WARP_S = 9, WARP_PV = 10;
 // TMEM columns: S_b buffer u at 128*b + 64*u; O1 at 256, O2 at 384
 constexpr int T_O = 256;
 
@@ -73,7 +79,7 @@ struct Misc {
   uint64_t v_full[VS], v_empty[VS];
   uint64_t s_full[2][2];     // [branch][buffer]: S sub-tile written by the MMA
   uint64_t p_full[2][2];     // [branch][buffer]: P written by the softmax warpgroup (128 arrivals)
-  uint64_t o_done[2];        // [branch]: one phase per P V sub-tile MMA
+  uint64_t pv_done[2][2];    // [branch][buffer]: P_b V of the sub-tile that used this buffer has completed
   uint64_t o_full;           // everything accumulated
   uint32_t tmem_slot;
   int abort_flag;
@@ -105,21 +111,21 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
   const int nkv = args.n / BN;
   const int nsub = 2 * nkv;          // 64-row sub-tiles
 
-  if (warp == 8 && lane == 0) {
+  if (warp == WARP_TMA && lane == 0) {
     mbar_init(&misc->bar_q, 1);
     for (int i = 0; i < KS; ++i) { mbar_init(&misc->k_full[i], 1); mbar_init(&misc->k_empty[i], 1); }
-    for (int i = 0; i < VS; ++i) { mbar_init(&misc->v_full[i], 1); mbar_init(&misc->v_empty[i], 1); }
+    for (int i = 0; i < VS; ++i) { mbar_init(&misc->v_full[i], 1); mbar_init(&misc->v_empty[i], 2); }
     for (int b = 0; b < 2; ++b) {
       for (int u = 0; u < 2; ++u) { mbar_init(&misc->s_full[b][u], 1); mbar_init(&misc->p_full[b][u], 128); }
-      mbar_init(&misc->o_done[b], 1);
+      for (int u = 0; u < 2; ++u) mbar_init(&misc->pv_done[b][u], 1);
     }
-    mbar_init(&misc->o_full, 1);
+    mbar_init(&misc->o_full, 2);
     misc->abort_flag = 0;
     mbar_init_fence();
     tma_prefetch_desc(&tm_q1); tma_prefetch_desc(&tm_q2); tma_prefetch_desc(&tm_k1);
     tma_prefetch_desc(&tm_k2); tma_prefetch_desc(&tm_v);
   }
-  if (warp == 9) {
+  if (warp == WARP_S) {
     tmem_alloc(&misc->tmem_slot, 512);
   }
   tc_fence_before();
@@ -127,7 +133,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&misc->tmem_slot);
 
-  if (warp == 8) {
+  if (warp == WARP_TMA) {
     // ------------------------------- TMA producer -------------------------------
     if (elect_one()) {
       mbar_expect_tx(&misc->bar_q, 2 * Q_BYTES);
@@ -145,103 +151,70 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
         tma_load_4d(smem + OFF_V + vs * V_BYTES + V_BYTES / 2, &tm_v, &misc->v_full[vs], 64, j * BN, h_idx, b_idx);
       }
     }
-  } else if (warp == 9) {
-    // -------------------------------- MMA issuer --------------------------------
+  } else if (warp == WARP_S) {
+    // ------------------- S issuer: S_b(t) = Q_b K_b(sub-tile t)^T for both branches -------------------
     // One thread, chosen by elect.sync, runs the whole loop.  (A thread picked by comparing the lane id
     // issues tcgen05.mma about three times slower: 152 against 48 clocks per instruction, measured.)
-    // Each K/V tile of 128 rows is two sub-tiles of 64; S_b of the next sub-tile is issued before the
-    // wait for P_b of the current one, so the softmax warpgroups always find their next scores ready.
-    // The loop body is kept to a few integer instructions per MMA: this thread shares its scheduler with
-    // two busy softmax warps.
+    // Sub-tile t goes to buffer t & 1, which is free once P_b V of sub-tile t-2 has completed, so the
+    // scores of the next sub-tile are ready while the softmax warpgroups work on the current one.
     if (elect_one()) {
-      constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0);   // S = Q K^T, both K-major
-      constexpr uint32_t IDESC_O = make_idesc(BM, DV, 0, 1);    // O += P V, V is MN-major
+      constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0);   // both operands K-major
       constexpr uint32_t HALF = (SUB * 128) >> 4;               // 64 rows of 128 bytes, in descriptor units
       const uint32_t q1_lo = sdesc_lo(smem_u32(smem + OFF_Q1)), q2_lo = sdesc_lo(smem_u32(smem + OFF_Q2));
       const uint32_t k_lo0 = sdesc_lo(smem_u32(smem + OFF_K));
-      const uint32_t v_lo0 = sdesc_lo(smem_u32(smem + OFF_V), V_BYTES / 2);
-      const uint32_t t_s1 = tmem_base, t_s2 = tmem_base + 128, t_o1 = tmem_base + T_O, t_o2 = tmem_base + T_O + 128;
-      // S_b(buffer u) = Q_b K_b(tile at k_lo, half u)^T
-      auto issue_s = [&](uint32_t k_lo, int u) {
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
-          mma_ss_lo(t_s1 + u * SUB, q1_lo + k * 2, k_lo + u * HALF + k * 2, IDESC_S, k > 0);
-        mma_commit(&misc->s_full[0][u]);
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
-          mma_ss_lo(t_s2 + u * SUB, q2_lo + k * 2, k_lo + (K_BYTES >> 4) + u * HALF + k * 2, IDESC_S, k > 0);
-        mma_commit(&misc->s_full[1][u]);
-      };
-      // O_b += P_b(buffer u) V(tile at v_lo, half u)
-      auto issue_pv = [&](int br, uint32_t v_lo, int u, uint32_t first) {
-        const uint32_t t_o = br ? t_o2 : t_o1, t_p = (br ? t_s2 : t_s1) + u * SUB;
-#pragma unroll
-        for (int k = 0; k < SUB / 16; ++k)
-          mma_ts_lo(t_o, t_p + k * 8, v_lo + u * HALF + k * (2048 >> 4), IDESC_O, k > 0 ? 1u : first);
-        mma_commit(&misc->o_done[br]);
-      };
       bool ok = mbar_wait(&misc->bar_q, 0, abort_flag, 201);
-      ok = ok && mbar_wait(&misc->k_full[0], 0, abort_flag, 202);
-      if (ok) {
-        tc_fence_after();
-        int ks = 0, vs = 0;
-        uint32_t k_par = 0, v_par = 0;
-        issue_s(k_lo0, 0);
-        for (int j = 0; j < nkv; ++j) {
-          const uint32_t k_lo = k_lo0 + ks * ((2 * K_BYTES) >> 4);
-          const uint32_t v_lo = v_lo0 + vs * (V_BYTES >> 4);
-          const uint32_t ph = j & 1;
-#ifdef DA_TIMING
-          const bool tm_on = (blockIdx.x == 3 && blockIdx.y == 1) && j >= 8 && j < 16;
-          const int tm_base = 512 + (j - 8) * 16;
-#endif
-          DA_TS(0);
-          // ---- sub-tile 2j (buffer 0): first issue the scores of sub-tile 2j+1 (same K tile, upper half)
-          issue_s(k_lo, 1);
-          DA_TS(1);
-          mma_commit(&misc->k_empty[ks]);
-          if (!mbar_wait(&misc->v_full[vs], v_par, abort_flag, 203, j)) break;
-#ifndef DA_NOPWAIT
-          if (!mbar_wait(&misc->p_full[0][0], ph, abort_flag, 204, j)) break;
-#endif
-          tc_fence_after();
-          DA_TS(2);
-          issue_pv(0, v_lo, 0, j > 0);
-          DA_TS(3);
-#ifndef DA_NOPWAIT
-          if (!mbar_wait(&misc->p_full[1][0], ph, abort_flag, 206, j)) break;
-#endif
-          tc_fence_after();
-          DA_TS(4);
-          issue_pv(1, v_lo, 0, j > 0);
-          DA_TS(5);
-          // ---- sub-tile 2j+1 (buffer 1): first issue the scores of sub-tile 2j+2 (next K tile, lower half)
-          if (++ks == KS) { ks = 0; k_par ^= 1; }
-          if (j + 1 < nkv) {
-            if (!mbar_wait(&misc->k_full[ks], k_par, abort_flag, 205, j)) break;
+      int ks = 0;
+      uint32_t k_par = 0;
+      for (int j = 0; ok && j < nkv; ++j) {
+        const uint32_t k_lo = k_lo0 + ks * ((2 * K_BYTES) >> 4);
+        if (!mbar_wait(&misc->k_full[ks], k_par, abort_flag, 202, j)) break;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+#pragma unroll
+          for (int br = 0; br < 2; ++br) {
+            if (j > 0) {
+              if (!mbar_wait(&misc->pv_done[br][u], (j - 1) & 1, abort_flag, 203 + u, j)) { ok = false; break; }
+            }
             tc_fence_after();
-            issue_s(k_lo0 + ks * ((2 * K_BYTES) >> 4), 0);
+#pragma unroll
+            for (int k = 0; k < HD / 16; ++k)
+              mma_ss_lo(tmem_base + br * 128 + u * SUB, (br ? q2_lo : q1_lo) + k * 2,
+                        k_lo + br * (K_BYTES >> 4) + u * HALF + k * 2, IDESC_S, k > 0);
+            mma_commit(&misc->s_full[br][u]);
           }
-          DA_TS(6);
-#ifndef DA_NOPWAIT
-          if (!mbar_wait(&misc->p_full[0][1], ph, abort_flag, 207, j)) break;
-#endif
-          tc_fence_after();
-          DA_TS(7);
-          issue_pv(0, v_lo, 1, 1);
-          DA_TS(8);
-#ifndef DA_NOPWAIT
-          if (!mbar_wait(&misc->p_full[1][1], ph, abort_flag, 208, j)) break;
-#endif
-          tc_fence_after();
-          DA_TS(9);
-          issue_pv(1, v_lo, 1, 1);
-          DA_TS(10);
-          mma_commit(&misc->v_empty[vs]);
-          if (++vs == VS) { vs = 0; v_par ^= 1; }
+          if (!ok) break;
         }
-        mma_commit(&misc->o_full);
+        mma_commit(&misc->k_empty[ks]);
+        if (++ks == KS) { ks = 0; k_par ^= 1; }
       }
+    }
+  } else if (warp == WARP_PV || warp == WARP_PV + 1) {
+    // ------------------- P V issuer of one branch: O_b += P_b(t) V(sub-tile t) -------------------
+    if (elect_one()) {
+      const int br = warp - WARP_PV;
+      constexpr uint32_t IDESC_O = make_idesc(BM, DV, 0, 1);    // V is MN-major
+      constexpr uint32_t HALF = (SUB * 128) >> 4;
+      const uint32_t v_lo0 = sdesc_lo(smem_u32(smem + OFF_V), V_BYTES / 2);
+      const uint32_t t_o = tmem_base + T_O + br * 128, t_p = tmem_base + br * 128;
+      int vs = 0;
+      uint32_t v_par = 0;
+      bool ok = true;
+      for (int j = 0; ok && j < nkv; ++j) {
+        const uint32_t v_lo = v_lo0 + vs * (V_BYTES >> 4);
+        if (!mbar_wait(&misc->v_full[vs], v_par, abort_flag, 205, j)) break;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (!mbar_wait(&misc->p_full[br][u], j & 1, abort_flag, 206 + u, j)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < SUB / 16; ++k)
+            mma_ts_lo(t_o, t_p + u * SUB + k * 8, v_lo + u * HALF + k * (2048 >> 4), IDESC_O, (j > 0 || u > 0 || k > 0));
+          mma_commit(&misc->pv_done[br][u]);
+        }
+        mma_commit(&misc->v_empty[vs]);
+        if (++vs == VS) { vs = 0; v_par ^= 1; }
+      }
+      mma_commit(&misc->o_full);
     }
   } else {
     // ------------------------- softmax warpgroups + epilogue -------------------------
@@ -324,7 +297,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
       if (__any_sync(0xffffffffu, need)) {
         if (t > 0) {
           // O_b must be quiescent: wait for P_b V of the previous sub-tile, then rescale it
-          if (!mbar_wait(&misc->o_done[br], (t - 1) & 1, abort_flag, 305 + br, t)) { ok = false; break; }
+          if (!mbar_wait(&misc->pv_done[br][(t - 1) & 1], ((t - 1) >> 1) & 1, abort_flag, 305 + br, t)) { ok = false; break; }
           tc_fence_after();
           const float scale = need ? ex2((m_run - m_new) * sl2) : 1.f;
           l_run *= scale;
@@ -429,7 +402,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == WARP_S) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
