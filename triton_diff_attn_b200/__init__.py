@@ -2,7 +2,8 @@
 (TMA + tcgen05 + TMEM) behind the C ABI of include/diffattn.h.  Importing this package loads
 libdiffattn.so and raises if it has not been built; there is no fallback path."""
 from .layers import DiffAttnFunction, MultiheadDiffAttnKernel, device_status  # noqa: F401
+from .host_pipeline import HostStepPipeline  # noqa: F401
 from .shard import shard_range, shard_batch, sum_dlambda_on_host  # noqa: F401
 
 __all__ = ["MultiheadDiffAttnKernel", "DiffAttnFunction", "device_status", "shard_range", "shard_batch",
-           "sum_dlambda_on_host"]
+           "sum_dlambda_on_host", "HostStepPipeline"]
