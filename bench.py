@@ -157,12 +157,59 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def run_flash_composition(args):
+    """Informational same-box LIBRARY baseline, not the product and not the reference arm: differential
+    attention composed from four FlashAttention-2 calls (each branch against the two halves of V), the
+    construction the reference compares its kernel with (reference src/layers.py:104-148), written here
+    against the flash_attn package of this image, RMSNorm in plain torch ops.  One GPU only."""
+    import math
+    from flash_attn import flash_attn_func
+    b, h, n, d, scale, lam, lam_init, rms = WORKLOADS[args.workload]
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(1234)
+    def draw(*shape):
+        return (torch.randn(*shape, generator=g, device=dev, dtype=torch.float32) * scale).to(torch.float16).requires_grad_(True)
+    # flash_attn wants [B, N, H, D]
+    q1, q2, k1, k2 = (draw(b, n, h, d) for _ in range(4))
+    v = draw(b, n, h, 2 * d)
+    dy = torch.randn(b, n, h, 2 * d, generator=g, device=dev, dtype=torch.float32).to(torch.float16)
+    lam_t = torch.tensor([lam], dtype=torch.float16, device=dev, requires_grad=True)
+
+    def step():
+        v1, v2 = v[..., :d], v[..., d:]
+        a1 = torch.cat([flash_attn_func(q1, k1, v1), flash_attn_func(q1, k1, v2)], dim=-1)
+        a2 = torch.cat([flash_attn_func(q2, k2, v1), flash_attn_func(q2, k2, v2)], dim=-1)
+        a = a1 - lam_t * a2
+        if rms:
+            a = (1.0 - lam_init) * a * torch.rsqrt((a.float() ** 2).mean(-1, keepdim=True) + 1e-5).to(a.dtype)
+        a.backward(dy)
+        for t in (q1, q2, k1, k2, v, lam_t):
+            t.grad = None
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    f, bk = flops(b, h, n, d)
+    print(json.dumps({"impl": "flash_composition", "metric": METRIC, "value": (f + bk) / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+                      "dtype": "fp16", "data": "synthetic",
+                      "config": {"workload": args.workload, "note": "library baseline: 4x flash_attn_func + torch ops; credited "
+                                 "flops as for the product (the composition executes S twice per branch)"}}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "flash_composition"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -171,6 +218,9 @@ def main():
 
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.impl == "flash_composition":
+        run_flash_composition(args)
         return
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
