@@ -23,7 +23,7 @@ struct BwdArgs {
   const float* lse2;
   const float* rstd;
   __half* da;           // workspace [B*H, N, 2D]
-  float4* stats;        // workspace [B*H, N] = {lse1*log2e, lse2*log2e, E1, E2}
+  float4* stats;        // workspace [B*H, N] = {lse1*log2e, lse2*log2e - log2|lam|, E1, sg*E2}, sg = -sign(lam)
   __half* dq1; __half* dq2; __half* dk1; __half* dk2; __half* dv;   // dense
   float* dlambda;
   const void* lambda_ptr;
@@ -109,8 +109,11 @@ __global__ void __launch_bounds__(256) diffattn_bwd_pre_kernel(const BwdArgs arg
     else if constexpr (VPL == 4) *reinterpret_cast<uint2*>(args.da + off) = *reinterpret_cast<uint2*>(hda);
     else *reinterpret_cast<uint32_t*>(args.da + off) = *reinterpret_cast<uint32_t*>(hda);
     if (lane == 0) {
-      // E1 - lam E2 = rowsum(dA * A)
-      args.stats[row] = make_float4(args.lse1[row] * LOG2E, args.lse2[row] * LOG2E, ea + lam * e2, e2);
+      // E1 - lam E2 = rowsum(dA * A).  lambda is folded into the branch-2 statistics so that the tensor-core
+      // kernels need no multiply for it: with P2' = |lam| P2 = 2^(s S2 log2e - y) and sg = -sign(lam),
+      // -lam P2 = sg P2' and -lam P2 (dP - E2) = P2' (sg dP - w).  lam = 0 gives y = +inf, P2' = 0.
+      const float sg = lam < 0.f ? 1.f : -1.f;
+      args.stats[row] = make_float4(args.lse1[row] * LOG2E, args.lse2[row] * LOG2E - log2f(fabsf(lam)), ea + lam * e2, sg * e2);
       dl_acc -= e2;
     }
   }
@@ -297,7 +300,7 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
     const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
     const uint32_t tb = tmem_base + lane_base;
     const float sl2 = args.sm_scale * 1.4426950408889634f;
-    const float lam = load_lambda(args.lambda_ptr, args.lambda_dtype);
+    const float sg = load_lambda(args.lambda_ptr, args.lambda_dtype) < 0.f ? 1.f : -1.f;   // -sign(lambda)
     bool ok = true;
     for (int i = 0; i < nq; ++i) {
       const int st = i % ST;
@@ -327,11 +330,11 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
           const int j = 2 * jj + u;
           const float4 sv = stats[j];
           const float p1 = ex2(fmaf(__uint_as_float(s1[j]), sl2, -sv.x));
-          const float p2l = -lam * ex2(fmaf(__uint_as_float(s2[j]), sl2, -sv.y));
+          const float p2 = ex2(fmaf(__uint_as_float(s2[j]), sl2, -sv.y));     // |lam| P2
           const float dpv = __uint_as_float(dp[j]);
-          pcv[u] = p1 + p2l;
+          pcv[u] = fmaf(sg, p2, p1);
           d1v[u] = p1 * (dpv - sv.z);
-          d2v[u] = p2l * (dpv - sv.w);
+          d2v[u] = p2 * fmaf(sg, dpv, -sv.w);
         }
         pc[jj] = pack_half2(pcv[0], pcv[1]);
         d1[jj] = pack_half2(d1v[0], d1v[1]);
@@ -574,7 +577,7 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
     const float4 sv = args.stats[grow];
     const float neg_l = br ? -sv.y : -sv.x;
     const float e = br ? sv.w : sv.z;
-    const float coef = br ? -lam : 1.f;
+    const float sg = (br && !(lam < 0.f)) ? -1.f : 1.f;      // branch 2: -sign(lambda) (|lambda| sits in neg_l, the sign in e)
     bool ok = true;
     for (int t = 0; t < nsub; ++t) {
       const int u = t & 1;
@@ -596,9 +599,9 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
       DA_TS(2);
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const float p0 = coef * ex2(fmaf(__uint_as_float(s[2 * i]), sl2, neg_l));
-        const float p1 = coef * ex2(fmaf(__uint_as_float(s[2 * i + 1]), sl2, neg_l));
-        s[i] = pack_half2(p0 * (__uint_as_float(dp[2 * i]) - e), p1 * (__uint_as_float(dp[2 * i + 1]) - e));
+        const float p0 = ex2(fmaf(__uint_as_float(s[2 * i]), sl2, neg_l));
+        const float p1 = ex2(fmaf(__uint_as_float(s[2 * i + 1]), sl2, neg_l));
+        s[i] = pack_half2(p0 * fmaf(sg, __uint_as_float(dp[2 * i]), -e), p1 * fmaf(sg, __uint_as_float(dp[2 * i + 1]), -e));
       }
       DA_TS(3);
       tmem_st16(t_s, s);

@@ -150,7 +150,7 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
     const uint32_t tb = tmem_base + lane_base;
     const float sl2 = args.sm_scale * 1.4426950408889634f;
     const float lam = load_lambda(args.lambda_ptr, args.lambda_dtype);
-    const float coef = br ? -lam : 1.f;
+    const float sg = (br && !(lam < 0.f)) ? -1.f : 1.f;      // branch 2: -sign(lambda); |lambda| is in the statistics
     const size_t grow = size_t(bh) * args.n + size_t(tile) * BM + row;
     float neg_l = 0.f, e = 0.f;
     if (QSIDE) {
@@ -182,8 +182,8 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
             nl = br ? -sv.y : -sv.x;
             ee = br ? sv.w : sv.z;
           }
-          const float p = coef * ex2(fmaf(__uint_as_float(s[j]), sl2, nl));
-          v[w] = p * (__uint_as_float(tt[j]) - ee);
+          const float p = ex2(fmaf(__uint_as_float(s[j]), sl2, nl));
+          v[w] = p * fmaf(sg, __uint_as_float(tt[j]), -ee);
         }
         ds[i] = pack_half2(v[0], v[1]);
       }
@@ -360,7 +360,7 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
     const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
     const uint32_t tb = tmem_base + lane_base;
     const float sl2 = args.sm_scale * 1.4426950408889634f;
-    const float lam = load_lambda(args.lambda_ptr, args.lambda_dtype);
+    const float sg = load_lambda(args.lambda_ptr, args.lambda_dtype) < 0.f ? 1.f : -1.f;   // -sign(lambda)
     bool ok = true;
     int st = 0;
     for (int i = 0; i < nq; ++i) {
@@ -379,7 +379,7 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
         for (int w = 0; w < 2; ++w) {
           const int j = 2 * jj + w;
           const float4 sv = stats[j];
-          v[w] = ex2(fmaf(__uint_as_float(s1[j]), sl2, -sv.x)) - lam * ex2(fmaf(__uint_as_float(s2[j]), sl2, -sv.y));
+          v[w] = fmaf(sg, ex2(fmaf(__uint_as_float(s2[j]), sl2, -sv.y)), ex2(fmaf(__uint_as_float(s1[j]), sl2, -sv.x)));
         }
         pc[jj] = pack_half2(v[0], v[1]);
       }
