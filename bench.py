@@ -157,6 +157,47 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def run_reference_protocol_sweep(args):
+    """The reference's runtime benchmark protocol (src/benchmark.py:19-25,83-148): H=16, D=32 (v width 64), fp16,
+    forward and forward+backward, rms_norm on, N in {512,...,16384} with batch 16384/N; median of per-call CUDA-event
+    times (the reference reports do_bench medians).  One JSON line per N; one GPU."""
+    from triton_diff_attn_b200 import MultiheadDiffAttnKernel
+    dev = torch.device("cuda", 0)
+    h, d = 16, 32
+    for n in (512, 1024, 2048, 4096, 8192, 16384):
+        b = 16384 // n
+        g = torch.Generator(device=dev).manual_seed(n)
+        def draw(*shape):
+            return (torch.randn(*shape, generator=g, device=dev, dtype=torch.float32) * 0.5).to(torch.float16).requires_grad_(True)
+        q1, q2, k1, k2 = (draw(b, h, n, d) for _ in range(4))
+        v = draw(b, h, n, 2 * d)
+        dy = torch.rand(b, h, n, 2 * d, generator=g, device=dev, dtype=torch.float32).to(torch.float16)
+        lam = torch.tensor([0.5], dtype=torch.float16, device=dev, requires_grad=True)
+
+        def fwd_only():
+            return MultiheadDiffAttnKernel(q1, q2, k1, k2, v, lam, 0.8, True)
+
+        def fwd_bwd():
+            fwd_only().backward(dy)
+            for t in (q1, q2, k1, k2, v, lam):
+                t.grad = None
+
+        res = {}
+        for name, fn in (("fwd", fwd_only), ("fwd_bwd", fwd_bwd)):
+            for _ in range(max(args.warmup, 3)):
+                fn()
+            times = []
+            for _ in range(max(args.steps, 10)):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(); fn(); e1.record(); torch.cuda.synchronize()
+                times.append(e0.elapsed_time(e1))
+            res[name] = statistics.median(times)
+        f, bk = flops(b, h, n, d)
+        print(json.dumps({"protocol": "reference src/benchmark.py:19-25", "B": b, "H": h, "N": n, "D": d,
+                          "fwd_ms_median": res["fwd"], "fwd_bwd_ms_median": res["fwd_bwd"],
+                          "fwd_tflops": f / (res["fwd"] * 1e-3) / 1e12, "fwd_bwd_tflops": (f + bk) / (res["fwd_bwd"] * 1e-3) / 1e12}))
+
+
 def run_flash_composition(args):
     """Informational same-box LIBRARY baseline, not the product and not the reference arm: differential
     attention composed from four FlashAttention-2 calls (each branch against the two halves of V), the
@@ -213,6 +254,9 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--sweep-reference-protocol", action="store_true",
+                    help="instead of the one-line benchmark: the reference's own sweep (src/benchmark.py:19-25): "
+                         "H=16, D=32, fp16, rms_norm, N in 512..16384 with B = 16384/N; one JSON line per N")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -221,6 +265,9 @@ def main():
         return
     if args.impl == "flash_composition":
         run_flash_composition(args)
+        return
+    if args.sweep_reference_protocol:
+        run_reference_protocol_sweep(args)
         return
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
