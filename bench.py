@@ -154,7 +154,7 @@ def run_reference(args):
         "e2e": {"value": r["tflops"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 def run_reference_protocol_sweep(args):
@@ -193,9 +193,9 @@ def run_reference_protocol_sweep(args):
                 times.append(e0.elapsed_time(e1))
             res[name] = statistics.median(times)
         f, bk = flops(b, h, n, d)
-        print(json.dumps({"protocol": "reference src/benchmark.py:19-25", "B": b, "H": h, "N": n, "D": d,
+        emit({"protocol": "reference src/benchmark.py:19-25", "B": b, "H": h, "N": n, "D": d,
                           "fwd_ms_median": res["fwd"], "fwd_bwd_ms_median": res["fwd_bwd"],
-                          "fwd_tflops": f / (res["fwd"] * 1e-3) / 1e12, "fwd_bwd_tflops": (f + bk) / (res["fwd_bwd"] * 1e-3) / 1e12}))
+                          "fwd_tflops": f / (res["fwd"] * 1e-3) / 1e12, "fwd_bwd_tflops": (f + bk) / (res["fwd_bwd"] * 1e-3) / 1e12})
 
 
 def run_flash_composition(args):
@@ -238,14 +238,34 @@ def run_flash_composition(args):
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
     f, bk = flops(b, h, n, d)
-    print(json.dumps({"impl": "flash_composition", "metric": METRIC, "value": (f + bk) / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+    emit({"impl": "flash_composition", "metric": METRIC, "value": (f + bk) / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                       "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
                       "dtype": "fp16", "data": "synthetic",
                       "config": {"workload": args.workload, "note": "library baseline: 4x flash_attn_func + torch ops; credited "
-                                 "flops as for the product (the composition executes S twice per branch)"}}))
+                                 "flops as for the product (the composition executes S twice per branch)"}})
+
+
+_REAL_STDOUT = None
+
+
+def _quiet_stdout():
+    """Send everything libraries print on file descriptor 1 (NCCL's version banner, for one) to stderr and
+    keep the real stdout for the result lines, so that a run prints exactly one JSON line there."""
+    global _REAL_STDOUT
+    if _REAL_STDOUT is None:
+        sys.stdout.flush()
+        _REAL_STDOUT = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(obj):
+    data = (json.dumps(obj) + "\n").encode()
+    sys.stdout.flush()
+    os.write(_REAL_STDOUT if _REAL_STDOUT is not None else 1, data)
 
 
 def main():
+    _quiet_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
@@ -442,7 +462,7 @@ def main():
         c = cpu_sample(args.workload, heads=2, steps=3, warmup=1)
         line["cpu_baseline"] = {"value": c["tflops"], "unit": "TFLOP/s", "cores": c["cores"], "kind": "port",
                                 "sample": c["sample"], "ms_per_sample": c["ms_per_step"]}
-    print(json.dumps(line))
+    emit(line)
     if world > 1:
         dist.destroy_process_group()
 
