@@ -118,8 +118,8 @@ def cpu_sample(workload, heads, steps, warmup, threads=None):
     """Times the oracle's forward + autograd backward (CPU fp32) on `heads` heads of the workload."""
     from oracle import diffattn_oracle as oracle
     b, h, n, d, scale, lam, lam_init, rms = WORKLOADS[workload]
-    if threads:
-        torch.set_num_threads(threads)
+    # all host cores, also under torchrun (which exports OMP_NUM_THREADS=1 to every rank)
+    torch.set_num_threads(threads or os.cpu_count() or 1)
     q1, q2, k1, k2, v, dy = oracle.make_inputs(1, heads, n, d, seed=4321, scale=scale)
     lam_t = torch.tensor([lam])
     times = []
