@@ -84,6 +84,27 @@ def test_fwd_bwd_matches_oracle(op, b, h, n, d, scale, lam, lam_init, rms, seed)
     check(got, want)
 
 
+@pytest.mark.parametrize("d", [64, 128])
+def test_growing_row_maximum_exercises_rescale(op, d):
+    """Keys whose magnitude grows along the sequence make the running row maximum jump by far more than
+    2^8 several times, so the forward's rescale-and-redo path (O and l rescaled, probabilities recomputed)
+    runs repeatedly; results must still match the oracle, logsumexp included."""
+    b, h, n = 1, 2, 1024
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(b, h, n, d, 51)
+    ramp = torch.linspace(0.2, 6.0, n).view(1, 1, n, 1)
+    k1 = (k1.float() * ramp).to(torch.float16)
+    k2 = (k2.float() * ramp.flip(2)).to(torch.float16)      # branch 2: the large keys come first
+    want = oracle.backward_closed_form(q1, q2, k1, k2, v, torch.tensor([0.5]), dy, 0.8, True)
+    got = run_gpu(op, q1, q2, k1, k2, v, dy, 0.5, 0.8, True)
+    check(got, want)
+    dev = torch.device("cuda", 0)
+    leaves = [t.to(dev).requires_grad_(True) for t in (q1, q2, k1, k2, v)]
+    y = op.MultiheadDiffAttnKernel(*leaves, torch.tensor([0.5], device=dev, requires_grad=True), 0.8, True)
+    lse1, lse2 = (t.cpu() for t in y.grad_fn.saved_tensors[8:10])
+    assert torch.allclose(lse1, want["lse1"], atol=5e-3, rtol=1e-5)
+    assert torch.allclose(lse2, want["lse2"], atol=5e-3, rtol=1e-5)
+
+
 def test_saved_statistics(op):
     """lse1/lse2/rstd/a2 written by the forward equal the oracle's."""
     q1, q2, k1, k2, v, dy = oracle.make_inputs(1, 2, 256, 64, 21)
