@@ -25,7 +25,7 @@ enum {
   DIFFATTN_OK = 0,
   DIFFATTN_ERR_NULL_PTR = -1,
   DIFFATTN_ERR_BAD_STRUCT = -2,     /* struct_size does not match this library */
-  DIFFATTN_ERR_BAD_SHAPE = -3,      /* negative sizes, N not a multiple of 128 */
+  DIFFATTN_ERR_BAD_SHAPE = -3,      /* negative sizes, B*H beyond the grid limit */
   DIFFATTN_ERR_UNSUPPORTED_D = -4,  /* head dim not compiled in */
   DIFFATTN_ERR_BAD_STRIDE = -5,     /* strides not a multiple of 8 elements (16 bytes) */
   DIFFATTN_ERR_MISALIGNED = -6,     /* base pointer not 16-byte aligned */

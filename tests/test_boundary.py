@@ -58,7 +58,6 @@ def test_null_and_struct(L):
 
 
 @pytest.mark.parametrize("mutate,code", [
-    (lambda p: setattr(p, "N", 100), -3),
     (lambda p: setattr(p, "N", -128), -3),
     (lambda p: setattr(p, "D", 48), -4),
     (lambda p: setattr(p, "qk_stride_n", 60), -5),
@@ -85,6 +84,8 @@ def test_bwd_rejects_missing_workspace_and_grads(L):
     need = L.lib.diffattn_workspace_bytes(p)
     rows = 2 * 2 * 256
     assert need == rows * 128 * 2 + rows * 16
+    q = _good(L, n=200)      # ragged length: the statistics rows are padded to a multiple of 128 per (batch, head)
+    assert L.lib.diffattn_workspace_bytes(q) == 2 * 2 * 200 * 128 * 2 + 2 * 2 * 256 * 16
     p.workspace, p.workspace_bytes = 0x10010, need
     assert L.lib.diffattn_bwd_stages(p, L.STAGE_PRE) == -6   # workspace not 256-byte aligned
     p.workspace, p.workspace_bytes = 0x10100, need - 1

@@ -34,6 +34,8 @@ struct BwdArgs {
   int n;
   int h;
   int d;                // real head dim (64, or 32 with zero-filled padding in the 64-wide tiles)
+  int n_pad;            // N rounded up to 128: row pitch of `stats` per (batch, head); rows N..n_pad-1 hold
+                        // {+inf, +inf, 0, 0}, which makes the probabilities of out-of-range query rows exactly 0
   long long rows;       // B*H*N
 };
 
@@ -113,7 +115,8 @@ __global__ void __launch_bounds__(256) diffattn_bwd_pre_kernel(const BwdArgs arg
       // kernels need no multiply for it: with P2' = |lam| P2 = 2^(s S2 log2e - y) and sg = -sign(lam),
       // -lam P2 = sg P2' and -lam P2 (dP - E2) = P2' (sg dP - w).  lam = 0 gives y = +inf, P2' = 0.
       const float sg = lam < 0.f ? 1.f : -1.f;
-      args.stats[row] = make_float4(args.lse1[row] * LOG2E, args.lse2[row] * LOG2E - log2f(fabsf(lam)), ea + lam * e2, sg * e2);
+      const long long bh_i = row / args.n;
+      args.stats[bh_i * args.n_pad + (row - bh_i * args.n)] = make_float4(args.lse1[row] * LOG2E, args.lse2[row] * LOG2E - log2f(fabsf(lam)), ea + lam * e2, sg * e2);
       dl_acc -= e2;
     }
   }
@@ -123,6 +126,16 @@ __global__ void __launch_bounds__(256) diffattn_bwd_pre_kernel(const BwdArgs arg
     float s = 0.f;
     for (int i = 0; i < (blockDim.x >> 5); ++i) s += red[i];
     atomicAdd(args.dlambda, s);
+  }
+}
+
+// rows N..n_pad-1 of every (batch, head) in `stats`: neutral values (see BwdArgs::n_pad)
+__global__ void diffattn_bwd_padstats_kernel(const BwdArgs args, int bh_total) {
+  const int pad = args.n_pad - args.n;
+  const long long total = (long long)bh_total * pad;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long bh_i = i / pad;
+    args.stats[bh_i * args.n_pad + args.n + (i - bh_i * pad)] = make_float4(INFINITY, INFINITY, 0.f, 0.f);
   }
 }
 
@@ -180,7 +193,7 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kv_tile = blockIdx.x, bh = blockIdx.y;
   const int b_idx = bh / args.h, h_idx = bh % args.h;
-  const int nq = args.n / BQ;
+  const int nq = args.n_pad / BQ;      // the last query tiles may reach past N (zero dA, neutral statistics)
 
   if (warp == WARP_TMA && lane == 0) {
     mbar_init(&misc->bar_kv, 1);
@@ -215,7 +228,7 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
         tma_load_4d(sp + Q_BYTES, &tm_q2, &misc->full[st], 0, i * BQ, h_idx, b_idx);
         tma_load_4d(sp + 2 * Q_BYTES, &tm_da, &misc->full[st], 0, i * BQ, bh, 0);
         tma_load_4d(sp + 2 * Q_BYTES + DA_BYTES / 2, &tm_da, &misc->full[st], 64, i * BQ, bh, 0);
-        bulk_load_1d(sp + 2 * Q_BYTES + DA_BYTES, args.stats + (size_t(bh) * args.n + size_t(i) * BQ), STAT_BYTES,
+        bulk_load_1d(sp + 2 * Q_BYTES + DA_BYTES, args.stats + (size_t(bh) * args.n_pad + size_t(i) * BQ), STAT_BYTES,
                      &misc->full[st]);
       }
     }
@@ -372,6 +385,7 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
     // warpgroup g reads accumulator columns [64g, 64g+64): g = 0,1 -> the two halves of dV, g = 2 -> dK1, g = 3 -> dK2
     uint32_t acc[64];
     const size_t grow = size_t(bh) * args.n + size_t(kv_tile) * BKV + row;
+    ok = ok && (kv_tile * BKV + row < args.n);          // key rows past the sequence end are dropped
     tmem_ld32(tb + g * 64, acc);
     tmem_ld32(tb + g * 64 + 32, acc + 32);
     tc_wait_ld();
@@ -448,7 +462,7 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_tile = blockIdx.x, bh = blockIdx.y;
   const int b_idx = bh / args.h, h_idx = bh % args.h;
-  const int nkv = args.n / BN;
+  const int nkv = args.n_pad / BN;
   const int nsub = 2 * nkv;
 
   if (warp == WARP_TMA && lane == 0) {
@@ -574,7 +588,7 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
     const float sl2 = args.sm_scale * 1.4426950408889634f;
     const float lam = load_lambda(args.lambda_ptr, args.lambda_dtype);
     const size_t grow = size_t(bh) * args.n + size_t(q_tile) * BM + row;
-    const float4 sv = args.stats[grow];
+    const float4 sv = args.stats[size_t(bh) * args.n_pad + size_t(q_tile) * BM + row];
     const float neg_l = br ? -sv.y : -sv.x;
     const float e = br ? sv.w : sv.z;
     const float sg = (br && !(lam < 0.f)) ? -1.f : 1.f;      // branch 2: -sign(lambda) (|lambda| sits in neg_l, the sign in e)
@@ -597,6 +611,13 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
       tmem_ld32(t_dp, dp);
       tc_wait_ld();
       DA_TS(2);
+      if (t * SUB + half * 32 + 32 > args.n) {
+        // key columns >= N: score -inf, probability 0
+        const int nv = args.n - (t * SUB + half * 32);
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i >= nv) s[i] = 0xff800000u;
+      }
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const float p0 = ex2(fmaf(__uint_as_float(s[2 * i]), sl2, neg_l));
@@ -615,7 +636,7 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
     uint32_t acc[32];
     tmem_ld32(tb + (br ? T_DQ2 : T_DQ1) + half * 32, acc);
     tc_wait_ld();
-    if (ok && !*abort_flag && half * 32 < args.d) {
+    if (ok && !*abort_flag && half * 32 < args.d && q_tile * BM + row < args.n) {
       const float sc = args.sm_scale;
       uint4* p = reinterpret_cast<uint4*>((br ? args.dq2 : args.dq1) + grow * args.d + half * 32);
 #pragma unroll

@@ -54,7 +54,7 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x, bh = blockIdx.y, br = blockIdx.z;
   const int b_idx = bh / args.h, h_idx = bh % args.h;
-  const int nsub = args.n / SUB;
+  const int nsub = args.n_pad / SUB;
   const CUtensorMap* tm_x = br ? &tm_x1 : &tm_x0;
   const CUtensorMap* tm_z = br ? &tm_z1 : &tm_z0;
   // dA is the Y operand on the query side and the W operand on the key side
@@ -89,7 +89,7 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
         for (int c = 0; c < 2; ++c) tma_load_4d(sp + c * 8192, tm_z, &misc->full[st], c * 64, t * SUB, h_idx, b_idx);
         for (int c = 0; c < 4; ++c) tma_load_4d(sp + Z_BYTES + c * 8192, &tm_w, &misc->full[st], c * 64, t * SUB, w_c2, w_c3);
         if (!QSIDE)
-          bulk_load_1d(sp + Z_BYTES + W_BYTES, args.stats + (size_t(bh) * args.n + size_t(t) * SUB), STAT_BYTES, &misc->full[st]);
+          bulk_load_1d(sp + Z_BYTES + W_BYTES, args.stats + (size_t(bh) * args.n_pad + size_t(t) * SUB), STAT_BYTES, &misc->full[st]);
         if (++st == ST) { st = 0; par ^= 1; }
       }
     }
@@ -154,7 +154,7 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
     const size_t grow = size_t(bh) * args.n + size_t(tile) * BM + row;
     float neg_l = 0.f, e = 0.f;
     if (QSIDE) {
-      const float4 sv = args.stats[grow];
+      const float4 sv = args.stats[size_t(bh) * args.n_pad + size_t(tile) * BM + row];
       neg_l = br ? -sv.y : -sv.x;
       e = br ? sv.w : sv.z;
     }
@@ -170,6 +170,14 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
       tmem_ld16(t_s, s);
       tmem_ld16(t_t, tt);
       tc_wait_ld();
+      if (QSIDE && t * SUB + g * 16 + 16 > args.n) {
+        // query side: streamed columns are key rows; those >= N get probability 0.  (On the key side the
+        // streamed columns are query rows, whose padded statistics already give probability 0.)
+        const int nv = args.n - (t * SUB + g * 16);
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          if (i >= nv) s[i] = 0xff800000u;
+      }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         float v[2];
@@ -199,7 +207,7 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
     uint32_t acc[32];
     tmem_ld32(tb + T_OUT + g * 32, acc);
     tc_wait_ld();
-    if (ok && !*abort_flag) {
+    if (ok && !*abort_flag && tile * BM + row < args.n) {
       const float sc = args.sm_scale;
       __half* out = QSIDE ? (br ? args.dq2 : args.dq1) : (br ? args.dk2 : args.dk1);
       uint4* p = reinterpret_cast<uint4*>(out + grow * HD + g * 32);
@@ -263,7 +271,7 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kv_tile = blockIdx.x, bh = blockIdx.y;
   const int b_idx = bh / args.h, h_idx = bh % args.h;
-  const int nq = args.n / BQ;
+  const int nq = args.n_pad / BQ;
 
   if (warp == WARP_TMA && lane == 0) {
     mbar_init(&misc->bar_kv, 1);
@@ -299,7 +307,7 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
           tma_load_4d(sp + Q_BYTES + c * 8192, &tm_q2, &misc->full[st], c * 64, i * BQ, h_idx, b_idx);
         }
         for (int c = 0; c < 4; ++c) tma_load_4d(sp + 2 * Q_BYTES + c * 8192, &tm_da, &misc->full[st], c * 64, i * BQ, bh, 0);
-        bulk_load_1d(sp + 2 * Q_BYTES + DA_BYTES, args.stats + (size_t(bh) * args.n + size_t(i) * BQ), STAT_BYTES, &misc->full[st]);
+        bulk_load_1d(sp + 2 * Q_BYTES + DA_BYTES, args.stats + (size_t(bh) * args.n_pad + size_t(i) * BQ), STAT_BYTES, &misc->full[st]);
         if (++st == ST) { st = 0; par ^= 1; }
       }
     }
@@ -407,7 +415,7 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
     tmem_ld32(tb + T_DV + g * 64, acc);
     tmem_ld32(tb + T_DV + g * 64 + 32, acc + 32);
     tc_wait_ld();
-    if (ok && !*abort_flag) {
+    if (ok && !*abort_flag && kv_tile * BKV + row < args.n) {
       uint4* p = reinterpret_cast<uint4*>(args.dv + grow * DV + g * 64);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {

@@ -82,8 +82,6 @@ int check_common(const DiffAttnParams* p, bool bwd) {
     return fail(DIFFATTN_ERR_BAD_SHAPE, "negative size: B=%d H=%d N=%d D=%d", p->B, p->H, p->N, p->D);
   if (!diffattn_supports(p->D, bwd ? 1 : 0))
     return fail(DIFFATTN_ERR_UNSUPPORTED_D, "head dim %d is not compiled in (supported: 32, 64, 128)", p->D);
-  if (p->N % 128 != 0)
-    return fail(DIFFATTN_ERR_BAD_SHAPE, "N=%d must be a multiple of 128 (no masking, as the reference)", p->N);
   if (p->lambda_dtype != DIFFATTN_LAMBDA_F16 && p->lambda_dtype != DIFFATTN_LAMBDA_F32)
     return fail(DIFFATTN_ERR_BAD_DTYPE, "lambda_dtype %d unknown", p->lambda_dtype);
   if ((long long)p->B * p->H > 65535)
@@ -140,7 +138,9 @@ int diffattn_supports(int32_t d, int32_t dir) {
 uint64_t diffattn_workspace_bytes(const DiffAttnParams* p) {
   if (!p || p->B <= 0 || p->H <= 0 || p->N <= 0 || p->D <= 0) return 0;
   const uint64_t rows = uint64_t(p->B) * p->H * p->N;
-  return round256(rows * 2 * p->D * 2) + round256(rows * 16);   // dA fp16 + per-row {lse1', lse2', E1, E2}
+  const uint64_t n_pad = (uint64_t(p->N) + 127) & ~uint64_t(127);
+  // dA fp16 [B*H, N, 2D] + per-row statistics {lse1', lse2', E1, E2} with a row pitch of N rounded up to 128
+  return round256(rows * 2 * p->D * 2) + round256(uint64_t(p->B) * p->H * n_pad * 16);
 }
 
 int diffattn_fwd(const DiffAttnParams* p) {
@@ -166,13 +166,13 @@ int diffattn_fwd(const DiffAttnParams* p) {
   a.rms_norm = p->rms_norm; a.n = p->N; a.h = p->H; a.d = p->D;
   if (D == 128) {
     if ((rc = set_smem(da::diffattn_fwd128_kernel, da::fwd128::SMEM_BYTES))) return rc;
-    dim3 grid128(p->N / da::fwd128::BM, p->B * p->H);
+    dim3 grid128((p->N + 127) / 128, p->B * p->H);
     da::diffattn_fwd128_kernel<<<grid128, da::fwd128::NUM_THREADS, da::fwd128::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, a);
     DA_CUDA(cudaGetLastError());
     return DIFFATTN_OK;
   }
   if ((rc = set_smem(da::diffattn_fwd64_kernel, da::fwd64::SMEM_BYTES))) return rc;
-  dim3 grid(p->N / da::fwd64::BM, p->B * p->H);
+  dim3 grid((p->N + 127) / 128, p->B * p->H);
   da::diffattn_fwd64_kernel<<<grid, da::fwd64::NUM_THREADS, da::fwd64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, a);
   DA_CUDA(cudaGetLastError());
   return DIFFATTN_OK;
@@ -203,6 +203,8 @@ int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages) {
   a.lambda_ptr = p->lambda_scale; a.lambda_dtype = p->lambda_dtype;
   a.sm_scale = p->sm_scale; a.out_scale = 1.f - p->lambda_init; a.rms_norm = p->rms_norm;
   a.n = p->N; a.h = p->H; a.d = p->D; a.rows = (long long)rows;
+  a.n_pad = (p->N + 127) & ~127;
+  const int n_tiles = a.n_pad / 128;
 
   // 1. preprocess (grid-stride; one atomic per CTA for d(lambda))
   if (stages & DIFFATTN_STAGE_PRE) {
@@ -213,6 +215,7 @@ int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages) {
     if (D == 128) da::diffattn_bwd_pre_kernel<8><<<(unsigned)blocks, 256, 0, stream>>>(a);
     else if (D == 64) da::diffattn_bwd_pre_kernel<4><<<(unsigned)blocks, 256, 0, stream>>>(a);
     else da::diffattn_bwd_pre_kernel<2><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    if (a.n_pad != a.n) da::diffattn_bwd_padstats_kernel<<<64, 256, 0, stream>>>(a, (int)bh);
     DA_CUDA(cudaGetLastError());
   }
   if (D == 128) {
@@ -235,18 +238,18 @@ int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages) {
     if ((rc = make_map(&da_128, a.da, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 128, "dA"))) return rc;
     if (stages & DIFFATTN_STAGE_DKDV) {
       if ((rc = set_smem(da::diffattn_bwd_dv128_kernel, da::dv128::SMEM_BYTES))) return rc;
-      dim3 g1(p->N / 128, (unsigned)bh);
+      dim3 g1(n_tiles, (unsigned)bh);
       da::diffattn_bwd_dv128_kernel<<<g1, da::dv128::NUM_THREADS, da::dv128::SMEM_BYTES, stream>>>(q1_64, q2_64, k1_128, k2_128, da_64, a);
       DA_CUDA(cudaGetLastError());
       if ((rc = set_smem(da::diffattn_bwd_side128_kernel<false>, da::side128::SMEM_BYTES))) return rc;
-      dim3 g2(p->N / 128, (unsigned)bh, 2);
+      dim3 g2(n_tiles, (unsigned)bh, 2);
       da::diffattn_bwd_side128_kernel<false><<<g2, da::side128::NUM_THREADS, da::side128::SMEM_BYTES, stream>>>(
           k1_128, k2_128, v_128, q1_64, q2_64, da_64, a);
       DA_CUDA(cudaGetLastError());
     }
     if (stages & DIFFATTN_STAGE_DQ) {
       if ((rc = set_smem(da::diffattn_bwd_side128_kernel<true>, da::side128::SMEM_BYTES))) return rc;
-      dim3 g3(p->N / 128, (unsigned)bh, 2);
+      dim3 g3(n_tiles, (unsigned)bh, 2);
       da::diffattn_bwd_side128_kernel<true><<<g3, da::side128::NUM_THREADS, da::side128::SMEM_BYTES, stream>>>(
           q1_128, q2_128, da_128, k1_64, k2_64, v_64, a);
       DA_CUDA(cudaGetLastError());
@@ -263,7 +266,7 @@ int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages) {
   if ((rc = make_map(&mda, a.da, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 64, "dA"))) return rc;
   if ((rc = set_smem(da::diffattn_bwd_dkdv64_kernel, da::dkdv64::SMEM_BYTES))) return rc;
   if (stages & DIFFATTN_STAGE_DKDV) {
-    dim3 grid(p->N / da::dkdv64::BKV, (unsigned)bh);
+    dim3 grid(n_tiles, (unsigned)bh);
     da::diffattn_bwd_dkdv64_kernel<<<grid, da::dkdv64::NUM_THREADS, da::dkdv64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, mda, a);
     DA_CUDA(cudaGetLastError());
   }
@@ -273,7 +276,7 @@ int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages) {
   if ((rc = make_map(&mda, a.da, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 128, "dA"))) return rc;
   if ((rc = set_smem(da::diffattn_bwd_dq64_kernel, da::dq64::SMEM_BYTES))) return rc;
   if (stages & DIFFATTN_STAGE_DQ) {
-    dim3 grid(p->N / da::dq64::BM, (unsigned)bh);
+    dim3 grid(n_tiles, (unsigned)bh);
     da::diffattn_bwd_dq64_kernel<<<grid, da::dq64::NUM_THREADS, da::dq64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, mda, a);
     DA_CUDA(cudaGetLastError());
   }

@@ -108,7 +108,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
   const int bh = blockIdx.y;
   const int b_idx = bh / args.h;
   const int h_idx = bh % args.h;
-  const int nkv = args.n / BN;
+  const int nkv = (args.n + BN - 1) / BN;   // the last tile may reach past N: TMA fills those rows with zeros
   const int nsub = 2 * nkv;          // 64-row sub-tiles
 
   if (warp == WARP_TMA && lane == 0) {
@@ -253,6 +253,13 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
       tmem_ld32(t_s + 32, sr + 32);
       tc_wait_ld();
       DA_TS(2);
+      if ((t + 1) * SUB > args.n) {
+        // sub-tile reaches past the sequence end: key columns >= N get a score of -inf (probability 0)
+        const int nv = args.n - t * SUB;
+#pragma unroll
+        for (int i = 0; i < SUB; ++i)
+          if (i >= nv) sr[i] = 0xff800000u;
+      }
 #ifdef DA_LDSTONLY
       tmem_st32(t_s, sr + 32);
       tc_wait_st();
@@ -371,6 +378,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     const float rstd = rsqrtf((misc->ssq[0][row] + misc->ssq[1][row]) / float(dv_real) + args.eps);
     const float yscale = args.rms_norm ? args.out_scale * rstd : 1.f;
     const size_t grow = size_t(bh) * args.n + size_t(q_tile) * BM + row;
+    ok = ok && (q_tile * BM + row < args.n);            // rows past the sequence end are computed on zero padding and dropped
     if (ok && !*abort_flag && br * 64 < dv_real) {
       uint4* yp = reinterpret_cast<uint4*>(args.y + grow * dv_real + br * 64);
       uint4* ap = reinterpret_cast<uint4*>(args.a2 + grow * dv_real + br * 64);

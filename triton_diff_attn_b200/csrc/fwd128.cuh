@@ -51,7 +51,7 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_tile = blockIdx.x, bh = blockIdx.y;
   const int b_idx = bh / args.h, h_idx = bh % args.h;
-  const int nsub = args.n / SUB;
+  const int nsub = ((args.n + 127) / 128) * 2;     // 64-row sub-tiles, N rounded up to 128 (TMA zero-fills)
   const int ntot = 2 * nsub;          // sub-tiles over both passes
 
   if (warp == 8 && lane == 0) {
@@ -178,6 +178,12 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
         tmem_ld32(t_s + 0, sr);
         tmem_ld32(t_s + 32, sr + 32);
         tc_wait_ld();
+        if ((t + 1) * SUB > args.n) {
+          const int nv = args.n - t * SUB;       // key columns >= N: score -inf, probability 0
+#pragma unroll
+          for (int i = 0; i < SUB; ++i)
+            if (i >= nv) sr[i] = 0xff800000u;
+        }
         float neg = -m_run * sl2;
         float sum[4] = {0.f, 0.f, 0.f, 0.f};
         float mx[4];
@@ -265,7 +271,7 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
       tc_fence_before();
       named_bar_sync(1, 256);          // all O reads are complete here: the next pass may overwrite O
       ssq_total += misc->ssq[0][row] + misc->ssq[1][row];
-      const bool live = ok && !*abort_flag;
+      const bool live = ok && !*abort_flag && (q_tile * BM + row < args.n);
       const int col0 = pass * 128 + br * 64;
       if (live) {
         uint4* ap = reinterpret_cast<uint4*>(args.a2 + grow * DV + col0);

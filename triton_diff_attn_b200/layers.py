@@ -138,7 +138,8 @@ def MultiheadDiffAttnKernel(q1, q2, k1, k2, v, lambda_scale=-0.5, lambda_init: f
     CUDA tensor (the reference's float default cannot be loaded by its kernel either,
     src/layers.py:16 vs src/kernel.py:138).  Returns fp16 [B,H,N,2D].  The softmax scale is
     1/sqrt(D) (src/layers.py:20-22); (1 - lambda_init) is applied only with rms_norm
-    (src/layers.py:74-78).  N must be a multiple of 128 (no masking, README.md:2).
+    (src/layers.py:74-78).  Any sequence length N >= 1 is accepted (key columns past N are masked in the last
+    tile); the reference needs N to be a multiple of its block sizes (src/kernel.py:148,527).
     """
     return DiffAttnFunction.apply(q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm)
 
