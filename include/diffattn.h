@@ -55,7 +55,8 @@ typedef struct DiffAttnParams {
   float sm_scale;                  /* 1/sqrt(D) (src/layers.py:20-22) */
   float lambda_init;
   float eps;                       /* 1e-5 (src/kernel.py:50) */
-  int32_t reserved0;
+  int32_t causal;                  /* 0/1: 1 = key j is visible to query i only if j <= i (extension; the reference
+                                      has no masking, README.md:2) */
   /* forward outputs (inputs of the backward) */
   void* y; void* a2; float* lse1; float* lse2; float* rstd;
   /* backward */

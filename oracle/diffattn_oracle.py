@@ -39,7 +39,8 @@ def _lam(lambda_scale, dtype, device="cpu") -> torch.Tensor:
 
 
 def forward(q1, q2, k1, k2, v, lambda_scale, lambda_init: float = 0.8, rms_norm: bool = False,
-            dtype=torch.float32, round_p_half: bool = False, eps: float = EPS, device="cpu") -> Dict[str, torch.Tensor]:
+            dtype=torch.float32, round_p_half: bool = False, eps: float = EPS, device="cpu",
+            causal: bool = False) -> Dict[str, torch.Tensor]:
     """Forward pass; returns Y and the intermediates the backward kernels save (src/layers.py:60-80).
 
     Keys: y, a (pre-norm), a1, a2 (per-branch P_b V), lse1, lse2 (natural-log logsumexp of S_b,
@@ -55,6 +56,12 @@ def forward(q1, q2, k1, k2, v, lambda_scale, lambda_init: float = 0.8, rms_norm:
     s = 1.0 / math.sqrt(d)                                             # layers.py:60-62
     s1 = torch.matmul(q1, k1.transpose(2, 3)) * s                      # layers.py:64
     s2 = torch.matmul(q2, k2.transpose(2, 3)) * s                      # layers.py:67
+    if causal:
+        # extension (the reference has no masking, README.md:2): key j is visible to query i iff j <= i
+        n = s1.shape[-1]
+        hidden = torch.ones(n, n, dtype=torch.bool, device=s1.device).triu(1)
+        s1 = s1.masked_fill(hidden, float("-inf"))
+        s2 = s2.masked_fill(hidden, float("-inf"))
     lse1 = torch.logsumexp(s1, dim=-1)
     lse2 = torch.logsumexp(s2, dim=-1)
     p1 = torch.softmax(s1, dim=-1)                                     # layers.py:65
@@ -76,7 +83,7 @@ def forward(q1, q2, k1, k2, v, lambda_scale, lambda_init: float = 0.8, rms_norm:
 
 def backward_closed_form(q1, q2, k1, k2, v, lambda_scale, dy, lambda_init: float = 0.8,
                          rms_norm: bool = False, dtype=torch.float32,
-                         eps: float = EPS, device="cpu") -> Dict[str, torch.Tensor]:
+                         eps: float = EPS, device="cpu", causal: bool = False) -> Dict[str, torch.Tensor]:
     """Closed-form gradients (no autograd).  Same quantities the reference's backward kernel forms
     (src/kernel.py:283-299 preprocess, :410-436 main loop), with the division-free d(lambda).
 
@@ -88,7 +95,7 @@ def backward_closed_form(q1, q2, k1, k2, v, lambda_scale, dy, lambda_init: float
         dQ_b = s dS_b K_b,  dK_b = s dS_b^T Q_b                       (kernel.py:423-424,435-436)
         dlam = - sum E_2
     """
-    f = forward(q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, dtype=dtype, eps=eps, device=device)
+    f = forward(q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, dtype=dtype, eps=eps, device=device, causal=causal)
     q1, q2, k1, k2, v, dy = (t.detach().to(device, dtype) for t in (q1, q2, k1, k2, v, dy))
     lam = _lam(lambda_scale, dtype, device)
     d = q1.shape[-1]
@@ -117,7 +124,7 @@ def backward_closed_form(q1, q2, k1, k2, v, lambda_scale, dy, lambda_init: float
 
 def forward_backward_autograd(q1, q2, k1, k2, v, lambda_scale, dy, lambda_init: float = 0.8,
                               rms_norm: bool = False, dtype=torch.float32, round_p_half: bool = False,
-                              eps: float = EPS, num_threads: Optional[int] = None) -> Dict[str, torch.Tensor]:
+                              eps: float = EPS, num_threads: Optional[int] = None, causal: bool = False) -> Dict[str, torch.Tensor]:
     """Forward + autograd backward of the literal op sequence of src/layers.py:60-80.
 
     This is the independent check of `backward_closed_form` and the function the CPU baseline times.
@@ -129,8 +136,15 @@ def forward_backward_autograd(q1, q2, k1, k2, v, lambda_scale, dy, lambda_init: 
     lq1, lq2, lk1, lk2, lv = leaves
     d = lq1.shape[-1]
     s = 1.0 / math.sqrt(d)
-    p1 = torch.softmax(torch.matmul(lq1, lk1.transpose(2, 3)) * s, dim=-1)
-    p2 = torch.softmax(torch.matmul(lq2, lk2.transpose(2, 3)) * s, dim=-1)
+    sc1 = torch.matmul(lq1, lk1.transpose(2, 3)) * s
+    sc2 = torch.matmul(lq2, lk2.transpose(2, 3)) * s
+    if causal:
+        n = sc1.shape[-1]
+        hidden = torch.ones(n, n, dtype=torch.bool).triu(1)
+        sc1 = sc1.masked_fill(hidden, float("-inf"))
+        sc2 = sc2.masked_fill(hidden, float("-inf"))
+    p1 = torch.softmax(sc1, dim=-1)
+    p2 = torch.softmax(sc2, dim=-1)
     if round_p_half:
         # straight-through is NOT used by the reference: .half() is differentiable as a cast
         p1 = p1.half().to(dtype)

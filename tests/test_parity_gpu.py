@@ -28,11 +28,12 @@ def op():
     return pkg
 
 
-def run_gpu(pkg, q1, q2, k1, k2, v, dy, lam, lam_init, rms, lam_dtype=torch.float32):
+def run_gpu(pkg, q1, q2, k1, k2, v, dy, lam, lam_init, rms, lam_dtype=torch.float32, causal=False):
     dev = torch.device("cuda", 0)
     leaves = [t.to(dev).clone().requires_grad_(True) for t in (q1, q2, k1, k2, v)]
     lam_t = torch.tensor([lam], dtype=lam_dtype, device=dev, requires_grad=True)
-    y = pkg.MultiheadDiffAttnKernel(*leaves, lam_t, lam_init, rms)
+    y = pkg.MultiheadDiffAttnKernel(*leaves, lam_t, lam_init, rms, causal=causal) if causal else \
+        pkg.MultiheadDiffAttnKernel(*leaves, lam_t, lam_init, rms)
     y.backward(dy.to(dev))
     pkg.device_status(0)
     out = {"y": y.detach().cpu()}
@@ -126,6 +127,30 @@ def test_ragged_sequence_lengths(op, b, h, n, d, lam, lam_init, rms, seed):
     check(got, want)
     for k in ("y",) + GRADS:
         assert torch.isfinite(got[k]).all(), k
+
+
+CAUSAL = [
+    # b, h, n, d, lam, lam_init, rms, seed -- causal mask (an extension: the reference has no masking, README.md:2)
+    (1, 2, 256, 64, 0.5, 0.8, True, 71),
+    (2, 2, 512, 64, 0.5, 0.8, True, 72),
+    (1, 1, 1024, 64, -0.4, 0.2, False, 73),
+    (1, 2, 328, 64, 0.5, 0.8, True, 74),       # causal and ragged
+    (1, 2, 384, 32, 0.5, 0.8, True, 75),
+    (1, 1, 512, 128, 0.7, 0.2, False, 76),
+    (1, 2, 200, 128, 0.5, 0.8, True, 77),
+]
+
+
+@pytest.mark.parametrize("b,h,n,d,lam,lam_init,rms,seed", CAUSAL)
+def test_causal_mask(op, b, h, n, d, lam, lam_init, rms, seed):
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(b, h, n, d, seed)
+    want = oracle.backward_closed_form(q1, q2, k1, k2, v, torch.tensor([lam]), dy, lam_init, rms, causal=True)
+    got = run_gpu(op, q1, q2, k1, k2, v, dy, lam, lam_init, rms, causal=True)
+    check(got, want)
+    # the first query row attends to key 0 only: A = (1 - lam) v_0 before the norm
+    if not rms:
+        a0 = (1 - lam) * v[:, :, 0, :].float()
+        assert torch.allclose(got["y"][:, :, 0, :].float(), a0, atol=2e-3, rtol=2e-3)
 
 
 def test_saved_statistics(op):

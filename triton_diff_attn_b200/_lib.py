@@ -34,7 +34,7 @@ class DiffAttnParams(C.Structure):
         ("v_stride_b", C.c_int64), ("v_stride_h", C.c_int64), ("v_stride_n", C.c_int64),
         ("q1", C.c_void_p), ("q2", C.c_void_p), ("k1", C.c_void_p), ("k2", C.c_void_p), ("v", C.c_void_p),
         ("lambda_scale", C.c_void_p), ("lambda_dtype", C.c_int32), ("rms_norm", C.c_int32),
-        ("sm_scale", C.c_float), ("lambda_init", C.c_float), ("eps", C.c_float), ("reserved0", C.c_int32),
+        ("sm_scale", C.c_float), ("lambda_init", C.c_float), ("eps", C.c_float), ("causal", C.c_int32),
         ("y", C.c_void_p), ("a2", C.c_void_p), ("lse1", C.c_void_p), ("lse2", C.c_void_p), ("rstd", C.c_void_p),
         ("dy", C.c_void_p),
         ("dq1", C.c_void_p), ("dq2", C.c_void_p), ("dk1", C.c_void_p), ("dk2", C.c_void_p), ("dv", C.c_void_p),

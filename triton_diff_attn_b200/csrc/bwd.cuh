@@ -34,6 +34,7 @@ struct BwdArgs {
   int n;
   int h;
   int d;                // real head dim (64, or 32 with zero-filled padding in the 64-wide tiles)
+  int causal;           // 1: query row i sees key columns j <= i only
   int n_pad;            // N rounded up to 128: row pitch of `stats` per (batch, head); rows N..n_pad-1 hold
                         // {+inf, +inf, 0, 0}, which makes the probabilities of out-of-range query rows exactly 0
   long long rows;       // B*H*N
@@ -193,7 +194,11 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kv_tile = blockIdx.x, bh = blockIdx.y;
   const int b_idx = bh / args.h, h_idx = bh % args.h;
-  const int nq = args.n_pad / BQ;      // the last query tiles may reach past N (zero dA, neutral statistics)
+  // the last query tiles may reach past N (zero dA, neutral statistics); under the causal mask only query tiles
+  // from the diagonal on see these keys: tiles i0 .. nq_all-1, visited with the local index i (tile i0 + i)
+  const int nq_all = args.n_pad / BQ;
+  const int i0 = args.causal ? kv_tile * (BKV / BQ) : 0;
+  const int nq = nq_all - i0;
 
   if (warp == WARP_TMA && lane == 0) {
     mbar_init(&misc->bar_kv, 1);
@@ -224,11 +229,11 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
         uint8_t* sp = smem + OFF_STAGE + st * STAGE_BYTES;
         if (!mbar_wait(&misc->empty[st], ((i / ST) & 1) ^ 1, abort_flag, 401, i)) break;
         mbar_expect_tx(&misc->full[st], STAGE_BYTES);
-        tma_load_4d(sp, &tm_q1, &misc->full[st], 0, i * BQ, h_idx, b_idx);
-        tma_load_4d(sp + Q_BYTES, &tm_q2, &misc->full[st], 0, i * BQ, h_idx, b_idx);
-        tma_load_4d(sp + 2 * Q_BYTES, &tm_da, &misc->full[st], 0, i * BQ, bh, 0);
-        tma_load_4d(sp + 2 * Q_BYTES + DA_BYTES / 2, &tm_da, &misc->full[st], 64, i * BQ, bh, 0);
-        bulk_load_1d(sp + 2 * Q_BYTES + DA_BYTES, args.stats + (size_t(bh) * args.n_pad + size_t(i) * BQ), STAT_BYTES,
+        tma_load_4d(sp, &tm_q1, &misc->full[st], 0, (i0 + i) * BQ, h_idx, b_idx);
+        tma_load_4d(sp + Q_BYTES, &tm_q2, &misc->full[st], 0, (i0 + i) * BQ, h_idx, b_idx);
+        tma_load_4d(sp + 2 * Q_BYTES, &tm_da, &misc->full[st], 0, (i0 + i) * BQ, bh, 0);
+        tma_load_4d(sp + 2 * Q_BYTES + DA_BYTES / 2, &tm_da, &misc->full[st], 64, (i0 + i) * BQ, bh, 0);
+        bulk_load_1d(sp + 2 * Q_BYTES + DA_BYTES, args.stats + (size_t(bh) * args.n_pad + size_t(i0 + i) * BQ), STAT_BYTES,
                      &misc->full[st]);
       }
     }
@@ -334,6 +339,15 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
       tc_fence_before();
       mbar_arrive(&misc->s_free);
       DA_TS(2);
+      if (args.causal) {
+        // this thread's key row sees query columns >= its own index only: the first c0 columns of its 16 are hidden
+        const int c0 = kv_tile * BKV + row - ((i0 + i) * BQ + g * 16);
+        if (c0 > 0) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (j < c0) { s1[j] = 0xff800000u; s2[j] = 0xff800000u; }
+        }
+      }
       uint32_t pc[8], d1[8], d2[8];
 #pragma unroll
       for (int jj = 0; jj < 8; ++jj) {
@@ -462,7 +476,8 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_tile = blockIdx.x, bh = blockIdx.y;
   const int b_idx = bh / args.h, h_idx = bh % args.h;
-  const int nkv = args.n_pad / BN;
+  const int nkv_all = args.n_pad / BN;
+  const int nkv = (args.causal && q_tile + 1 < nkv_all) ? q_tile + 1 : nkv_all;   // causal: stop at the diagonal tile
   const int nsub = 2 * nkv;
 
   if (warp == WARP_TMA && lane == 0) {
@@ -611,12 +626,16 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
       tmem_ld32(t_dp, dp);
       tc_wait_ld();
       DA_TS(2);
-      if (t * SUB + half * 32 + 32 > args.n) {
-        // key columns >= N: score -inf, probability 0
-        const int nv = args.n - (t * SUB + half * 32);
+      {
+        // key columns past the sequence end or (causal) right of the diagonal: score -inf, probability 0
+        const int c_first = t * SUB + half * 32;
+        int nv = args.n - c_first;
+        if (args.causal) nv = min(nv, q_tile * BM + row - c_first + 1);
+        if (nv < 32) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (i >= nv) s[i] = 0xff800000u;
+          for (int i = 0; i < 32; ++i)
+            if (i >= nv) s[i] = 0xff800000u;
+        }
       }
 #pragma unroll
       for (int i = 0; i < 16; ++i) {

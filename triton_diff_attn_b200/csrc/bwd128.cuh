@@ -54,7 +54,11 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x, bh = blockIdx.y, br = blockIdx.z;
   const int b_idx = bh / args.h, h_idx = bh % args.h;
-  const int nsub = args.n_pad / SUB;
+  // streamed 64-row sub-tiles t0 .. t0+nsub-1 (local index t).  Causal: the query side streams keys up to its
+  // diagonal tile, the key side streams queries from its diagonal tile on.
+  const int nsub_all = args.n_pad / SUB;
+  const int t0 = (args.causal && !QSIDE) ? 2 * tile : 0;
+  const int nsub = (args.causal && QSIDE) ? min(nsub_all, 2 * (tile + 1)) : nsub_all - t0;
   const CUtensorMap* tm_x = br ? &tm_x1 : &tm_x0;
   const CUtensorMap* tm_z = br ? &tm_z1 : &tm_z0;
   // dA is the Y operand on the query side and the W operand on the key side
@@ -86,10 +90,10 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
         uint8_t* sp = smem + OFF_STAGE + st * STAGE_BYTES;
         if (!mbar_wait(&misc->empty[st], par, abort_flag, 1101, t)) break;
         mbar_expect_tx(&misc->full[st], QSIDE ? (Z_BYTES + W_BYTES) : STAGE_BYTES);
-        for (int c = 0; c < 2; ++c) tma_load_4d(sp + c * 8192, tm_z, &misc->full[st], c * 64, t * SUB, h_idx, b_idx);
-        for (int c = 0; c < 4; ++c) tma_load_4d(sp + Z_BYTES + c * 8192, &tm_w, &misc->full[st], c * 64, t * SUB, w_c2, w_c3);
+        for (int c = 0; c < 2; ++c) tma_load_4d(sp + c * 8192, tm_z, &misc->full[st], c * 64, (t0 + t) * SUB, h_idx, b_idx);
+        for (int c = 0; c < 4; ++c) tma_load_4d(sp + Z_BYTES + c * 8192, &tm_w, &misc->full[st], c * 64, (t0 + t) * SUB, w_c2, w_c3);
         if (!QSIDE)
-          bulk_load_1d(sp + Z_BYTES + W_BYTES, args.stats + (size_t(bh) * args.n_pad + size_t(t) * SUB), STAT_BYTES, &misc->full[st]);
+          bulk_load_1d(sp + Z_BYTES + W_BYTES, args.stats + (size_t(bh) * args.n_pad + size_t(t0 + t) * SUB), STAT_BYTES, &misc->full[st]);
         if (++st == ST) { st = 0; par ^= 1; }
       }
     }
@@ -170,13 +174,25 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
       tmem_ld16(t_s, s);
       tmem_ld16(t_t, tt);
       tc_wait_ld();
-      if (QSIDE && t * SUB + g * 16 + 16 > args.n) {
-        // query side: streamed columns are key rows; those >= N get probability 0.  (On the key side the
-        // streamed columns are query rows, whose padded statistics already give probability 0.)
-        const int nv = args.n - (t * SUB + g * 16);
+      if (QSIDE) {
+        // query side: streamed columns are key rows; those >= N, or (causal) right of this row's diagonal, get
+        // probability 0.  (On the key side the streamed columns are query rows: out-of-range ones already have
+        // neutral statistics, and the causal mask hides the columns LEFT of the diagonal.)
+        const int c_first = t * SUB + g * 16;
+        int nv = args.n - c_first;
+        if (args.causal) nv = min(nv, tile * BM + row - c_first + 1);
+        if (nv < 16) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-          if (i >= nv) s[i] = 0xff800000u;
+          for (int i = 0; i < 16; ++i)
+            if (i >= nv) s[i] = 0xff800000u;
+        }
+      } else if (args.causal) {
+        const int c0 = tile * BM + row - ((t0 + t) * SUB + g * 16);
+        if (c0 > 0) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (i < c0) s[i] = 0xff800000u;
+        }
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -271,7 +287,9 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kv_tile = blockIdx.x, bh = blockIdx.y;
   const int b_idx = bh / args.h, h_idx = bh % args.h;
-  const int nq = args.n_pad / BQ;
+  const int nq_all = args.n_pad / BQ;
+  const int i0 = args.causal ? kv_tile * (BKV / BQ) : 0;     // causal: query tiles from the diagonal on
+  const int nq = nq_all - i0;
 
   if (warp == WARP_TMA && lane == 0) {
     mbar_init(&misc->bar_kv, 1);
@@ -303,11 +321,11 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
         if (!mbar_wait(&misc->empty[st], par, abort_flag, 1401, i)) break;
         mbar_expect_tx(&misc->full[st], STAGE_BYTES);
         for (int c = 0; c < 2; ++c) {
-          tma_load_4d(sp + c * 8192, &tm_q1, &misc->full[st], c * 64, i * BQ, h_idx, b_idx);
-          tma_load_4d(sp + Q_BYTES + c * 8192, &tm_q2, &misc->full[st], c * 64, i * BQ, h_idx, b_idx);
+          tma_load_4d(sp + c * 8192, &tm_q1, &misc->full[st], c * 64, (i0 + i) * BQ, h_idx, b_idx);
+          tma_load_4d(sp + Q_BYTES + c * 8192, &tm_q2, &misc->full[st], c * 64, (i0 + i) * BQ, h_idx, b_idx);
         }
-        for (int c = 0; c < 4; ++c) tma_load_4d(sp + 2 * Q_BYTES + c * 8192, &tm_da, &misc->full[st], c * 64, i * BQ, bh, 0);
-        bulk_load_1d(sp + 2 * Q_BYTES + DA_BYTES, args.stats + (size_t(bh) * args.n_pad + size_t(i) * BQ), STAT_BYTES, &misc->full[st]);
+        for (int c = 0; c < 4; ++c) tma_load_4d(sp + 2 * Q_BYTES + c * 8192, &tm_da, &misc->full[st], c * 64, (i0 + i) * BQ, bh, 0);
+        bulk_load_1d(sp + 2 * Q_BYTES + DA_BYTES, args.stats + (size_t(bh) * args.n_pad + size_t(i0 + i) * BQ), STAT_BYTES, &misc->full[st]);
         if (++st == ST) { st = 0; par ^= 1; }
       }
     }
@@ -380,6 +398,14 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
       tmem_ld16(tb + T_S1 + u * BQ + g * 16, s1);
       tmem_ld16(tb + T_S2 + u * BQ + g * 16, s2);
       tc_wait_ld();
+      if (args.causal) {
+        const int c0 = kv_tile * BKV + row - ((i0 + i) * BQ + g * 16);   // hidden query columns left of the diagonal
+        if (c0 > 0) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (j < c0) { s1[j] = 0xff800000u; s2[j] = 0xff800000u; }
+        }
+      }
 #pragma unroll
       for (int jj = 0; jj < 8; ++jj) {
         float v[2];

@@ -163,7 +163,7 @@ int diffattn_fwd(const DiffAttnParams* p) {
   a.lse1 = p->lse1; a.lse2 = p->lse2; a.rstd = p->rstd;
   a.lambda_ptr = p->lambda_scale; a.lambda_dtype = p->lambda_dtype;
   a.sm_scale = p->sm_scale; a.out_scale = 1.f - p->lambda_init; a.eps = p->eps;
-  a.rms_norm = p->rms_norm; a.n = p->N; a.h = p->H; a.d = p->D;
+  a.rms_norm = p->rms_norm; a.n = p->N; a.h = p->H; a.d = p->D; a.causal = p->causal ? 1 : 0;
   if (D == 128) {
     if ((rc = set_smem(da::diffattn_fwd128_kernel, da::fwd128::SMEM_BYTES))) return rc;
     dim3 grid128((p->N + 127) / 128, p->B * p->H);
@@ -204,6 +204,7 @@ int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages) {
   a.sm_scale = p->sm_scale; a.out_scale = 1.f - p->lambda_init; a.rms_norm = p->rms_norm;
   a.n = p->N; a.h = p->H; a.d = p->D; a.rows = (long long)rows;
   a.n_pad = (p->N + 127) & ~127;
+  a.causal = p->causal ? 1 : 0;
   const int n_tiles = a.n_pad / 128;
 
   // 1. preprocess (grid-stride; one atomic per CTA for d(lambda))

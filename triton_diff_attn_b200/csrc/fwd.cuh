@@ -33,6 +33,7 @@ struct FwdArgs {
   int n;              // sequence length
   int h;              // heads
   int d;              // real head dim: 64, or 32 (then the 64-wide tiles are zero-filled by TMA beyond column 32 / 64)
+  int causal;         // 1: query row i sees key columns j <= i only
 };
 
 __device__ __forceinline__ float load_lambda(const void* p, int dtype) {
@@ -108,7 +109,10 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
   const int bh = blockIdx.y;
   const int b_idx = bh / args.h;
   const int h_idx = bh % args.h;
-  const int nkv = (args.n + BN - 1) / BN;   // the last tile may reach past N: TMA fills those rows with zeros
+  // the last tile may reach past N (TMA fills those rows with zeros); with a causal mask the tiles right of
+  // the diagonal tile are skipped altogether
+  const int nkv_all = (args.n + BN - 1) / BN;
+  const int nkv = (args.causal && q_tile + 1 < nkv_all) ? q_tile + 1 : nkv_all;
   const int nsub = 2 * nkv;          // 64-row sub-tiles
 
   if (warp == WARP_TMA && lane == 0) {
@@ -253,12 +257,16 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
       tmem_ld32(t_s + 32, sr + 32);
       tc_wait_ld();
       DA_TS(2);
-      if ((t + 1) * SUB > args.n) {
-        // sub-tile reaches past the sequence end: key columns >= N get a score of -inf (probability 0)
-        const int nv = args.n - t * SUB;
+      {
+        // key columns past the sequence end, or right of the diagonal under the causal mask, get a score of
+        // -inf (probability 0); nv = number of visible columns of this row in this sub-tile
+        int nv = args.n - t * SUB;
+        if (args.causal) nv = min(nv, q_tile * BM + row - t * SUB + 1);
+        if (nv < SUB) {
 #pragma unroll
-        for (int i = 0; i < SUB; ++i)
-          if (i >= nv) sr[i] = 0xff800000u;
+          for (int i = 0; i < SUB; ++i)
+            if (i >= nv) sr[i] = 0xff800000u;
+        }
       }
 #ifdef DA_LDSTONLY
       tmem_st32(t_s, sr + 32);

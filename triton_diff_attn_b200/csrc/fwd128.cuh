@@ -51,7 +51,8 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_tile = blockIdx.x, bh = blockIdx.y;
   const int b_idx = bh / args.h, h_idx = bh % args.h;
-  const int nsub = ((args.n + 127) / 128) * 2;     // 64-row sub-tiles, N rounded up to 128 (TMA zero-fills)
+  const int nsub_all = ((args.n + 127) / 128) * 2;     // 64-row sub-tiles, N rounded up to 128 (TMA zero-fills)
+  const int nsub = (args.causal && 2 * (q_tile + 1) < nsub_all) ? 2 * (q_tile + 1) : nsub_all;   // causal: stop at the diagonal tile
   const int ntot = 2 * nsub;          // sub-tiles over both passes
 
   if (warp == 8 && lane == 0) {
@@ -178,11 +179,14 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
         tmem_ld32(t_s + 0, sr);
         tmem_ld32(t_s + 32, sr + 32);
         tc_wait_ld();
-        if ((t + 1) * SUB > args.n) {
-          const int nv = args.n - t * SUB;       // key columns >= N: score -inf, probability 0
+        {
+          int nv = args.n - t * SUB;             // visible key columns of this row in this sub-tile; the rest get -inf
+          if (args.causal) nv = min(nv, q_tile * BM + row - t * SUB + 1);
+          if (nv < SUB) {
 #pragma unroll
-          for (int i = 0; i < SUB; ++i)
-            if (i >= nv) sr[i] = 0xff800000u;
+            for (int i = 0; i < SUB; ++i)
+              if (i >= nv) sr[i] = 0xff800000u;
+          }
         }
         float neg = -m_run * sl2;
         float sum[4] = {0.f, 0.f, 0.f, 0.f};

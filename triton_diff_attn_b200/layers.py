@@ -59,7 +59,7 @@ def _same_layout(ts):
     return ts
 
 
-def _fill_common(p, q1, q2, k1, k2, v, lam, lambda_init, rms_norm, saved):
+def _fill_common(p, q1, q2, k1, k2, v, lam, lambda_init, rms_norm, saved, causal=False):
     b, h, n, d = q1.shape
     p.device = q1.device.index if q1.device.index is not None else torch.cuda.current_device()
     p.stream = torch.cuda.current_stream(q1.device).cuda_stream
@@ -70,6 +70,7 @@ def _fill_common(p, q1, q2, k1, k2, v, lam, lambda_init, rms_norm, saved):
     p.lambda_scale = lam.data_ptr()
     p.lambda_dtype = _lib.LAMBDA_F16 if lam.dtype == torch.float16 else _lib.LAMBDA_F32
     p.rms_norm = 1 if rms_norm else 0
+    p.causal = 1 if causal else 0
     p.sm_scale = 1.0 / math.sqrt(d)          # reference src/layers.py:20-22 (D, not 2D)
     p.lambda_init = float(lambda_init)
     p.eps = EPS
@@ -82,7 +83,7 @@ class DiffAttnFunction(torch.autograd.Function):
     (reference src/kernel.py:461-575)."""
 
     @staticmethod
-    def forward(ctx, q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm):
+    def forward(ctx, q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, causal=False):
         _check_inputs(q1, q2, k1, k2, v, lambda_scale)
         q1, q2, k1, k2 = _same_layout([q1, q2, k1, k2])
         if v.stride(-1) != 1:
@@ -96,11 +97,12 @@ class DiffAttnFunction(torch.autograd.Function):
             lse2 = torch.empty_like(lse1)
             rstd = torch.empty_like(lse1)
             p = _lib.new_params()
-            _fill_common(p, q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, (y, a2, lse1, lse2, rstd))
+            _fill_common(p, q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, (y, a2, lse1, lse2, rstd), causal)
             _lib.check(_lib.lib.diffattn_fwd(p), "diffattn_fwd")
         ctx.save_for_backward(q1, q2, k1, k2, v, lambda_scale, y, a2, lse1, lse2, rstd)
         ctx.lambda_init = float(lambda_init)
         ctx.rms_norm = bool(rms_norm)
+        ctx.causal = bool(causal)
         return y
 
     @staticmethod
@@ -115,7 +117,7 @@ class DiffAttnFunction(torch.autograd.Function):
             dv = torch.empty((b, h, n, 2 * d), dtype=torch.float16, device=dev)
             dlam = torch.zeros(1, dtype=torch.float32, device=dev)
             p = _lib.new_params()
-            _fill_common(p, q1, q2, k1, k2, v, lam, ctx.lambda_init, ctx.rms_norm, (y, a2, lse1, lse2, rstd))
+            _fill_common(p, q1, q2, k1, k2, v, lam, ctx.lambda_init, ctx.rms_norm, (y, a2, lse1, lse2, rstd), ctx.causal)
             nbytes = int(_lib.lib.diffattn_workspace_bytes(p))
             ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
             p.dy = dy.data_ptr()
@@ -126,12 +128,13 @@ class DiffAttnFunction(torch.autograd.Function):
         # fp32 partial kept for callers that shard (batch*head) and sum partials themselves
         DiffAttnFunction.last_dlambda_fp32 = dlam
         dlam_out = dlam.to(lam.dtype).reshape(lam.shape) if ctx.needs_input_grad[5] else None
-        return dq1, dq2, dk1, dk2, dv, dlam_out, None, None
+        return dq1, dq2, dk1, dk2, dv, dlam_out, None, None, None
 
     last_dlambda_fp32 = None
 
 
-def MultiheadDiffAttnKernel(q1, q2, k1, k2, v, lambda_scale=-0.5, lambda_init: float = 0.8, rms_norm: bool = False):
+def MultiheadDiffAttnKernel(q1, q2, k1, k2, v, lambda_scale=-0.5, lambda_init: float = 0.8, rms_norm: bool = False,
+                            causal: bool = False):
     """Fused differential attention, same signature as the reference (src/layers.py:10-26).
 
     q1,q2,k1,k2: fp16 CUDA [B,H,N,D]; v: fp16 CUDA [B,H,N,2D]; lambda_scale: 1-element fp16/fp32
@@ -140,8 +143,10 @@ def MultiheadDiffAttnKernel(q1, q2, k1, k2, v, lambda_scale=-0.5, lambda_init: f
     1/sqrt(D) (src/layers.py:20-22); (1 - lambda_init) is applied only with rms_norm
     (src/layers.py:74-78).  Any sequence length N >= 1 is accepted (key columns past N are masked in the last
     tile); the reference needs N to be a multiple of its block sizes (src/kernel.py:148,527).
+    `causal=True` (keyword, after the reference's eight parameters) restricts query i to keys j <= i; the
+    reference has no masking (README.md:2).
     """
-    return DiffAttnFunction.apply(q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm)
+    return DiffAttnFunction.apply(q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, causal)
 
 
 def device_status(device=None) -> None:
