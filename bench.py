@@ -274,6 +274,8 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--causal", action="store_true", help="causal mask (extension); flops credited for the visible "
+                    "N(N+1)/2 pairs only")
     ap.add_argument("--sweep-reference-protocol", action="store_true",
                     help="instead of the one-line benchmark: the reference's own sweep (src/benchmark.py:19-25): "
                          "H=16, D=32, fp16, rms_norm, N in 512..16384 with B = 16384/N; one JSON line per N")
@@ -322,7 +324,7 @@ def main():
     dv = torch.empty_like(v)
     dlam = torch.zeros(1, dtype=torch.float32, device=dev)
     p = _lib.new_params()
-    layers._fill_common(p, q1, q2, k1, k2, v, lam_t, lam_init, rms, (y, a2, lse1, lse2, rstd))
+    layers._fill_common(p, q1, q2, k1, k2, v, lam_t, lam_init, rms, (y, a2, lse1, lse2, rstd), args.causal)
     ws_bytes = int(_lib.lib.diffattn_workspace_bytes(p))
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
     p.dy = dy.data_ptr()
@@ -381,6 +383,8 @@ def main():
     dl_total = sum_dlambda_on_host(dlam)
 
     f_fwd, f_bwd = flops(b, h, n, d)
+    if args.causal:
+        f_fwd, f_bwd = f_fwd * (n + 1) / (2.0 * n), f_bwd * (n + 1) / (2.0 * n)
     total_flops = (f_fwd + f_bwd) * world
     value = total_flops / (ms_step * 1e-3) / 1e12
 
@@ -401,7 +405,7 @@ def main():
             its y / gradients / d(lambda) back; copies of neighbouring steps overlap with the kernels."""
             pipe.begin()
             for _ in range(iters):
-                pipe.submit(host_in, host_out, host_dl, lam_t, lam_init, rms)
+                pipe.submit(host_in, host_out, host_dl, lam_t, lam_init, rms, args.causal)
             pipe.end()
 
         e2e_run(3)
@@ -447,7 +451,7 @@ def main():
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16",
         "data": "synthetic",
         "config": {"workload": f"{args.workload}: B={b} H={h} N={n} D={d} (v width {2 * d}) per GPU, rms_norm={rms}, "
-                               f"lambda={lam}, lambda_init={lam_init}, fwd+bwd",
+                               f"lambda={lam}, lambda_init={lam_init}, fwd+bwd" + (", causal" if args.causal else ""),
                    "sharding": f"(batch*head) shards, {world} rank(s), no data-path collective; d(lambda) summed on host",
                    "l2": "inputs+outputs per step (~0.8 GB) exceed the 126 MB L2; no explicit flush"},
         "fwd": {"ms": ms_fwd, "tflops": f_fwd / (ms_fwd * 1e-3) / 1e12, "frac_nominal": f_fwd / (ms_fwd * 1e-3) / 1e12 / NOMINAL_TFLOPS},

@@ -35,7 +35,7 @@ class HostStepPipeline:
             s.wait_stream(cur)
 
     def submit(self, host_in: Sequence[torch.Tensor], host_out: Sequence[torch.Tensor], host_dlambda: torch.Tensor,
-               lambda_scale: torch.Tensor, lambda_init: float, rms_norm: bool) -> None:
+               lambda_scale: torch.Tensor, lambda_init: float, rms_norm: bool, causal: bool = False) -> None:
         """host_in = (q1, q2, k1, k2, v, dy) pinned; host_out = (y, dq1, dq2, dk1, dk2, dv) pinned."""
         slot = self.count % self.depth
         if len(self.staging) <= slot:
@@ -51,7 +51,7 @@ class HostStepPipeline:
             self.s_run.wait_event(self.in_done[slot])
             leaves = [b.detach().requires_grad_(True) for b in bufs[:5]]
             lam = lambda_scale.detach().clone().requires_grad_(True)
-            y = MultiheadDiffAttnKernel(*leaves, lam, lambda_init, rms_norm)
+            y = MultiheadDiffAttnKernel(*leaves, lam, lambda_init, rms_norm, causal)
             y.backward(bufs[5])
             self.run_done[slot].record(self.s_run)
             results = [y.detach()] + [t.grad for t in leaves] + [lam.grad]
