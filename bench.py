@@ -192,8 +192,24 @@ def run_reference_protocol_sweep(args):
                 e0.record(); fn(); e1.record(); torch.cuda.synchronize()
                 times.append(e0.elapsed_time(e1))
             res[name] = statistics.median(times)
+        # peak device memory of one call, as the reference's memory benchmark takes it (src/benchmark.py:181-250):
+        # allocator peak in MiB after reset, inputs and dY included
+        peak = {}
+        for name in ("fwd", "fwd_bwd"):
+            torch.cuda.synchronize()
+            torch.cuda.reset_peak_memory_stats(dev)
+            y = fwd_only()
+            if name == "fwd_bwd":
+                y.backward(dy)
+            torch.cuda.synchronize()
+            peak[name] = torch.cuda.max_memory_allocated(dev) / 2**20
+            del y
+            for t in (q1, q2, k1, k2, v, lam):
+                t.grad = None
+        resident = sum(t.numel() * t.element_size() for t in (q1, q2, k1, k2, v, dy)) / 2**20
         f, bk = flops(b, h, n, d)
         emit({"protocol": "reference src/benchmark.py:19-25", "B": b, "H": h, "N": n, "D": d,
+              "fwd_peak_mib": peak["fwd"], "fwd_bwd_peak_mib": peak["fwd_bwd"], "inputs_and_dy_mib": resident,
                           "fwd_ms_median": res["fwd"], "fwd_bwd_ms_median": res["fwd_bwd"],
                           "fwd_tflops": f / (res["fwd"] * 1e-3) / 1e12, "fwd_bwd_tflops": (f + bk) / (res["fwd_bwd"] * 1e-3) / 1e12})
 
@@ -274,6 +290,8 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--io-dtype", default="fp16", choices=["fp16", "bf16"],
+                    help="16-bit type of the tensors: fp16 (the reference's and the headline) or bf16 (extension)")
     ap.add_argument("--causal", action="store_true", help="causal mask (extension); flops credited for the visible "
                     "N(N+1)/2 pairs only")
     ap.add_argument("--sweep-reference-protocol", action="store_true",
@@ -310,12 +328,14 @@ def main():
     b, h, n, d, scale, lam, lam_init, rms = WORKLOADS[args.workload]
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
 
+    io_dtype = torch.bfloat16 if args.io_dtype == "bf16" else torch.float16
+
     def draw(*shape):
-        return (torch.randn(*shape, generator=g, device=dev, dtype=torch.float32) * scale).to(torch.float16)
+        return (torch.randn(*shape, generator=g, device=dev, dtype=torch.float32) * scale).to(io_dtype)
 
     q1, q2, k1, k2 = (draw(b, h, n, d) for _ in range(4))
     v = draw(b, h, n, 2 * d)
-    dy = torch.randn(b, h, n, 2 * d, generator=g, device=dev, dtype=torch.float32).to(torch.float16)
+    dy = torch.randn(b, h, n, 2 * d, generator=g, device=dev, dtype=torch.float32).to(io_dtype)
     lam_t = torch.tensor([lam], dtype=torch.float32, device=dev)
 
     y = torch.empty_like(v); a2 = torch.empty_like(v)
@@ -448,7 +468,7 @@ def main():
     }
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16",
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": args.io_dtype,
         "data": "synthetic",
         "config": {"workload": f"{args.workload}: B={b} H={h} N={n} D={d} (v width {2 * d}) per GPU, rms_norm={rms}, "
                                f"lambda={lam}, lambda_init={lam_init}, fwd+bwd" + (", causal" if args.causal else ""),

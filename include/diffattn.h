@@ -35,9 +35,13 @@ enum {
   DIFFATTN_ERR_TIMEOUT = -10        /* a device-side wait gave up (reported by diffattn_status) */
 };
 
-enum { DIFFATTN_LAMBDA_F16 = 0, DIFFATTN_LAMBDA_F32 = 1 };
+enum { DIFFATTN_LAMBDA_F16 = 0, DIFFATTN_LAMBDA_F32 = 1, DIFFATTN_LAMBDA_BF16 = 2 };
+/* 16-bit type of q1,q2,k1,k2,v,y,a2,dy and every gradient tensor.  The reference computes in fp16 only
+ * (it casts P to tl.float16, src/kernel.py:175-176); bf16 is an extension for callers that train in bf16. */
+enum { DIFFATTN_IO_F16 = 0, DIFFATTN_IO_BF16 = 1 };
 
-/* q1,q2,k1,k2: fp16 [B,H,N,D] sharing one set of element strides (last dim contiguous), as the
+/* ("fp16" below reads "bf16" when io_dtype = DIFFATTN_IO_BF16.)
+ * q1,q2,k1,k2: fp16 [B,H,N,D] sharing one set of element strides (last dim contiguous), as the
  * reference takes them from Q1 alone (src/kernel.py:487-490).  v: fp16 [B,H,N,2D] with its own
  * strides (src/kernel.py:491-494).  Everything the library writes is dense row-major:
  * y, a2, dy, dv [B,H,N,2D] fp16; dq1,dq2,dk1,dk2 [B,H,N,D] fp16; lse1,lse2,rstd [B,H,N] fp32. */
@@ -65,6 +69,8 @@ typedef struct DiffAttnParams {
   float* dlambda;                  /* ONE fp32 on the device; the backward ADDS -sum(E2) into it */
   void* workspace;                 /* diffattn_workspace_bytes() bytes, 256-byte aligned */
   uint64_t workspace_bytes;
+  int32_t io_dtype;                /* DIFFATTN_IO_*: 0 = fp16 (the reference's type), 1 = bf16 */
+  int32_t reserved1;               /* must be 0 */
 } DiffAttnParams;
 
 /* Forward.  Reads q1,q2,k1,k2,v,lambda_scale; writes y,a2,lse1,lse2,rstd.

@@ -66,6 +66,7 @@ def test_null_and_struct(L):
     (lambda p: setattr(p, "q2", 0), -1),
     (lambda p: setattr(p, "k1", 0x10008), -6),
     (lambda p: setattr(p, "lambda_dtype", 9), -7),
+    (lambda p: setattr(p, "io_dtype", 2), -7),
     (lambda p: setattr(p, "B", 70000), -3),
 ])
 def test_fwd_rejects(L, mutate, code):

@@ -20,7 +20,8 @@ ERR_NAMES = {
 }
 VALUE_ERRORS = (-1, -2, -3, -4, -5, -6, -7, -8)   # caller mistakes -> ValueError; the rest RuntimeError
 
-LAMBDA_F16, LAMBDA_F32 = 0, 1
+LAMBDA_F16, LAMBDA_F32, LAMBDA_BF16 = 0, 1, 2
+IO_F16, IO_BF16 = 0, 1
 STAGE_PRE, STAGE_DKDV, STAGE_DQ, STAGE_ALL = 1, 2, 4, 7
 STATIC_SCRATCH_BYTES = 32 << 20
 
@@ -39,6 +40,7 @@ class DiffAttnParams(C.Structure):
         ("dy", C.c_void_p),
         ("dq1", C.c_void_p), ("dq2", C.c_void_p), ("dk1", C.c_void_p), ("dk2", C.c_void_p), ("dv", C.c_void_p),
         ("dlambda", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64),
+        ("io_dtype", C.c_int32), ("reserved1", C.c_int32),
     ]
 
 

@@ -43,7 +43,7 @@ struct BwdArgs {
 // ------------------------------------------------------------------------------------------------
 // 1. preprocess: one warp per row, DV = 32 * VPL halves per row
 // ------------------------------------------------------------------------------------------------
-template <int VPL>   // halves per lane: 2 (DV=64), 4 (DV=128), 8 (DV=256)
+template <int VPL, bool BF>   // 16-bit elements per lane: 2 (DV=64), 4 (DV=128), 8 (DV=256); BF: bf16 tensors
 __global__ void __launch_bounds__(256) diffattn_bwd_pre_kernel(const BwdArgs args) {
   constexpr int DV = 32 * VPL;
   constexpr float LOG2E = 1.4426950408889634f;
@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(256) diffattn_bwd_pre_kernel(const BwdArgs arg
         *reinterpret_cast<uint32_t*>(ha) = *reinterpret_cast<const uint32_t*>(args.a2 + off);
       }
 #pragma unroll
-      for (int i = 0; i < VPL; ++i) { dy[i] = __half2float(hd[i]); yv[i] = __half2float(hy[i]); a2[i] = __half2float(ha[i]); }
+      for (int i = 0; i < VPL; ++i) { dy[i] = to_float16b<BF>(hd[i]); yv[i] = to_float16b<BF>(hy[i]); a2[i] = to_float16b<BF>(ha[i]); }
     }
     float da[VPL], av[VPL];
     if (args.rms_norm) {
@@ -93,13 +93,13 @@ __global__ void __launch_bounds__(256) diffattn_bwd_pre_kernel(const BwdArgs arg
 #pragma unroll
       for (int i = 0; i < VPL; ++i) { da[i] = dy[i]; av[i] = yv[i]; }
     }
-    // round dA to fp16 first: the row sums below must agree with what the MMAs will see
+    // round dA to the 16-bit type first: the row sums below must agree with what the MMAs will see
     __half hda[VPL];
     float e2 = 0.f, ea = 0.f;
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
-      hda[i] = __float2half_rn(da[i]);
-      const float d = __half2float(hda[i]);
+      hda[i] = from_float16b<BF>(da[i]);
+      const float d = to_float16b<BF>(hda[i]);
       e2 += d * a2[i];
       ea += d * av[i];
     }
@@ -181,6 +181,7 @@ struct Misc {
 };
 }  // namespace dkdv64
 
+template <bool BF>
 __global__ void __launch_bounds__(dkdv64::NUM_THREADS, 1)
 diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
                            const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k2,
@@ -240,9 +241,9 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
   } else if (warp == WARP_MMA) {
     // One elected thread issues every MMA; descriptors advance by 32-bit adds (see sm100.cuh).
     if (elect_one()) {
-      constexpr uint32_t IDESC_S = make_idesc(BKV, BQ, 0, 0);     // S^T = K Q^T, dP^T = V dA^T
-      constexpr uint32_t IDESC_DV = make_idesc(BKV, DV, 0, 1);    // dV += Pc^T dA   (Pc K-major smem, dA MN-major)
-      constexpr uint32_t IDESC_DK = make_idesc(BKV, HD, 0, 1);    // dK += dS^T Q    (dS^T in TMEM, Q MN-major)
+      constexpr uint32_t IDESC_S = make_idesc(BKV, BQ, 0, 0, BF);     // S^T = K Q^T, dP^T = V dA^T
+      constexpr uint32_t IDESC_DV = make_idesc(BKV, DV, 0, 1, BF);    // dV += Pc^T dA   (Pc K-major smem, dA MN-major)
+      constexpr uint32_t IDESC_DK = make_idesc(BKV, HD, 0, 1, BF);    // dK += dS^T Q    (dS^T in TMEM, Q MN-major)
       const uint32_t k1_lo = sdesc_lo(smem_u32(smem + OFF_K1)), k2_lo = sdesc_lo(smem_u32(smem + OFF_K2));
       const uint32_t v_lo = sdesc_lo(smem_u32(smem + OFF_V));
       const uint32_t pc_lo0 = sdesc_lo(smem_u32(smem + OFF_PC));
@@ -363,9 +364,9 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
           d1v[u] = p1 * (dpv - sv.z);
           d2v[u] = p2 * fmaf(sg, dpv, -sv.w);
         }
-        pc[jj] = pack_half2(pcv[0], pcv[1]);
-        d1[jj] = pack_half2(d1v[0], d1v[1]);
-        d2[jj] = pack_half2(d2v[0], d2v[1]);
+        pc[jj] = pack2<BF>(pcv[0], pcv[1]);
+        d1[jj] = pack2<BF>(d1v[0], d1v[1]);
+        d2[jj] = pack2<BF>(d2v[0], d2v[1]);
       }
       DA_TS(3);
       // operand buffers of tile i-1 (dS^T columns, and Pc buffer of tile i-2) must have been consumed
@@ -414,10 +415,10 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
       for (int i = 0; i < 8; ++i) {
         if (8 * i >= ncols) break;
         uint4 v;
-        v.x = pack_half2(__uint_as_float(acc[8 * i + 0]) * s, __uint_as_float(acc[8 * i + 1]) * s);
-        v.y = pack_half2(__uint_as_float(acc[8 * i + 2]) * s, __uint_as_float(acc[8 * i + 3]) * s);
-        v.z = pack_half2(__uint_as_float(acc[8 * i + 4]) * s, __uint_as_float(acc[8 * i + 5]) * s);
-        v.w = pack_half2(__uint_as_float(acc[8 * i + 6]) * s, __uint_as_float(acc[8 * i + 7]) * s);
+        v.x = pack2<BF>(__uint_as_float(acc[8 * i + 0]) * s, __uint_as_float(acc[8 * i + 1]) * s);
+        v.y = pack2<BF>(__uint_as_float(acc[8 * i + 2]) * s, __uint_as_float(acc[8 * i + 3]) * s);
+        v.z = pack2<BF>(__uint_as_float(acc[8 * i + 4]) * s, __uint_as_float(acc[8 * i + 5]) * s);
+        v.w = pack2<BF>(__uint_as_float(acc[8 * i + 6]) * s, __uint_as_float(acc[8 * i + 7]) * s);
         p[i] = v;
       }
     }
@@ -463,6 +464,7 @@ struct Misc {
 };
 }  // namespace dq64
 
+template <bool BF>
 __global__ void __launch_bounds__(dq64::NUM_THREADS, 1)
 diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
                          const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k2,
@@ -516,8 +518,8 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
   } else if (warp == WARP_MMA) {
     // One elected thread issues every MMA; descriptors advance by 32-bit adds (see sm100.cuh).
     if (elect_one()) {
-      constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0);    // S = Q K^T, dP = dA V^T
-      constexpr uint32_t IDESC_DQ = make_idesc(BM, HD, 0, 1);    // dQ += dS K   (K MN-major)
+      constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0, BF);    // S = Q K^T, dP = dA V^T
+      constexpr uint32_t IDESC_DQ = make_idesc(BM, HD, 0, 1, BF);    // dQ += dS K   (K MN-major)
       constexpr uint32_t HALF = (SUB * 128) >> 4;
       const uint32_t q1_lo = sdesc_lo(smem_u32(smem + OFF_Q1)), q2_lo = sdesc_lo(smem_u32(smem + OFF_Q2));
       const uint32_t da_lo = sdesc_lo(smem_u32(smem + OFF_DA));
@@ -641,7 +643,7 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
       for (int i = 0; i < 16; ++i) {
         const float p0 = ex2(fmaf(__uint_as_float(s[2 * i]), sl2, neg_l));
         const float p1 = ex2(fmaf(__uint_as_float(s[2 * i + 1]), sl2, neg_l));
-        s[i] = pack_half2(p0 * fmaf(sg, __uint_as_float(dp[2 * i]), -e), p1 * fmaf(sg, __uint_as_float(dp[2 * i + 1]), -e));
+        s[i] = pack2<BF>(p0 * fmaf(sg, __uint_as_float(dp[2 * i]), -e), p1 * fmaf(sg, __uint_as_float(dp[2 * i + 1]), -e));
       }
       DA_TS(3);
       tmem_st16(t_s, s);
@@ -661,10 +663,10 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         uint4 v;
-        v.x = pack_half2(__uint_as_float(acc[8 * i + 0]) * sc, __uint_as_float(acc[8 * i + 1]) * sc);
-        v.y = pack_half2(__uint_as_float(acc[8 * i + 2]) * sc, __uint_as_float(acc[8 * i + 3]) * sc);
-        v.z = pack_half2(__uint_as_float(acc[8 * i + 4]) * sc, __uint_as_float(acc[8 * i + 5]) * sc);
-        v.w = pack_half2(__uint_as_float(acc[8 * i + 6]) * sc, __uint_as_float(acc[8 * i + 7]) * sc);
+        v.x = pack2<BF>(__uint_as_float(acc[8 * i + 0]) * sc, __uint_as_float(acc[8 * i + 1]) * sc);
+        v.y = pack2<BF>(__uint_as_float(acc[8 * i + 2]) * sc, __uint_as_float(acc[8 * i + 3]) * sc);
+        v.z = pack2<BF>(__uint_as_float(acc[8 * i + 4]) * sc, __uint_as_float(acc[8 * i + 5]) * sc);
+        v.w = pack2<BF>(__uint_as_float(acc[8 * i + 6]) * sc, __uint_as_float(acc[8 * i + 7]) * sc);
         p[i] = v;
       }
     }

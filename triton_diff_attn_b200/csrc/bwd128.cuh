@@ -40,7 +40,7 @@ struct Misc {
 
 // tm_x, tm_z: the branch's stationary / streamed [N, 128] operand (box rows 128 / 64);
 // tm_y, tm_w: the [N, 256] operands.  dA lives in the dense workspace and is addressed (col, row, b*h, 0).
-template <bool QSIDE>
+template <bool QSIDE, bool BF>
 __global__ void __launch_bounds__(side128::NUM_THREADS, 1)
 diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__ CUtensorMap tm_x1,
                             const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ CUtensorMap tm_z0,
@@ -99,8 +99,8 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
     }
   } else if (warp == WARP_MMA) {
     if (elect_one()) {
-      constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0);
-      constexpr uint32_t IDESC_OUT = make_idesc(BM, HD, 0, 1);     // OUT += dS Z, Z MN-major (two 64-column atoms)
+      constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0, BF);
+      constexpr uint32_t IDESC_OUT = make_idesc(BM, HD, 0, 1, BF);     // OUT += dS Z, Z MN-major (two 64-column atoms)
       const uint32_t x_lo = sdesc_lo(smem_u32(smem + OFF_X)), y_lo = sdesc_lo(smem_u32(smem + OFF_Y));
       const uint32_t st_lo0 = sdesc_lo(smem_u32(smem + OFF_STAGE));
       const uint32_t tb = tmem_base;
@@ -209,7 +209,7 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
           const float p = ex2(fmaf(__uint_as_float(s[j]), sl2, nl));
           v[w] = p * fmaf(sg, __uint_as_float(tt[j]), -ee);
         }
-        ds[i] = pack_half2(v[0], v[1]);
+        ds[i] = pack2<BF>(v[0], v[1]);
       }
       asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
                    ::"r"(t_s), "r"(ds[0]), "r"(ds[1]), "r"(ds[2]), "r"(ds[3]), "r"(ds[4]), "r"(ds[5]), "r"(ds[6]), "r"(ds[7]) : "memory");
@@ -230,10 +230,10 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         uint4 v;
-        v.x = pack_half2(__uint_as_float(acc[8 * i + 0]) * sc, __uint_as_float(acc[8 * i + 1]) * sc);
-        v.y = pack_half2(__uint_as_float(acc[8 * i + 2]) * sc, __uint_as_float(acc[8 * i + 3]) * sc);
-        v.z = pack_half2(__uint_as_float(acc[8 * i + 4]) * sc, __uint_as_float(acc[8 * i + 5]) * sc);
-        v.w = pack_half2(__uint_as_float(acc[8 * i + 6]) * sc, __uint_as_float(acc[8 * i + 7]) * sc);
+        v.x = pack2<BF>(__uint_as_float(acc[8 * i + 0]) * sc, __uint_as_float(acc[8 * i + 1]) * sc);
+        v.y = pack2<BF>(__uint_as_float(acc[8 * i + 2]) * sc, __uint_as_float(acc[8 * i + 3]) * sc);
+        v.z = pack2<BF>(__uint_as_float(acc[8 * i + 4]) * sc, __uint_as_float(acc[8 * i + 5]) * sc);
+        v.w = pack2<BF>(__uint_as_float(acc[8 * i + 6]) * sc, __uint_as_float(acc[8 * i + 7]) * sc);
         p[i] = v;
       }
     }
@@ -275,6 +275,7 @@ struct Misc {
 };
 }  // namespace dv128
 
+template <bool BF>
 __global__ void __launch_bounds__(dv128::NUM_THREADS, 1)
 diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
                           const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k2,
@@ -331,8 +332,8 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
     }
   } else if (warp == WARP_MMA) {
     if (elect_one()) {
-      constexpr uint32_t IDESC_S = make_idesc(BKV, BQ, 0, 0);
-      constexpr uint32_t IDESC_DV = make_idesc(BKV, DV, 0, 1);     // N = 256: dA as MN-major B, four atoms 8 KB apart
+      constexpr uint32_t IDESC_S = make_idesc(BKV, BQ, 0, 0, BF);
+      constexpr uint32_t IDESC_DV = make_idesc(BKV, DV, 0, 1, BF);     // N = 256: dA as MN-major B, four atoms 8 KB apart
       const uint32_t k1_lo = sdesc_lo(smem_u32(smem + OFF_K1)), k2_lo = sdesc_lo(smem_u32(smem + OFF_K2));
       const uint32_t pc_lo = sdesc_lo(smem_u32(smem + OFF_PC));
       const uint32_t st_lo0 = sdesc_lo(smem_u32(smem + OFF_STAGE));
@@ -415,7 +416,7 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
           const float4 sv = stats[j];
           v[w] = fmaf(sg, ex2(fmaf(__uint_as_float(s2[j]), sl2, -sv.y)), ex2(fmaf(__uint_as_float(s1[j]), sl2, -sv.x)));
         }
-        pc[jj] = pack_half2(v[0], v[1]);
+        pc[jj] = pack2<BF>(v[0], v[1]);
       }
       // the single Pc tile is free once dV of the previous query tile has been accumulated
       if (i > 0) {
@@ -446,10 +447,10 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         uint4 v;
-        v.x = pack_half2(__uint_as_float(acc[8 * i + 0]), __uint_as_float(acc[8 * i + 1]));
-        v.y = pack_half2(__uint_as_float(acc[8 * i + 2]), __uint_as_float(acc[8 * i + 3]));
-        v.z = pack_half2(__uint_as_float(acc[8 * i + 4]), __uint_as_float(acc[8 * i + 5]));
-        v.w = pack_half2(__uint_as_float(acc[8 * i + 6]), __uint_as_float(acc[8 * i + 7]));
+        v.x = pack2<BF>(__uint_as_float(acc[8 * i + 0]), __uint_as_float(acc[8 * i + 1]));
+        v.y = pack2<BF>(__uint_as_float(acc[8 * i + 2]), __uint_as_float(acc[8 * i + 3]));
+        v.z = pack2<BF>(__uint_as_float(acc[8 * i + 4]), __uint_as_float(acc[8 * i + 5]));
+        v.w = pack2<BF>(__uint_as_float(acc[8 * i + 6]), __uint_as_float(acc[8 * i + 7]));
         p[i] = v;
       }
     }

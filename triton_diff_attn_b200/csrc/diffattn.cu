@@ -48,8 +48,9 @@ PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
   return fn;
 }
 
-// fp16 tensor [d3, d2, rows, cols] with element strides (s3, s2, s_row, 1); box = box_rows x 64 columns,
+// 16-bit (fp16, or bf16 when BF) tensor [d3, d2, rows, cols] with element strides (s3, s2, s_row, 1); box = box_rows x 64 columns,
 // 128-byte swizzle (the layout the tcgen05 shared-memory descriptors in sm100.cuh describe).
+template <bool BF>
 int make_map(CUtensorMap* map, const void* base, int cols, int rows, int d2, int d3, int64_t s_row, int64_t s2, int64_t s3,
              int box_rows, const char* what) {
   auto enc = get_encode();
@@ -65,7 +66,7 @@ int make_map(CUtensorMap* map, const void* base, int cols, int rows, int d2, int
   cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B;
   (void)cols;
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = enc(map, BF ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(DIFFATTN_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, int(r));
@@ -82,8 +83,10 @@ int check_common(const DiffAttnParams* p, bool bwd) {
     return fail(DIFFATTN_ERR_BAD_SHAPE, "negative size: B=%d H=%d N=%d D=%d", p->B, p->H, p->N, p->D);
   if (!diffattn_supports(p->D, bwd ? 1 : 0))
     return fail(DIFFATTN_ERR_UNSUPPORTED_D, "head dim %d is not compiled in (supported: 32, 64, 128)", p->D);
-  if (p->lambda_dtype != DIFFATTN_LAMBDA_F16 && p->lambda_dtype != DIFFATTN_LAMBDA_F32)
+  if (p->lambda_dtype != DIFFATTN_LAMBDA_F16 && p->lambda_dtype != DIFFATTN_LAMBDA_F32 && p->lambda_dtype != DIFFATTN_LAMBDA_BF16)
     return fail(DIFFATTN_ERR_BAD_DTYPE, "lambda_dtype %d unknown", p->lambda_dtype);
+  if (p->io_dtype != DIFFATTN_IO_F16 && p->io_dtype != DIFFATTN_IO_BF16)
+    return fail(DIFFATTN_ERR_BAD_DTYPE, "io_dtype %d unknown", p->io_dtype);
   if ((long long)p->B * p->H > 65535)
     return fail(DIFFATTN_ERR_BAD_SHAPE, "B*H=%lld exceeds the grid limit 65535", (long long)p->B * p->H);
   if (p->B == 0 || p->H == 0 || p->N == 0) return 1;   // empty: nothing to do
@@ -143,20 +146,23 @@ uint64_t diffattn_workspace_bytes(const DiffAttnParams* p) {
   return round256(rows * 2 * p->D * 2) + round256(uint64_t(p->B) * p->H * n_pad * 16);
 }
 
-int diffattn_fwd(const DiffAttnParams* p) {
-  int rc = check_common(p, false);
-  if (rc < 0) return rc;
-  if (rc == 1) return DIFFATTN_OK;
+}  // extern "C"
+
+namespace {
+
+template <bool BF>
+int fwd_impl(const DiffAttnParams* p) {
+  int rc = 0;
   DA_CUDA(cudaSetDevice(p->device));
   cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
   CUtensorMap mq1, mq2, mk1, mk2, mv;
   const int D = p->D, DV = 2 * p->D;
   const int kv_rows = D == 128 ? 64 : 128;      // the D = 128 kernel streams 64-row tiles
-  if ((rc = make_map(&mq1, p->q1, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "q1"))) return rc;
-  if ((rc = make_map(&mq2, p->q2, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "q2"))) return rc;
-  if ((rc = make_map(&mk1, p->k1, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, kv_rows, "k1"))) return rc;
-  if ((rc = make_map(&mk2, p->k2, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, kv_rows, "k2"))) return rc;
-  if ((rc = make_map(&mv, p->v, DV, p->N, p->H, p->B, p->v_stride_n, p->v_stride_h, p->v_stride_b, kv_rows, "v"))) return rc;
+  if ((rc = make_map<BF>(&mq1, p->q1, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "q1"))) return rc;
+  if ((rc = make_map<BF>(&mq2, p->q2, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "q2"))) return rc;
+  if ((rc = make_map<BF>(&mk1, p->k1, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, kv_rows, "k1"))) return rc;
+  if ((rc = make_map<BF>(&mk2, p->k2, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, kv_rows, "k2"))) return rc;
+  if ((rc = make_map<BF>(&mv, p->v, DV, p->N, p->H, p->B, p->v_stride_n, p->v_stride_h, p->v_stride_b, kv_rows, "v"))) return rc;
   da::FwdArgs a;
   a.y = static_cast<__half*>(p->y);
   a.a2 = static_cast<__half*>(p->a2);
@@ -165,25 +171,22 @@ int diffattn_fwd(const DiffAttnParams* p) {
   a.sm_scale = p->sm_scale; a.out_scale = 1.f - p->lambda_init; a.eps = p->eps;
   a.rms_norm = p->rms_norm; a.n = p->N; a.h = p->H; a.d = p->D; a.causal = p->causal ? 1 : 0;
   if (D == 128) {
-    if ((rc = set_smem(da::diffattn_fwd128_kernel, da::fwd128::SMEM_BYTES))) return rc;
+    if ((rc = set_smem(da::diffattn_fwd128_kernel<BF>, da::fwd128::SMEM_BYTES))) return rc;
     dim3 grid128((p->N + 127) / 128, p->B * p->H);
-    da::diffattn_fwd128_kernel<<<grid128, da::fwd128::NUM_THREADS, da::fwd128::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, a);
+    da::diffattn_fwd128_kernel<BF><<<grid128, da::fwd128::NUM_THREADS, da::fwd128::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, a);
     DA_CUDA(cudaGetLastError());
     return DIFFATTN_OK;
   }
-  if ((rc = set_smem(da::diffattn_fwd64_kernel, da::fwd64::SMEM_BYTES))) return rc;
+  if ((rc = set_smem(da::diffattn_fwd64_kernel<BF>, da::fwd64::SMEM_BYTES))) return rc;
   dim3 grid((p->N + 127) / 128, p->B * p->H);
-  da::diffattn_fwd64_kernel<<<grid, da::fwd64::NUM_THREADS, da::fwd64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, a);
+  da::diffattn_fwd64_kernel<BF><<<grid, da::fwd64::NUM_THREADS, da::fwd64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, a);
   DA_CUDA(cudaGetLastError());
   return DIFFATTN_OK;
 }
 
-int diffattn_bwd(const DiffAttnParams* p) { return diffattn_bwd_stages(p, DIFFATTN_STAGE_ALL); }
-
-int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages) {
-  int rc = check_common(p, true);
-  if (rc < 0) return rc;
-  if (rc == 1) return DIFFATTN_OK;
+template <bool BF>
+int bwd_impl(const DiffAttnParams* p, int32_t stages) {
+  int rc = 0;
   DA_CUDA(cudaSetDevice(p->device));
   cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
   const int D = p->D, DV = 2 * p->D;
@@ -213,16 +216,16 @@ int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages) {
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, p->device);
     long long blocks = (long long)((rows + 7) / 8);
     if (blocks > (long long)sms * 8) blocks = (long long)sms * 8;
-    if (D == 128) da::diffattn_bwd_pre_kernel<8><<<(unsigned)blocks, 256, 0, stream>>>(a);
-    else if (D == 64) da::diffattn_bwd_pre_kernel<4><<<(unsigned)blocks, 256, 0, stream>>>(a);
-    else da::diffattn_bwd_pre_kernel<2><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    if (D == 128) da::diffattn_bwd_pre_kernel<8, BF><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    else if (D == 64) da::diffattn_bwd_pre_kernel<4, BF><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    else da::diffattn_bwd_pre_kernel<2, BF><<<(unsigned)blocks, 256, 0, stream>>>(a);
     if (a.n_pad != a.n) da::diffattn_bwd_padstats_kernel<<<64, 256, 0, stream>>>(a, (int)bh);
     DA_CUDA(cudaGetLastError());
   }
   if (D == 128) {
     // D = 128: dV kernel, then dK and dQ through the per-branch "side" kernel (bwd128.cuh)
     auto qk = [&](CUtensorMap* m, const void* ptr, int rows, const char* nm) {
-      return make_map(m, ptr, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, rows, nm);
+      return make_map<BF>(m, ptr, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, rows, nm);
     };
     CUtensorMap q1_64, q2_64, k1_64, k2_64, q1_128, q2_128, k1_128, k2_128, v_64, v_128, da_64, da_128;
     if ((rc = qk(&q1_64, p->q1, 64, "q1"))) return rc;
@@ -233,25 +236,25 @@ int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages) {
     if ((rc = qk(&q2_128, p->q2, 128, "q2"))) return rc;
     if ((rc = qk(&k1_128, p->k1, 128, "k1"))) return rc;
     if ((rc = qk(&k2_128, p->k2, 128, "k2"))) return rc;
-    if ((rc = make_map(&v_64, p->v, DV, p->N, p->H, p->B, p->v_stride_n, p->v_stride_h, p->v_stride_b, 64, "v"))) return rc;
-    if ((rc = make_map(&v_128, p->v, DV, p->N, p->H, p->B, p->v_stride_n, p->v_stride_h, p->v_stride_b, 128, "v"))) return rc;
-    if ((rc = make_map(&da_64, a.da, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 64, "dA"))) return rc;
-    if ((rc = make_map(&da_128, a.da, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 128, "dA"))) return rc;
+    if ((rc = make_map<BF>(&v_64, p->v, DV, p->N, p->H, p->B, p->v_stride_n, p->v_stride_h, p->v_stride_b, 64, "v"))) return rc;
+    if ((rc = make_map<BF>(&v_128, p->v, DV, p->N, p->H, p->B, p->v_stride_n, p->v_stride_h, p->v_stride_b, 128, "v"))) return rc;
+    if ((rc = make_map<BF>(&da_64, a.da, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 64, "dA"))) return rc;
+    if ((rc = make_map<BF>(&da_128, a.da, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 128, "dA"))) return rc;
     if (stages & DIFFATTN_STAGE_DKDV) {
-      if ((rc = set_smem(da::diffattn_bwd_dv128_kernel, da::dv128::SMEM_BYTES))) return rc;
+      if ((rc = set_smem(da::diffattn_bwd_dv128_kernel<BF>, da::dv128::SMEM_BYTES))) return rc;
       dim3 g1(n_tiles, (unsigned)bh);
-      da::diffattn_bwd_dv128_kernel<<<g1, da::dv128::NUM_THREADS, da::dv128::SMEM_BYTES, stream>>>(q1_64, q2_64, k1_128, k2_128, da_64, a);
+      da::diffattn_bwd_dv128_kernel<BF><<<g1, da::dv128::NUM_THREADS, da::dv128::SMEM_BYTES, stream>>>(q1_64, q2_64, k1_128, k2_128, da_64, a);
       DA_CUDA(cudaGetLastError());
-      if ((rc = set_smem(da::diffattn_bwd_side128_kernel<false>, da::side128::SMEM_BYTES))) return rc;
+      if ((rc = set_smem(da::diffattn_bwd_side128_kernel<false, BF>, da::side128::SMEM_BYTES))) return rc;
       dim3 g2(n_tiles, (unsigned)bh, 2);
-      da::diffattn_bwd_side128_kernel<false><<<g2, da::side128::NUM_THREADS, da::side128::SMEM_BYTES, stream>>>(
+      da::diffattn_bwd_side128_kernel<false, BF><<<g2, da::side128::NUM_THREADS, da::side128::SMEM_BYTES, stream>>>(
           k1_128, k2_128, v_128, q1_64, q2_64, da_64, a);
       DA_CUDA(cudaGetLastError());
     }
     if (stages & DIFFATTN_STAGE_DQ) {
-      if ((rc = set_smem(da::diffattn_bwd_side128_kernel<true>, da::side128::SMEM_BYTES))) return rc;
+      if ((rc = set_smem(da::diffattn_bwd_side128_kernel<true, BF>, da::side128::SMEM_BYTES))) return rc;
       dim3 g3(n_tiles, (unsigned)bh, 2);
-      da::diffattn_bwd_side128_kernel<true><<<g3, da::side128::NUM_THREADS, da::side128::SMEM_BYTES, stream>>>(
+      da::diffattn_bwd_side128_kernel<true, BF><<<g3, da::side128::NUM_THREADS, da::side128::SMEM_BYTES, stream>>>(
           q1_128, q2_128, da_128, k1_64, k2_64, v_64, a);
       DA_CUDA(cudaGetLastError());
     }
@@ -259,29 +262,49 @@ int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages) {
   }
   CUtensorMap mq1, mq2, mk1, mk2, mv, mda;
   // 2. dK, dV: key/value tiles of 128 rows resident, query-side tiles of 64 rows streamed
-  if ((rc = make_map(&mq1, p->q1, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 64, "q1"))) return rc;
-  if ((rc = make_map(&mq2, p->q2, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 64, "q2"))) return rc;
-  if ((rc = make_map(&mk1, p->k1, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "k1"))) return rc;
-  if ((rc = make_map(&mk2, p->k2, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "k2"))) return rc;
-  if ((rc = make_map(&mv, p->v, DV, p->N, p->H, p->B, p->v_stride_n, p->v_stride_h, p->v_stride_b, 128, "v"))) return rc;
-  if ((rc = make_map(&mda, a.da, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 64, "dA"))) return rc;
-  if ((rc = set_smem(da::diffattn_bwd_dkdv64_kernel, da::dkdv64::SMEM_BYTES))) return rc;
+  if ((rc = make_map<BF>(&mq1, p->q1, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 64, "q1"))) return rc;
+  if ((rc = make_map<BF>(&mq2, p->q2, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 64, "q2"))) return rc;
+  if ((rc = make_map<BF>(&mk1, p->k1, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "k1"))) return rc;
+  if ((rc = make_map<BF>(&mk2, p->k2, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "k2"))) return rc;
+  if ((rc = make_map<BF>(&mv, p->v, DV, p->N, p->H, p->B, p->v_stride_n, p->v_stride_h, p->v_stride_b, 128, "v"))) return rc;
+  if ((rc = make_map<BF>(&mda, a.da, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 64, "dA"))) return rc;
+  if ((rc = set_smem(da::diffattn_bwd_dkdv64_kernel<BF>, da::dkdv64::SMEM_BYTES))) return rc;
   if (stages & DIFFATTN_STAGE_DKDV) {
     dim3 grid(n_tiles, (unsigned)bh);
-    da::diffattn_bwd_dkdv64_kernel<<<grid, da::dkdv64::NUM_THREADS, da::dkdv64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, mda, a);
+    da::diffattn_bwd_dkdv64_kernel<BF><<<grid, da::dkdv64::NUM_THREADS, da::dkdv64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, mda, a);
     DA_CUDA(cudaGetLastError());
   }
   // 3. dQ: query tiles of 128 rows resident, key/value tiles of 128 rows streamed
-  if ((rc = make_map(&mq1, p->q1, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "q1"))) return rc;
-  if ((rc = make_map(&mq2, p->q2, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "q2"))) return rc;
-  if ((rc = make_map(&mda, a.da, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 128, "dA"))) return rc;
-  if ((rc = set_smem(da::diffattn_bwd_dq64_kernel, da::dq64::SMEM_BYTES))) return rc;
+  if ((rc = make_map<BF>(&mq1, p->q1, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "q1"))) return rc;
+  if ((rc = make_map<BF>(&mq2, p->q2, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "q2"))) return rc;
+  if ((rc = make_map<BF>(&mda, a.da, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 128, "dA"))) return rc;
+  if ((rc = set_smem(da::diffattn_bwd_dq64_kernel<BF>, da::dq64::SMEM_BYTES))) return rc;
   if (stages & DIFFATTN_STAGE_DQ) {
     dim3 grid(n_tiles, (unsigned)bh);
-    da::diffattn_bwd_dq64_kernel<<<grid, da::dq64::NUM_THREADS, da::dq64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, mda, a);
+    da::diffattn_bwd_dq64_kernel<BF><<<grid, da::dq64::NUM_THREADS, da::dq64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, mda, a);
     DA_CUDA(cudaGetLastError());
   }
   return DIFFATTN_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int diffattn_fwd(const DiffAttnParams* p) {
+  const int rc = check_common(p, false);
+  if (rc < 0) return rc;
+  if (rc == 1) return DIFFATTN_OK;
+  return p->io_dtype == DIFFATTN_IO_BF16 ? fwd_impl<true>(p) : fwd_impl<false>(p);
+}
+
+int diffattn_bwd(const DiffAttnParams* p) { return diffattn_bwd_stages(p, DIFFATTN_STAGE_ALL); }
+
+int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages) {
+  const int rc = check_common(p, true);
+  if (rc < 0) return rc;
+  if (rc == 1) return DIFFATTN_OK;
+  return p->io_dtype == DIFFATTN_IO_BF16 ? bwd_impl<true>(p, stages) : bwd_impl<false>(p, stages);
 }
 
 // ---- allocation-free backward: scratch in a file-scope device array -------------------------------

@@ -19,7 +19,7 @@
 namespace da {
 
 struct FwdArgs {
-  __half* y;          // [B*H, N, 2D] dense
+  __half* y;          // [B*H, N, 2D] dense; "__half" stands for a 16-bit element here: fp16, or bf16 in the BF kernels
   __half* a2;         // [B*H, N, 2D] dense, branch-2 output P2 V (kept for the backward)
   float* lse1;        // [B*H, N] natural-log logsumexp of s Q1 K1^T
   float* lse2;
@@ -37,7 +37,9 @@ struct FwdArgs {
 };
 
 __device__ __forceinline__ float load_lambda(const void* p, int dtype) {
-  return dtype == 0 ? __half2float(*reinterpret_cast<const __half*>(p)) : *reinterpret_cast<const float*>(p);
+  if (dtype == 0) return __half2float(*reinterpret_cast<const __half*>(p));
+  if (dtype == 2) return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(p));
+  return *reinterpret_cast<const float*>(p);
 }
 
 #ifdef DA_TIMING
@@ -93,6 +95,7 @@ static_assert(sizeof(Misc) <= MISC_BYTES, "misc area too small");
 
 __device__ __forceinline__ float max3(float a, float b, float c) { return fmaxf(fmaxf(a, b), c); }
 
+template <bool BF>   // BF: tensors are bf16 instead of fp16
 __global__ void __launch_bounds__(fwd64::NUM_THREADS, 1)
 diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
                       const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k2,
@@ -162,7 +165,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     // Sub-tile t goes to buffer t & 1, which is free once P_b V of sub-tile t-2 has completed, so the
     // scores of the next sub-tile are ready while the softmax warpgroups work on the current one.
     if (elect_one()) {
-      constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0);   // both operands K-major
+      constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0, BF);   // both operands K-major
       constexpr uint32_t HALF = (SUB * 128) >> 4;               // 64 rows of 128 bytes, in descriptor units
       const uint32_t q1_lo = sdesc_lo(smem_u32(smem + OFF_Q1)), q2_lo = sdesc_lo(smem_u32(smem + OFF_Q2));
       const uint32_t k_lo0 = sdesc_lo(smem_u32(smem + OFF_K));
@@ -196,7 +199,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     // ------------------- P V issuer of one branch: O_b += P_b(t) V(sub-tile t) -------------------
     if (elect_one()) {
       const int br = warp - WARP_PV;
-      constexpr uint32_t IDESC_O = make_idesc(BM, DV, 0, 1);    // V is MN-major
+      constexpr uint32_t IDESC_O = make_idesc(BM, DV, 0, 1, BF);    // V is MN-major
       constexpr uint32_t HALF = (SUB * 128) >> 4;
       const uint32_t v_lo0 = sdesc_lo(smem_u32(smem + OFF_V), V_BYTES / 2);
       const uint32_t t_o = tmem_base + T_O + br * 128, t_p = tmem_base + br * 128;
@@ -298,7 +301,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
 #endif
           sum[(2 * i) & 3] += p0;
           sum[(2 * i + 1) & 3] += p1;
-          pk[i] = pack_half2(p0, p1);
+          pk[i] = pack2<BF>(p0, p1);
           mx[i & 3] = max3(mx[i & 3], __uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]));
         }
       } else {
@@ -336,7 +339,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
           const float p1 = ex2(fmaf(__uint_as_float(sr[2 * i + 1]), sl2, neg));
           sum[(2 * i) & 3] += p0;
           sum[(2 * i + 1) & 3] += p1;
-          pk[i] = pack_half2(p0, p1);
+          pk[i] = pack2<BF>(p0, p1);
         }
       }
       l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
@@ -393,14 +396,14 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         uint4 yv, av;
-        yv.x = pack_half2(__uint_as_float(o1[8 * i + 0]) * yscale, __uint_as_float(o1[8 * i + 1]) * yscale);
-        yv.y = pack_half2(__uint_as_float(o1[8 * i + 2]) * yscale, __uint_as_float(o1[8 * i + 3]) * yscale);
-        yv.z = pack_half2(__uint_as_float(o1[8 * i + 4]) * yscale, __uint_as_float(o1[8 * i + 5]) * yscale);
-        yv.w = pack_half2(__uint_as_float(o1[8 * i + 6]) * yscale, __uint_as_float(o1[8 * i + 7]) * yscale);
-        av.x = pack_half2(__uint_as_float(o2[8 * i + 0]), __uint_as_float(o2[8 * i + 1]));
-        av.y = pack_half2(__uint_as_float(o2[8 * i + 2]), __uint_as_float(o2[8 * i + 3]));
-        av.z = pack_half2(__uint_as_float(o2[8 * i + 4]), __uint_as_float(o2[8 * i + 5]));
-        av.w = pack_half2(__uint_as_float(o2[8 * i + 6]), __uint_as_float(o2[8 * i + 7]));
+        yv.x = pack2<BF>(__uint_as_float(o1[8 * i + 0]) * yscale, __uint_as_float(o1[8 * i + 1]) * yscale);
+        yv.y = pack2<BF>(__uint_as_float(o1[8 * i + 2]) * yscale, __uint_as_float(o1[8 * i + 3]) * yscale);
+        yv.z = pack2<BF>(__uint_as_float(o1[8 * i + 4]) * yscale, __uint_as_float(o1[8 * i + 5]) * yscale);
+        yv.w = pack2<BF>(__uint_as_float(o1[8 * i + 6]) * yscale, __uint_as_float(o1[8 * i + 7]) * yscale);
+        av.x = pack2<BF>(__uint_as_float(o2[8 * i + 0]), __uint_as_float(o2[8 * i + 1]));
+        av.y = pack2<BF>(__uint_as_float(o2[8 * i + 2]), __uint_as_float(o2[8 * i + 3]));
+        av.z = pack2<BF>(__uint_as_float(o2[8 * i + 4]), __uint_as_float(o2[8 * i + 5]));
+        av.w = pack2<BF>(__uint_as_float(o2[8 * i + 6]), __uint_as_float(o2[8 * i + 7]));
         yp[i] = yv;
         ap[i] = av;
       }

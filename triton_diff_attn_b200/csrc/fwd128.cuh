@@ -39,6 +39,7 @@ struct Misc {
 static_assert(sizeof(Misc) <= MISC_BYTES, "misc area too small");
 }  // namespace fwd128
 
+template <bool BF>
 __global__ void __launch_bounds__(fwd128::NUM_THREADS, 1)
 diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
                        const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k2,
@@ -96,8 +97,8 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
     }
   } else if (warp == 9) {
     if (elect_one()) {
-      constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0);
-      constexpr uint32_t IDESC_O = make_idesc(BM, 128, 0, 1);
+      constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0, BF);
+      constexpr uint32_t IDESC_O = make_idesc(BM, 128, 0, 1, BF);
       const uint32_t q1_lo = sdesc_lo(smem_u32(smem + OFF_Q1)), q2_lo = sdesc_lo(smem_u32(smem + OFF_Q2));
       const uint32_t st_lo0 = sdesc_lo(smem_u32(smem + OFF_STAGE));
       const uint32_t tb = tmem_base;
@@ -201,7 +202,7 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
             const float p1 = ex2(fmaf(__uint_as_float(sr[2 * i + 1]), sl2, neg));
             sum[(2 * i) & 3] += p0;
             sum[(2 * i + 1) & 3] += p1;
-            pk[i] = pack_half2(p0, p1);
+            pk[i] = pack2<BF>(p0, p1);
             mx[i & 3] = max3(mx[i & 3], __uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]));
           }
         } else {
@@ -237,7 +238,7 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
             const float p1 = ex2(fmaf(__uint_as_float(sr[2 * i + 1]), sl2, neg));
             sum[(2 * i) & 3] += p0;
             sum[(2 * i + 1) & 3] += p1;
-            pk[i] = pack_half2(p0, p1);
+            pk[i] = pack2<BF>(p0, p1);
           }
         }
         l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
@@ -282,10 +283,10 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           uint4 av;
-          av.x = pack_half2(__uint_as_float(o2[8 * i + 0]), __uint_as_float(o2[8 * i + 1]));
-          av.y = pack_half2(__uint_as_float(o2[8 * i + 2]), __uint_as_float(o2[8 * i + 3]));
-          av.z = pack_half2(__uint_as_float(o2[8 * i + 4]), __uint_as_float(o2[8 * i + 5]));
-          av.w = pack_half2(__uint_as_float(o2[8 * i + 6]), __uint_as_float(o2[8 * i + 7]));
+          av.x = pack2<BF>(__uint_as_float(o2[8 * i + 0]), __uint_as_float(o2[8 * i + 1]));
+          av.y = pack2<BF>(__uint_as_float(o2[8 * i + 2]), __uint_as_float(o2[8 * i + 3]));
+          av.z = pack2<BF>(__uint_as_float(o2[8 * i + 4]), __uint_as_float(o2[8 * i + 5]));
+          av.w = pack2<BF>(__uint_as_float(o2[8 * i + 6]), __uint_as_float(o2[8 * i + 7]));
           ap[i] = av;
         }
       }
@@ -295,16 +296,16 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             uint4 yv;
-            yv.x = pack_half2(__uint_as_float(o1[8 * i + 0]), __uint_as_float(o1[8 * i + 1]));
-            yv.y = pack_half2(__uint_as_float(o1[8 * i + 2]), __uint_as_float(o1[8 * i + 3]));
-            yv.z = pack_half2(__uint_as_float(o1[8 * i + 4]), __uint_as_float(o1[8 * i + 5]));
-            yv.w = pack_half2(__uint_as_float(o1[8 * i + 6]), __uint_as_float(o1[8 * i + 7]));
+            yv.x = pack2<BF>(__uint_as_float(o1[8 * i + 0]), __uint_as_float(o1[8 * i + 1]));
+            yv.y = pack2<BF>(__uint_as_float(o1[8 * i + 2]), __uint_as_float(o1[8 * i + 3]));
+            yv.z = pack2<BF>(__uint_as_float(o1[8 * i + 4]), __uint_as_float(o1[8 * i + 5]));
+            yv.w = pack2<BF>(__uint_as_float(o1[8 * i + 6]), __uint_as_float(o1[8 * i + 7]));
             yp[i] = yv;
           }
         }
       } else if (pass == 0) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) parked[i] = pack_half2(__uint_as_float(o1[2 * i]), __uint_as_float(o1[2 * i + 1]));
+        for (int i = 0; i < 32; ++i) parked[i] = pack2<BF>(__uint_as_float(o1[2 * i]), __uint_as_float(o1[2 * i + 1]));
       } else {
         const float rstd = rsqrtf(ssq_total * (1.f / DV) + args.eps);
         const float ys = args.out_scale * rstd;
@@ -316,15 +317,15 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
             uint32_t w[4];
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-              const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&parked[4 * i + c]));
-              w[c] = pack_half2(f.x * ys, f.y * ys);
+              const float2 f = unpack2<BF>(parked[4 * i + c]);
+              w[c] = pack2<BF>(f.x * ys, f.y * ys);
             }
             y0[i] = make_uint4(w[0], w[1], w[2], w[3]);
             uint4 yv;
-            yv.x = pack_half2(__uint_as_float(o1[8 * i + 0]) * ys, __uint_as_float(o1[8 * i + 1]) * ys);
-            yv.y = pack_half2(__uint_as_float(o1[8 * i + 2]) * ys, __uint_as_float(o1[8 * i + 3]) * ys);
-            yv.z = pack_half2(__uint_as_float(o1[8 * i + 4]) * ys, __uint_as_float(o1[8 * i + 5]) * ys);
-            yv.w = pack_half2(__uint_as_float(o1[8 * i + 6]) * ys, __uint_as_float(o1[8 * i + 7]) * ys);
+            yv.x = pack2<BF>(__uint_as_float(o1[8 * i + 0]) * ys, __uint_as_float(o1[8 * i + 1]) * ys);
+            yv.y = pack2<BF>(__uint_as_float(o1[8 * i + 2]) * ys, __uint_as_float(o1[8 * i + 3]) * ys);
+            yv.z = pack2<BF>(__uint_as_float(o1[8 * i + 4]) * ys, __uint_as_float(o1[8 * i + 5]) * ys);
+            yv.w = pack2<BF>(__uint_as_float(o1[8 * i + 6]) * ys, __uint_as_float(o1[8 * i + 7]) * ys);
             y1[i] = yv;
           }
         }

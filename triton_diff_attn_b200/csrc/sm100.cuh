@@ -4,6 +4,7 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_fp16.h>
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -156,12 +157,12 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
                : "memory");
 }
 
-// Instruction descriptor, kind::f16, fp16 A and B, fp32 accumulate.
-//   [4,6) D format (1 = f32)  [7,10) A format (0 = f16)  [10,13) B format (0 = f16)
+// Instruction descriptor, kind::f16, A and B both fp16 or both bf16, fp32 accumulate.
+//   [4,6) D format (1 = f32)  [7,10) A format (0 = f16, 1 = bf16)  [10,13) B format (same)
 //   [15] A major (0 = K, 1 = MN)  [16] B major  [17,23) N>>3  [24,29) M>>4
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n, int a_mn_major, int b_mn_major) {
-  return (1u << 4) | (uint32_t(a_mn_major) << 15) | (uint32_t(b_mn_major) << 16) | (uint32_t(n >> 3) << 17) |
-         (uint32_t(m >> 4) << 24);
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, int a_mn_major, int b_mn_major, bool bf16 = false) {
+  return (1u << 4) | (uint32_t(bf16) << 7) | (uint32_t(bf16) << 10) | (uint32_t(a_mn_major) << 15) |
+         (uint32_t(b_mn_major) << 16) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
 }
 
 // Shared-memory matrix descriptor, 128-byte swizzle.
@@ -249,6 +250,32 @@ __device__ __forceinline__ float ex2(float x) {
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
+}
+// 16-bit storage type of the tensors: BF = false fp16, BF = true bf16.  Two floats -> one packed word
+// (lo in the low half), round to nearest even, and back; one raw 16-bit element <-> float.
+template <bool BF>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (BF) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  } else {
+    return pack_half2(lo, hi);
+  }
+}
+template <bool BF>
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+  if constexpr (BF) return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+  else return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+template <bool BF>
+__device__ __forceinline__ float to_float16b(__half raw) {      // raw: 16 bits of either type
+  if constexpr (BF) return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(&raw));
+  else return __half2float(raw);
+}
+template <bool BF>
+__device__ __forceinline__ __half from_float16b(float x) {
+  if constexpr (BF) { __nv_bfloat16 b = __float2bfloat16_rn(x); return *reinterpret_cast<__half*>(&b); }
+  else return __float2half_rn(x);
 }
 
 }  // namespace da

@@ -30,13 +30,15 @@ def _check_inputs(q1, q2, k1, k2, v, lambda_scale):
             raise TypeError(f"{name} must be a tensor")
         if not t.is_cuda:
             raise RuntimeError(f"{name} must be a CUDA tensor: this operator has no CPU path")
-        if t.dtype != torch.float16:
-            raise ValueError(f"{name} must be float16 (got {t.dtype}); the kernels compute P in fp16 like "
-                             "the reference (src/kernel.py:175-176)")
+        if t.dtype not in (torch.float16, torch.bfloat16):
+            raise ValueError(f"{name} must be float16 (the reference's type: it computes P in fp16, "
+                             f"src/kernel.py:175-176) or bfloat16 (extension), got {t.dtype}")
+        if t.dtype != q1.dtype:
+            raise ValueError(f"{name} is {t.dtype} but q1 is {q1.dtype}: q1, q2, k1, k2 and v must share one dtype")
         if t.dim() != 4:
             raise ValueError(f"{name} must be [B, H, N, D]")
-    if lambda_scale.numel() != 1 or lambda_scale.dtype not in (torch.float16, torch.float32):
-        raise ValueError("lambda_scale must hold one float16 or float32 element")
+    if lambda_scale.numel() != 1 or lambda_scale.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        raise ValueError("lambda_scale must hold one float16, bfloat16 or float32 element")
     if lambda_scale.device != q1.device:
         raise RuntimeError("lambda_scale must live on the same device as q1")
     b, h, n, d = q1.shape
@@ -68,7 +70,8 @@ def _fill_common(p, q1, q2, k1, k2, v, lam, lambda_init, rms_norm, saved, causal
     p.v_stride_b, p.v_stride_h, p.v_stride_n = v.stride(0), v.stride(1), v.stride(2)
     p.q1, p.q2, p.k1, p.k2, p.v = (t.data_ptr() for t in (q1, q2, k1, k2, v))
     p.lambda_scale = lam.data_ptr()
-    p.lambda_dtype = _lib.LAMBDA_F16 if lam.dtype == torch.float16 else _lib.LAMBDA_F32
+    p.lambda_dtype = {torch.float16: _lib.LAMBDA_F16, torch.bfloat16: _lib.LAMBDA_BF16}.get(lam.dtype, _lib.LAMBDA_F32)
+    p.io_dtype = _lib.IO_BF16 if q1.dtype == torch.bfloat16 else _lib.IO_F16
     p.rms_norm = 1 if rms_norm else 0
     p.causal = 1 if causal else 0
     p.sm_scale = 1.0 / math.sqrt(d)          # reference src/layers.py:20-22 (D, not 2D)
@@ -91,7 +94,7 @@ class DiffAttnFunction(torch.autograd.Function):
         b, h, n, d = q1.shape
         dev = q1.device
         with torch.cuda.device(dev):
-            y = torch.empty((b, h, n, 2 * d), dtype=torch.float16, device=dev)
+            y = torch.empty((b, h, n, 2 * d), dtype=v.dtype, device=dev)
             a2 = torch.empty_like(y)
             lse1 = torch.empty((b, h, n), dtype=torch.float32, device=dev)
             lse2 = torch.empty_like(lse1)
@@ -110,11 +113,11 @@ class DiffAttnFunction(torch.autograd.Function):
         q1, q2, k1, k2, v, lam, y, a2, lse1, lse2, rstd = ctx.saved_tensors
         b, h, n, d = q1.shape
         dev = q1.device
-        dy = dy.to(torch.float16).contiguous()   # the kernels index dY densely (as src/kernel.py:278-280)
+        dy = dy.to(v.dtype).contiguous()   # the kernels index dY densely (as src/kernel.py:278-280)
         with torch.cuda.device(dev):
-            dq1 = torch.empty((b, h, n, d), dtype=torch.float16, device=dev)
+            dq1 = torch.empty((b, h, n, d), dtype=q1.dtype, device=dev)
             dq2, dk1, dk2 = torch.empty_like(dq1), torch.empty_like(dq1), torch.empty_like(dq1)
-            dv = torch.empty((b, h, n, 2 * d), dtype=torch.float16, device=dev)
+            dv = torch.empty((b, h, n, 2 * d), dtype=v.dtype, device=dev)
             dlam = torch.zeros(1, dtype=torch.float32, device=dev)
             p = _lib.new_params()
             _fill_common(p, q1, q2, k1, k2, v, lam, ctx.lambda_init, ctx.rms_norm, (y, a2, lse1, lse2, rstd), ctx.causal)
