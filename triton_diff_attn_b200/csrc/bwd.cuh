@@ -186,7 +186,8 @@ __global__ void __launch_bounds__(dkdv64::NUM_THREADS, 1)
 diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
                            const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k2,
                            const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_da,
-                           const BwdArgs args) {
+                           const __grid_constant__ CUtensorMap tm_dk1, const __grid_constant__ CUtensorMap tm_dk2,
+                           const __grid_constant__ CUtensorMap tm_dv, const BwdArgs args) {
   using namespace dkdv64;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -399,27 +400,36 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
     tc_fence_after();
     // warpgroup g reads accumulator columns [64g, 64g+64): g = 0,1 -> the two halves of dV, g = 2 -> dK1, g = 3 -> dK2
     uint32_t acc[64];
-    const size_t grow = size_t(bh) * args.n + size_t(kv_tile) * BKV + row;
-    ok = ok && (kv_tile * BKV + row < args.n);          // key rows past the sequence end are dropped
     tmem_ld32(tb + g * 64, acc);
     tmem_ld32(tb + g * 64 + 32, acc + 32);
     tc_wait_ld();
-    const int d_real = args.d, dv_real = 2 * args.d;
-    // real columns among this warpgroup's 64: dV half g holds columns [64g, 64g+64) of dv_real; dK holds d_real
-    const int ncols = g < 2 ? (dv_real - g * 64 < 64 ? dv_real - g * 64 : 64) : d_real;
-    if (ok && !*abort_flag && ncols > 0) {
+    // The gradients leave through shared memory and the TMA engine (row-per-thread global stores of 16-byte
+    // pieces are several times slower): each warpgroup lays its 64 columns into a swizzled [128][64] tile over
+    // the resident K1 / K2 / V tiles, which no MMA reads any more, and one of its threads stores the tile.
+    // The engine clips at the tensor's bounds: key rows past the sequence end and, for head dim 32, the
+    // padding columns are not written.
+    {
       const float s = g < 2 ? 1.f : args.sm_scale;
-      __half* base = g < 2 ? args.dv + grow * dv_real + g * 64 : (g == 2 ? args.dk1 : args.dk2) + grow * d_real;
-      uint4* p = reinterpret_cast<uint4*>(base);
+      uint8_t* tile = smem + ((g + 2) & 3) * K_BYTES;     // g = 0,1 -> the two halves of V; 2 -> K1; 3 -> K2
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        if (8 * i >= ncols) break;
         uint4 v;
         v.x = pack2<BF>(__uint_as_float(acc[8 * i + 0]) * s, __uint_as_float(acc[8 * i + 1]) * s);
         v.y = pack2<BF>(__uint_as_float(acc[8 * i + 2]) * s, __uint_as_float(acc[8 * i + 3]) * s);
         v.z = pack2<BF>(__uint_as_float(acc[8 * i + 4]) * s, __uint_as_float(acc[8 * i + 5]) * s);
         v.w = pack2<BF>(__uint_as_float(acc[8 * i + 6]) * s, __uint_as_float(acc[8 * i + 7]) * s);
-        p[i] = v;
+        st_swizzled_chunk(tile, row, i, v);
+      }
+      fence_proxy_async_smem();
+      named_bar_sync(1 + g, 128);
+      const int dv_real = 2 * args.d;
+      if ((warp & 3) == 0 && elect_one()) {
+        if (!*abort_flag && (g != 1 || dv_real > 64)) {
+          const CUtensorMap* map = g < 2 ? &tm_dv : (g == 2 ? &tm_dk1 : &tm_dk2);
+          tma_store_4d(tile, map, g == 1 ? 64 : 0, kv_tile * BKV, bh, 0);
+          tma_store_commit();
+          tma_store_wait_read();
+        }
       }
     }
   }
@@ -469,6 +479,7 @@ __global__ void __launch_bounds__(dq64::NUM_THREADS, 1)
 diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
                          const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k2,
                          const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_da,
+                         const __grid_constant__ CUtensorMap tm_dq1, const __grid_constant__ CUtensorMap tm_dq2,
                          const BwdArgs args) {
   using namespace dq64;
   extern __shared__ uint8_t smem_raw[];
@@ -657,9 +668,11 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
     uint32_t acc[32];
     tmem_ld32(tb + (br ? T_DQ2 : T_DQ1) + half * 32, acc);
     tc_wait_ld();
-    if (ok && !*abort_flag && half * 32 < args.d && q_tile * BM + row < args.n) {
+    // dQ_b leaves through a swizzled [128][64] tile laid over the resident Q_b tile (its MMAs are complete) and
+    // one TMA store per branch; the engine drops query rows past the sequence end and padding columns.
+    {
       const float sc = args.sm_scale;
-      uint4* p = reinterpret_cast<uint4*>((br ? args.dq2 : args.dq1) + grow * args.d + half * 32);
+      uint8_t* tile = smem + (br ? OFF_Q2 : OFF_Q1);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         uint4 v;
@@ -667,7 +680,16 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
         v.y = pack2<BF>(__uint_as_float(acc[8 * i + 2]) * sc, __uint_as_float(acc[8 * i + 3]) * sc);
         v.z = pack2<BF>(__uint_as_float(acc[8 * i + 4]) * sc, __uint_as_float(acc[8 * i + 5]) * sc);
         v.w = pack2<BF>(__uint_as_float(acc[8 * i + 6]) * sc, __uint_as_float(acc[8 * i + 7]) * sc);
-        p[i] = v;
+        st_swizzled_chunk(tile, row, half * 4 + i, v);
+      }
+      fence_proxy_async_smem();
+      named_bar_sync(1 + br, 256);
+      if ((warp & 7) == 0 && elect_one()) {
+        if (!*abort_flag) {
+          tma_store_4d(tile, br ? &tm_dq2 : &tm_dq1, 0, q_tile * BM, bh, 0);
+          tma_store_commit();
+          tma_store_wait_read();
+        }
       }
     }
   }

@@ -43,7 +43,9 @@ __device__ __forceinline__ float load_lambda(const void* p, int dtype) {
 }
 
 #ifdef DA_TIMING
-__device__ long long g_timing[4096];
+__device__ long long g_timing[16384];
+__device__ __forceinline__ long long gtimer() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ int smid() { int r; asm volatile("mov.u32 %0, %smid;" : "=r"(r)); return r; }
 #define DA_TS(slot) do { if (tm_on) g_timing[tm_base + (slot)] = clock64(); } while (0)
 #else
 #define DA_TS(slot) do { } while (0)
@@ -67,6 +69,8 @@ constexpr int OFF_V = OFF_K + KS * 2 * K_BYTES;
 constexpr int OFF_MISC = OFF_V + VS * V_BYTES;           // barriers, coefficients
 constexpr int MISC_BYTES = 4096;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024; // +1024 for manual alignment
+constexpr int STORE_TILE_BYTES = BM * 128;               // epilogue staging: 128 rows x 64 columns x 2 bytes
+static_assert(4 * STORE_TILE_BYTES <= KS * 2 * K_BYTES, "the y / a2 staging tiles reuse the K ring");
 // warps 0-7 softmax; 8 TMA producer; 9 S issuer (both branches); 10, 11 P V issuers of branch 1, 2: one role
 // warp per scheduler (warp % 4).  A single warp issuing every MMA slows the row quarter that shares its
 // scheduler by about 30 %, and every barrier waits for that quarter.  Twelve warps keep three per scheduler,
@@ -99,7 +103,8 @@ template <bool BF>   // BF: tensors are bf16 instead of fp16
 __global__ void __launch_bounds__(fwd64::NUM_THREADS, 1)
 diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
                       const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k2,
-                      const __grid_constant__ CUtensorMap tm_v, const FwdArgs args) {
+                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_y,
+                      const __grid_constant__ CUtensorMap tm_a2, const FwdArgs args) {
   using namespace fwd64;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -110,6 +115,11 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
   const int lane = threadIdx.x & 31;
   const int q_tile = blockIdx.x;
   const int bh = blockIdx.y;
+#ifdef DA_TIMING
+  const int cta_lin = blockIdx.y * gridDim.x + blockIdx.x;
+  const bool life_on = threadIdx.x == 0 && cta_lin < 2048;
+  if (life_on) { g_timing[4096 + 6 * cta_lin] = smid(); g_timing[4096 + 6 * cta_lin + 1] = gtimer(); }
+#endif
   const int b_idx = bh / args.h;
   const int h_idx = bh % args.h;
   // the last tile may reach past N (TMA fills those rows with zeros); with a causal mask the tiles right of
@@ -250,6 +260,9 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
       if (!mbar_wait(&misc->s_full[br][t & 1], (t >> 1) & 1, abort_flag, 301 + br, t)) { ok = false; break; }
       tc_fence_after();
       DA_TS(1);
+#ifdef DA_TIMING
+      if (life_on && t == 0) g_timing[4096 + 6 * cta_lin + 2] = gtimer();
+#endif
 #ifdef DA_NOSOFTMAX
       tc_fence_before();
       mbar_arrive(&misc->p_full[br][t & 1]);
@@ -356,9 +369,15 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
       DA_TS(6);
     }
 
+#ifdef DA_TIMING
+    if (life_on) g_timing[4096 + 6 * cta_lin + 3] = gtimer();
+#endif
     // ---- epilogue: every thread runs every barrier; only the global writes depend on `ok`
     ok = ok && mbar_wait(&misc->o_full, 0, abort_flag, 311 + br);
     tc_fence_after();
+#ifdef DA_TIMING
+    if (life_on) g_timing[4096 + 6 * cta_lin + 4] = gtimer();
+#endif
     const float inv_l = 1.f / l_run;
     if (br == 0) misc->coef1[row] = inv_l; else misc->coef2[row] = inv_l;
     named_bar_sync(1, 256);
@@ -390,9 +409,12 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     const float yscale = args.rms_norm ? args.out_scale * rstd : 1.f;
     const size_t grow = size_t(bh) * args.n + size_t(q_tile) * BM + row;
     ok = ok && (q_tile * BM + row < args.n);            // rows past the sequence end are computed on zero padding and dropped
-    if (ok && !*abort_flag && br * 64 < dv_real) {
-      uint4* yp = reinterpret_cast<uint4*>(args.y + grow * dv_real + br * 64);
-      uint4* ap = reinterpret_cast<uint4*>(args.a2 + grow * dv_real + br * 64);
+    // y and a2 leave through shared memory and the TMA engine: each thread lays its 64 columns into a swizzled
+    // [128 rows][64 columns] tile in the (now idle) K ring, and one thread per warpgroup stores the two tiles.
+    // (Row-per-thread global stores of 16-byte pieces cost 3.6 us per CTA, 8 % of the kernel at N = 4096.)
+    {
+      uint8_t* ytile = smem + OFF_K + br * (2 * STORE_TILE_BYTES);
+      uint8_t* atile = ytile + STORE_TILE_BYTES;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         uint4 yv, av;
@@ -404,8 +426,18 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
         av.y = pack2<BF>(__uint_as_float(o2[8 * i + 2]), __uint_as_float(o2[8 * i + 3]));
         av.z = pack2<BF>(__uint_as_float(o2[8 * i + 4]), __uint_as_float(o2[8 * i + 5]));
         av.w = pack2<BF>(__uint_as_float(o2[8 * i + 6]), __uint_as_float(o2[8 * i + 7]));
-        yp[i] = yv;
-        ap[i] = av;
+        st_swizzled_chunk(ytile, row, i, yv);
+        st_swizzled_chunk(atile, row, i, av);
+      }
+      fence_proxy_async_smem();
+      named_bar_sync(2 + br, 128);
+      if ((warp & 3) == 0 && elect_one()) {
+        if (!*abort_flag && br * 64 < dv_real) {
+          tma_store_4d(ytile, &tm_y, br * 64, q_tile * BM, bh, 0);
+          tma_store_4d(atile, &tm_a2, br * 64, q_tile * BM, bh, 0);
+          tma_store_commit();
+          tma_store_wait_read();
+        }
       }
     }
     if (ok && !*abort_flag) {
@@ -425,6 +457,9 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
+#ifdef DA_TIMING
+  if (life_on) g_timing[4096 + 6 * cta_lin + 5] = gtimer();
+#endif
 }
 
 }  // namespace da

@@ -111,6 +111,24 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
+// 4-D tiled store shared -> global (bulk-group completion).  The engine clips the box at the tensor's bounds, so
+// rows past the sequence end and columns past a narrow head are simply not written.  Coordinates must be >= 0.
+__device__ __forceinline__ void tma_store_4d(const void* smem_src, const CUtensorMap* map, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(map), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// returns once the engine has read the shared-memory sources of every committed store (the global writes
+// themselves complete by the end of the kernel)
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// generic-proxy writes to shared memory -> visible to the async proxy (TMA, tcgen05.mma operand reads)
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// One 16-byte chunk of a [rows][64 x 16-bit] tile in the 128-byte-swizzled layout TMA and the MMA descriptors
+// use: row r occupies 128 bytes, chunk c of it sits at position c ^ (r & 7).  The tile base is 1024-aligned.
+__device__ __forceinline__ void st_swizzled_chunk(uint8_t* tile, int r, int c, uint4 v) {
+  *reinterpret_cast<uint4*>(tile + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
