@@ -274,12 +274,10 @@ int bwd_impl(const DiffAttnParams* p, int32_t stages) {
   if ((rc = make_map<BF>(&mv, p->v, DV, p->N, p->H, p->B, p->v_stride_n, p->v_stride_h, p->v_stride_b, 128, "v"))) return rc;
   if ((rc = make_map<BF>(&mda, a.da, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 64, "dA"))) return rc;
   // gradients leave through TMA stores: dense [B*H, N, D] / [B*H, N, 2D] maps with 128-row boxes
-  CUtensorMap mdq1, mdq2, mdk1, mdk2, mdv;
+  CUtensorMap mdk1, mdk2, mdv;
   auto grad_map = [&](CUtensorMap* m, void* ptr, int cols, const char* nm) {
     return make_map<BF>(m, ptr, cols, p->N, (int)bh, 1, cols, (int64_t)p->N * cols, (int64_t)p->N * cols * bh, 128, nm);
   };
-  if ((rc = grad_map(&mdq1, p->dq1, D, "dq1"))) return rc;
-  if ((rc = grad_map(&mdq2, p->dq2, D, "dq2"))) return rc;
   if ((rc = grad_map(&mdk1, p->dk1, D, "dk1"))) return rc;
   if ((rc = grad_map(&mdk2, p->dk2, D, "dk2"))) return rc;
   if ((rc = grad_map(&mdv, p->dv, DV, "dv"))) return rc;
@@ -296,7 +294,7 @@ int bwd_impl(const DiffAttnParams* p, int32_t stages) {
   if ((rc = set_smem(da::diffattn_bwd_dq64_kernel<BF>, da::dq64::SMEM_BYTES))) return rc;
   if (stages & DIFFATTN_STAGE_DQ) {
     dim3 grid(n_tiles, (unsigned)bh);
-    da::diffattn_bwd_dq64_kernel<BF><<<grid, da::dq64::NUM_THREADS, da::dq64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, mda, mdq1, mdq2, a);
+    da::diffattn_bwd_dq64_kernel<BF><<<grid, da::dq64::NUM_THREADS, da::dq64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, mda, a);
     DA_CUDA(cudaGetLastError());
   }
   return DIFFATTN_OK;

@@ -69,6 +69,7 @@ constexpr int OFF_V = OFF_K + KS * 2 * K_BYTES;
 constexpr int OFF_MISC = OFF_V + VS * V_BYTES;           // barriers, coefficients
 constexpr int MISC_BYTES = 4096;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024; // +1024 for manual alignment
+constexpr int PRELOAD = 2;                               // key/value tiles requested before the setup barrier (<= KS, VS)
 constexpr int STORE_TILE_BYTES = BM * 128;               // epilogue staging: 128 rows x 64 columns x 2 bytes
 static_assert(4 * STORE_TILE_BYTES <= KS * 2 * K_BYTES, "the y / a2 staging tiles reuse the K ring");
 // warps 0-7 softmax; 8 TMA producer; 9 S issuer (both branches); 10, 11 P V issuers of branch 1, 2: one role
@@ -139,8 +140,20 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     mbar_init(&misc->o_full, 2);
     misc->abort_flag = 0;
     mbar_init_fence();
-    tma_prefetch_desc(&tm_q1); tma_prefetch_desc(&tm_q2); tma_prefetch_desc(&tm_k1);
-    tma_prefetch_desc(&tm_k2); tma_prefetch_desc(&tm_v);
+    // The first loads go out before the CTA-wide setup barrier (TMEM allocation, everyone's arrival): the
+    // barriers they complete on are initialised above, and the first pass over a ring needs no "empty" wait.
+    mbar_expect_tx(&misc->bar_q, 2 * Q_BYTES);
+    tma_load_4d(smem + OFF_Q1, &tm_q1, &misc->bar_q, 0, q_tile * BM, h_idx, b_idx);
+    tma_load_4d(smem + OFF_Q2, &tm_q2, &misc->bar_q, 0, q_tile * BM, h_idx, b_idx);
+    for (int j = 0; j < PRELOAD && j < nkv; ++j) {
+      mbar_expect_tx(&misc->k_full[j], 2 * K_BYTES);
+      tma_load_4d(smem + OFF_K + j * 2 * K_BYTES, &tm_k1, &misc->k_full[j], 0, j * BN, h_idx, b_idx);
+      tma_load_4d(smem + OFF_K + j * 2 * K_BYTES + K_BYTES, &tm_k2, &misc->k_full[j], 0, j * BN, h_idx, b_idx);
+      mbar_expect_tx(&misc->v_full[j], V_BYTES);
+      tma_load_4d(smem + OFF_V + j * V_BYTES, &tm_v, &misc->v_full[j], 0, j * BN, h_idx, b_idx);
+      tma_load_4d(smem + OFF_V + j * V_BYTES + V_BYTES / 2, &tm_v, &misc->v_full[j], 64, j * BN, h_idx, b_idx);
+    }
+    tma_prefetch_desc(&tm_y); tma_prefetch_desc(&tm_a2);
   }
   if (warp == WARP_S) {
     tmem_alloc(&misc->tmem_slot, 512);
@@ -153,10 +166,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
   if (warp == WARP_TMA) {
     // ------------------------------- TMA producer -------------------------------
     if (elect_one()) {
-      mbar_expect_tx(&misc->bar_q, 2 * Q_BYTES);
-      tma_load_4d(smem + OFF_Q1, &tm_q1, &misc->bar_q, 0, q_tile * BM, h_idx, b_idx);
-      tma_load_4d(smem + OFF_Q2, &tm_q2, &misc->bar_q, 0, q_tile * BM, h_idx, b_idx);
-      for (int j = 0; j < nkv; ++j) {
+      for (int j = PRELOAD; j < nkv; ++j) {
         const int ks = j % KS, vs = j % VS;
         if (!mbar_wait(&misc->k_empty[ks], ((j / KS) & 1) ^ 1, abort_flag, 101, j)) break;
         mbar_expect_tx(&misc->k_full[ks], 2 * K_BYTES);
