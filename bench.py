@@ -292,6 +292,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--io-dtype", default="fp16", choices=["fp16", "bf16"],
                     help="16-bit type of the tensors: fp16 (the reference's and the headline) or bf16 (extension)")
+    ap.add_argument("--dropout", type=float, default=0.0, help="attention dropout probability (extension); flops are "
+                    "credited as without dropout")
     ap.add_argument("--causal", action="store_true", help="causal mask (extension); flops credited for the visible "
                     "N(N+1)/2 pairs only")
     ap.add_argument("--sweep-reference-protocol", action="store_true",
@@ -344,7 +346,8 @@ def main():
     dv = torch.empty_like(v)
     dlam = torch.zeros(1, dtype=torch.float32, device=dev)
     p = _lib.new_params()
-    layers._fill_common(p, q1, q2, k1, k2, v, lam_t, lam_init, rms, (y, a2, lse1, lse2, rstd), args.causal)
+    layers._fill_common(p, q1, q2, k1, k2, v, lam_t, lam_init, rms, (y, a2, lse1, lse2, rstd), args.causal,
+                        layers.dropout_threshold(args.dropout), 20241125)
     ws_bytes = int(_lib.lib.diffattn_workspace_bytes(p))
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
     p.dy = dy.data_ptr()
@@ -471,13 +474,14 @@ def main():
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": args.io_dtype,
         "data": "synthetic",
         "config": {"workload": f"{args.workload}: B={b} H={h} N={n} D={d} (v width {2 * d}) per GPU, rms_norm={rms}, "
-                               f"lambda={lam}, lambda_init={lam_init}, fwd+bwd" + (", causal" if args.causal else ""),
+                               f"lambda={lam}, lambda_init={lam_init}, fwd+bwd" + (", causal" if args.causal else "")
+                               + (f", dropout {layers.dropout_threshold(args.dropout)}/256" if args.dropout else ""),
                    "sharding": f"(batch*head) shards, {world} rank(s), no data-path collective; d(lambda) summed on host",
                    "l2": "inputs+outputs per step (~0.8 GB) exceed the 126 MB L2; no explicit flush"},
         "fwd": {"ms": ms_fwd, "tflops": f_fwd / (ms_fwd * 1e-3) / 1e12, "frac_nominal": f_fwd / (ms_fwd * 1e-3) / 1e12 / NOMINAL_TFLOPS},
         "bwd": {"ms": ms_bwd, "tflops": f_bwd / (ms_bwd * 1e-3) / 1e12, "frac_nominal": f_bwd / (ms_bwd * 1e-3) / 1e12 / NOMINAL_TFLOPS},
         "fwd_bwd_frac_nominal": value / world / NOMINAL_TFLOPS,
-        "kernels": kernels, "roofline": roofline, "clocks": clocks, "gpu_launches": (6 if d == 128 else 4) * args.steps,
+        "kernels": kernels, "roofline": roofline, "clocks": clocks, "gpu_launches": (5 if d == 128 else 4) * args.steps,   # fwd, pre, then dK/dV + dQ (D<=64) or dV + dK + dQ (D=128)
         "dlambda_host_sum": dl_total,
     }
     if e2e:

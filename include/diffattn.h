@@ -70,7 +70,11 @@ typedef struct DiffAttnParams {
   void* workspace;                 /* diffattn_workspace_bytes() bytes, 256-byte aligned */
   uint64_t workspace_bytes;
   int32_t io_dtype;                /* DIFFATTN_IO_*: 0 = fp16 (the reference's type), 1 = bf16 */
-  int32_t reserved1;               /* must be 0 */
+  uint32_t dropout_threshold;      /* attention dropout (extension; the reference has none, README.md:2): 0 = off,
+                                      else 1..255 = round(256 p): a probability is dropped when its hash byte is
+                                      below the threshold, kept ones are scaled by 256/(256 - threshold).  The
+                                      backward must be given the forward's threshold and seed. */
+  uint64_t dropout_seed;           /* the mask is a pure function of (seed, batch*head, branch, row, column) */
 } DiffAttnParams;
 
 /* Forward.  Reads q1,q2,k1,k2,v,lambda_scale; writes y,a2,lse1,lse2,rstd.

@@ -27,6 +27,7 @@ from __future__ import annotations
 import math
 from typing import Dict, Optional
 
+import numpy as np
 import torch
 
 EPS = 1e-5  # src/kernel.py:50
@@ -38,9 +39,47 @@ def _lam(lambda_scale, dtype, device="cpu") -> torch.Tensor:
     return lambda_scale.detach().reshape(-1)[0].to(dtype=dtype, device=device)
 
 
+def _mix32(h: np.ndarray) -> np.ndarray:
+    """Two-multiply xorshift finaliser on uint32 arrays (wrap-around arithmetic), as in csrc/sm100.cuh."""
+    h = h.astype(np.uint32)
+    h = h ^ (h >> np.uint32(16))
+    h = (h * np.uint32(0x7feb352d)).astype(np.uint32)
+    h = h ^ (h >> np.uint32(15))
+    h = (h * np.uint32(0x846ca68b)).astype(np.uint32)
+    h = h ^ (h >> np.uint32(16))
+    return h
+
+
+def dropout_keep_mask(seed: int, bh: int, branch: int, n: int, threshold: int) -> np.ndarray:
+    """Keep decisions [n, n] (query row, key column) of attention dropout for one (batch*head, branch).
+
+    Restates the device rule (extension; the reference has no dropout, README.md:2): one 32-bit hash per 2x2
+    block, h = mix32(((row>>1)<<16 | (col>>1)) ^ key), key = mix32(seed_lo ^ mix32(seed_hi + 0x9E3779B9 (2 bh +
+    branch + 1))); position (row, col) is kept iff byte 2 (row&1) + (col&1) of h is >= threshold."""
+    with np.errstate(over="ignore"):
+        lo, hi = np.uint32(seed & 0xffffffff), np.uint32((seed >> 32) & 0xffffffff)
+        inner = np.array([(int(hi) + 0x9E3779B9 * (2 * bh + branch + 1)) & 0xffffffff], dtype=np.uint32)
+        key = _mix32(lo ^ _mix32(inner))[0]
+        r = np.arange(n, dtype=np.uint32)[:, None]
+        c = np.arange(n, dtype=np.uint32)[None, :]
+        h = _mix32((((r >> np.uint32(1)) << np.uint32(16)) | (c >> np.uint32(1))) ^ key)
+        byte = (np.uint32(2) * (r & np.uint32(1)) + (c & np.uint32(1))) * np.uint32(8)
+        return ((h >> byte) & np.uint32(0xff)) >= np.uint32(threshold)
+
+
+def dropout_multipliers(b: int, h: int, n: int, threshold: int, seed: int, dtype, device):
+    """(m1, m2): [b, h, n, n] tensors holding 0 (dropped) or 256/(256 - threshold) (kept) per branch."""
+    scale = 256.0 / (256 - threshold)
+    out = []
+    for br in (0, 1):
+        m = np.stack([dropout_keep_mask(seed, i, br, n, threshold) for i in range(b * h)]).reshape(b, h, n, n)
+        out.append(torch.from_numpy(m).to(device=device, dtype=dtype) * scale)
+    return out
+
+
 def forward(q1, q2, k1, k2, v, lambda_scale, lambda_init: float = 0.8, rms_norm: bool = False,
             dtype=torch.float32, round_p_half: bool = False, eps: float = EPS, device="cpu",
-            causal: bool = False) -> Dict[str, torch.Tensor]:
+            causal: bool = False, dropout_threshold: int = 0, dropout_seed: int = 0) -> Dict[str, torch.Tensor]:
     """Forward pass; returns Y and the intermediates the backward kernels save (src/layers.py:60-80).
 
     Keys: y, a (pre-norm), a1, a2 (per-branch P_b V), lse1, lse2 (natural-log logsumexp of S_b,
@@ -69,21 +108,28 @@ def forward(q1, q2, k1, k2, v, lambda_scale, lambda_init: float = 0.8, rms_norm:
     if round_p_half:
         p1 = p1.half().to(dtype)
         p2 = p2.half().to(dtype)
-    a1 = torch.matmul(p1, v)
-    a2 = torch.matmul(p2, v)
-    a = torch.matmul(p1 - lam * p2, v)                                 # layers.py:70-72
+    m1 = m2 = None
+    pd1, pd2 = p1, p2
+    if dropout_threshold:
+        # extension: P_b -> P_b * keep_b / (1 - p), after the softmax (its denominator sees every key)
+        m1, m2 = dropout_multipliers(q1.shape[0], q1.shape[1], q1.shape[2], dropout_threshold, dropout_seed, dtype, s1.device)
+        pd1, pd2 = p1 * m1, p2 * m2
+    a1 = torch.matmul(pd1, v)
+    a2 = torch.matmul(pd2, v)
+    a = torch.matmul(pd1 - lam * pd2, v)                               # layers.py:70-72
     rstd = torch.rsqrt((a * a).mean(dim=-1) + eps)                     # kernel.py:196-197
     if rms_norm:
         y = (1.0 - lambda_init) * a * rstd[..., None]                  # layers.py:75-78
     else:
         y = a                                                          # layers.py:80
     return {"y": y, "a": a, "a1": a1, "a2": a2, "lse1": lse1, "lse2": lse2, "rstd": rstd,
-            "p1": p1, "p2": p2}
+            "p1": p1, "p2": p2, "m1": m1, "m2": m2}
 
 
 def backward_closed_form(q1, q2, k1, k2, v, lambda_scale, dy, lambda_init: float = 0.8,
                          rms_norm: bool = False, dtype=torch.float32,
-                         eps: float = EPS, device="cpu", causal: bool = False) -> Dict[str, torch.Tensor]:
+                         eps: float = EPS, device="cpu", causal: bool = False,
+                         dropout_threshold: int = 0, dropout_seed: int = 0) -> Dict[str, torch.Tensor]:
     """Closed-form gradients (no autograd).  Same quantities the reference's backward kernel forms
     (src/kernel.py:283-299 preprocess, :410-436 main loop), with the division-free d(lambda).
 
@@ -95,7 +141,8 @@ def backward_closed_form(q1, q2, k1, k2, v, lambda_scale, dy, lambda_init: float
         dQ_b = s dS_b K_b,  dK_b = s dS_b^T Q_b                       (kernel.py:423-424,435-436)
         dlam = - sum E_2
     """
-    f = forward(q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, dtype=dtype, eps=eps, device=device, causal=causal)
+    f = forward(q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, dtype=dtype, eps=eps, device=device, causal=causal,
+                dropout_threshold=dropout_threshold, dropout_seed=dropout_seed)
     q1, q2, k1, k2, v, dy = (t.detach().to(device, dtype) for t in (q1, q2, k1, k2, v, dy))
     lam = _lam(lambda_scale, dtype, device)
     d = q1.shape[-1]
@@ -110,9 +157,12 @@ def backward_closed_form(q1, q2, k1, k2, v, lambda_scale, dy, lambda_init: float
     dp = torch.matmul(da, v.transpose(2, 3))
     e1 = (da * f["a1"]).sum(-1, keepdim=True)
     e2 = (da * f["a2"]).sum(-1, keepdim=True)
-    dvv = torch.matmul((f["p1"] - lam * f["p2"]).transpose(2, 3), da)
-    ds1 = f["p1"] * (dp - e1)
-    ds2 = -lam * f["p2"] * (dp - e2)
+    # with dropout (multipliers m_b = keep_b / (1 - p)): P_b m_b feeds A_b and dV, and dP reaches S_b through m_b
+    m1 = f["m1"] if f["m1"] is not None else 1.0
+    m2 = f["m2"] if f["m2"] is not None else 1.0
+    dvv = torch.matmul((f["p1"] * m1 - lam * f["p2"] * m2).transpose(2, 3), da)
+    ds1 = f["p1"] * (m1 * dp - e1)
+    ds2 = -lam * f["p2"] * (m2 * dp - e2)
     out = {
         "dq1": s * torch.matmul(ds1, k1), "dq2": s * torch.matmul(ds2, k2),
         "dk1": s * torch.matmul(ds1.transpose(2, 3), q1), "dk2": s * torch.matmul(ds2.transpose(2, 3), q2),
@@ -124,7 +174,8 @@ def backward_closed_form(q1, q2, k1, k2, v, lambda_scale, dy, lambda_init: float
 
 def forward_backward_autograd(q1, q2, k1, k2, v, lambda_scale, dy, lambda_init: float = 0.8,
                               rms_norm: bool = False, dtype=torch.float32, round_p_half: bool = False,
-                              eps: float = EPS, num_threads: Optional[int] = None, causal: bool = False) -> Dict[str, torch.Tensor]:
+                              eps: float = EPS, num_threads: Optional[int] = None, causal: bool = False,
+                              dropout_threshold: int = 0, dropout_seed: int = 0) -> Dict[str, torch.Tensor]:
     """Forward + autograd backward of the literal op sequence of src/layers.py:60-80.
 
     This is the independent check of `backward_closed_form` and the function the CPU baseline times.
@@ -149,6 +200,9 @@ def forward_backward_autograd(q1, q2, k1, k2, v, lambda_scale, dy, lambda_init: 
         # straight-through is NOT used by the reference: .half() is differentiable as a cast
         p1 = p1.half().to(dtype)
         p2 = p2.half().to(dtype)
+    if dropout_threshold:
+        m1, m2 = dropout_multipliers(lq1.shape[0], lq1.shape[1], lq1.shape[2], dropout_threshold, dropout_seed, dtype, "cpu")
+        p1, p2 = p1 * m1, p2 * m2
     a = torch.matmul(p1 - lam * p2, lv)
     if rms_norm:
         y = (1.0 - lambda_init) * a * torch.rsqrt((a * a).mean(-1, keepdim=True) + eps)

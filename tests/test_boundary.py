@@ -67,6 +67,7 @@ def test_null_and_struct(L):
     (lambda p: setattr(p, "k1", 0x10008), -6),
     (lambda p: setattr(p, "lambda_dtype", 9), -7),
     (lambda p: setattr(p, "io_dtype", 2), -7),
+    (lambda p: setattr(p, "dropout_threshold", 256), -3),
     (lambda p: setattr(p, "B", 70000), -3),
 ])
 def test_fwd_rejects(L, mutate, code):
@@ -137,3 +138,12 @@ def test_preprocess_formula_matches_oracle():
     e2 = (da * w["a2"]).sum(-1)
     e1 = (da * a).sum(-1) + 0.4 * e2
     assert torch.allclose(e1, w["e1"], rtol=1e-9, atol=1e-11)
+
+
+def test_dropout_probability_quantisation():
+    from triton_diff_attn_b200.layers import dropout_threshold
+    assert dropout_threshold(0.0) == 0 and dropout_threshold(0.25) == 64 and dropout_threshold(0.1) == 26
+    assert dropout_threshold(0.001) == 0            # below 1/512: off
+    for bad in (-0.1, 1.0, 0.999):
+        with pytest.raises(ValueError):
+            dropout_threshold(bad)

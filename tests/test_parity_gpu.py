@@ -28,11 +28,11 @@ def op():
     return pkg
 
 
-def run_gpu(pkg, q1, q2, k1, k2, v, dy, lam, lam_init, rms, lam_dtype=torch.float32, causal=False):
+def run_gpu(pkg, q1, q2, k1, k2, v, dy, lam, lam_init, rms, lam_dtype=torch.float32, causal=False, **extra):
     dev = torch.device("cuda", 0)
     leaves = [t.to(dev).clone().requires_grad_(True) for t in (q1, q2, k1, k2, v)]
     lam_t = torch.tensor([lam], dtype=lam_dtype, device=dev, requires_grad=True)
-    y = pkg.MultiheadDiffAttnKernel(*leaves, lam_t, lam_init, rms, causal=causal) if causal else \
+    y = pkg.MultiheadDiffAttnKernel(*leaves, lam_t, lam_init, rms, causal=causal, **extra) if (causal or extra) else \
         pkg.MultiheadDiffAttnKernel(*leaves, lam_t, lam_init, rms)
     y.backward(dy.to(dev))
     pkg.device_status(0)
@@ -177,6 +177,51 @@ def test_bfloat16_tensors(op, b, h, n, d, lam, lam_init, rms, causal, seed):
     check(got, want, loosen=8.0)
     # and it must not be the fp16 path fed with reinterpreted bits: measurably less exact than fp16, yet sane
     assert oracle.error_metrics(got["y"], want["y"])["rel_l2"] > 5e-4
+
+
+DROPOUT = [
+    # b, h, n, d, lam, lam_init, rms, causal, p, seed -- attention dropout (an extension: the reference has none, README.md:2)
+    (1, 2, 256, 64, 0.5, 0.8, True, False, 0.25, 91),
+    (2, 2, 512, 64, 0.5, 0.8, False, False, 0.1, 92),
+    (1, 2, 384, 32, 0.5, 0.8, True, False, 0.5, 93),
+    (1, 2, 512, 128, 0.7, 0.2, True, False, 0.25, 94),
+    (1, 2, 328, 64, -0.4, 0.8, True, True, 0.25, 95),
+    (1, 1, 1000, 128, 0.5, 0.8, False, True, 0.125, 96),
+]
+
+
+@pytest.mark.parametrize("b,h,n,d,lam,lam_init,rms,causal,p,seed", DROPOUT)
+def test_dropout_matches_oracle(op, b, h, n, d, lam, lam_init, rms, causal, p, seed):
+    """The keep mask is a pure function of (seed, batch*head, branch, row, column) that the oracle restates, so
+    outputs and gradients are compared at the usual fp16 tolerance: one wrong decision would miss it by far."""
+    th = op.layers.dropout_threshold(p)
+    drop_seed = 0x1234_5678_9ABC_DEF0 + seed
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(b, h, n, d, seed)
+    want = oracle.backward_closed_form(q1, q2, k1, k2, v, torch.tensor([lam]), dy, lam_init, rms, causal=causal,
+                                       dropout_threshold=th, dropout_seed=drop_seed)
+    got = run_gpu(op, q1, q2, k1, k2, v, dy, lam, lam_init, rms, causal=causal, dropout_p=p, dropout_seed=drop_seed)
+    check(got, want)
+    plain = oracle.forward(q1, q2, k1, k2, v, torch.tensor([lam]), lam_init, rms, causal=causal)
+    assert oracle.error_metrics(got["y"], plain["y"])["rel_l2"] > 0.05      # and it is not the undropped result
+
+
+def test_dropout_seed_and_bf16(op):
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(1, 2, 256, 64, 97, dtype=torch.bfloat16)
+    a = run_gpu(op, q1, q2, k1, k2, v, dy, 0.5, 0.8, True, dropout_p=0.25, dropout_seed=5)
+    b = run_gpu(op, q1, q2, k1, k2, v, dy, 0.5, 0.8, True, dropout_p=0.25, dropout_seed=5)
+    c = run_gpu(op, q1, q2, k1, k2, v, dy, 0.5, 0.8, True, dropout_p=0.25, dropout_seed=6)
+    for k in ("y",) + GRADS:
+        assert torch.equal(a[k], b[k]), k                                  # same seed: bit-identical
+    assert not torch.equal(a["y"], c["y"])                                 # another seed: another mask
+    want = oracle.backward_closed_form(q1, q2, k1, k2, v, torch.tensor([0.5]), dy, 0.8, True,
+                                       dropout_threshold=64, dropout_seed=5)
+    check(a, want, loosen=8.0)
+    # no seed given: one is drawn from torch's CPU generator, reproducible under torch.manual_seed
+    torch.manual_seed(11)
+    d1 = run_gpu(op, q1, q2, k1, k2, v, dy, 0.5, 0.8, True, dropout_p=0.25)
+    torch.manual_seed(11)
+    d2 = run_gpu(op, q1, q2, k1, k2, v, dy, 0.5, 0.8, True, dropout_p=0.25)
+    assert torch.equal(d1["y"], d2["y"])
 
 
 def test_mixed_dtypes_rejected(op):

@@ -38,6 +38,9 @@ struct BwdArgs {
   int n_pad;            // N rounded up to 128: row pitch of `stats` per (batch, head); rows N..n_pad-1 hold
                         // {+inf, +inf, 0, 0}, which makes the probabilities of out-of-range query rows exactly 0
   long long rows;       // B*H*N
+  uint32_t drop_thresh; // dropout: 0 = off (see sm100.cuh); must equal the forward's
+  uint32_t seed_lo, seed_hi;
+  float drop_scale;     // 256 / (256 - drop_thresh)
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -181,7 +184,7 @@ struct Misc {
 };
 }  // namespace dkdv64
 
-template <bool BF>
+template <bool BF, bool DROP>
 __global__ void __launch_bounds__(dkdv64::NUM_THREADS, 1)
 diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
                            const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k2,
@@ -323,6 +326,12 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
     const uint32_t tb = tmem_base + lane_base;
     const float sl2 = args.sm_scale * 1.4426950408889634f;
     const float sg = load_lambda(args.lambda_ptr, args.lambda_dtype) < 0.f ? 1.f : -1.f;   // -sign(lambda)
+    // dropout: this thread owns key column kv_tile*BKV + row; a hash covers two consecutive query rows of it
+    const uint32_t dkey1 = DROP ? drop_key(args.seed_lo, args.seed_hi, uint32_t(bh), 0u) : 0u;
+    const uint32_t dkey2 = DROP ? drop_key(args.seed_lo, args.seed_hi, uint32_t(bh), 1u) : 0u;
+    const uint32_t dcol2 = uint32_t(kv_tile * BKV + row) >> 1;
+    const int dcol_odd = row & 1;
+    const float dscale = DROP ? args.drop_scale : 1.f;
     bool ok = true;
     for (int i = 0; i < nq; ++i) {
       const int st = i % ST;
@@ -356,6 +365,12 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
 #pragma unroll
       for (int jj = 0; jj < 8; ++jj) {
         float pcv[2], d1v[2], d2v[2];
+        uint32_t h1 = 0, h2 = 0;
+        if constexpr (DROP) {
+          const uint32_t drow2 = uint32_t((i0 + i) * (BQ / 2) + g * 8 + jj);
+          h1 = drop_hash(dkey1, drow2, dcol2);
+          h2 = drop_hash(dkey2, drow2, dcol2);
+        }
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
           const int j = 2 * jj + u;
@@ -363,9 +378,18 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
           const float p1 = ex2(fmaf(__uint_as_float(s1[j]), sl2, -sv.x));
           const float p2 = ex2(fmaf(__uint_as_float(s2[j]), sl2, -sv.y));     // |lam| P2
           const float dpv = __uint_as_float(dp[j]);
-          pcv[u] = fmaf(sg, p2, p1);
-          d1v[u] = p1 * (dpv - sv.z);
-          d2v[u] = p2 * fmaf(sg, dpv, -sv.w);
+          if constexpr (DROP) {
+            // dropped positions contribute neither to dV nor to dP; kept ones carry the factor 1/(1-p)
+            const float k1 = drop_keep(h1, 2 * u + dcol_odd, args.drop_thresh) ? dscale : 0.f;
+            const float k2 = drop_keep(h2, 2 * u + dcol_odd, args.drop_thresh) ? sg * dscale : 0.f;
+            pcv[u] = fmaf(k2, p2, k1 * p1);
+            d1v[u] = p1 * fmaf(k1, dpv, -sv.z);
+            d2v[u] = p2 * fmaf(k2, dpv, -sv.w);
+          } else {
+            pcv[u] = fmaf(sg, p2, p1);
+            d1v[u] = p1 * (dpv - sv.z);
+            d2v[u] = p2 * fmaf(sg, dpv, -sv.w);
+          }
         }
         pc[jj] = pack2<BF>(pcv[0], pcv[1]);
         d1[jj] = pack2<BF>(d1v[0], d1v[1]);
@@ -476,7 +500,7 @@ struct Misc {
 };
 }  // namespace dq64
 
-template <bool BF>
+template <bool BF, bool DROP>
 __global__ void __launch_bounds__(dq64::NUM_THREADS, 1)
 diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
                          const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k2,
@@ -629,6 +653,10 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
     const float neg_l = br ? -sv.y : -sv.x;
     const float e = br ? sv.w : sv.z;
     const float sg = (br && !(lam < 0.f)) ? -1.f : 1.f;      // branch 2: -sign(lambda) (|lambda| sits in neg_l, the sign in e)
+    const uint32_t dkey = DROP ? drop_key(args.seed_lo, args.seed_hi, uint32_t(bh), uint32_t(br)) : 0u;
+    const uint32_t drow2 = uint32_t(q_tile * BM + row) >> 1;
+    const int drow_odd = row & 1;
+    const float sgs = DROP ? sg * args.drop_scale : sg;
     bool ok = true;
     for (int t = 0; t < nsub; ++t) {
       const int u = t & 1;
@@ -663,7 +691,15 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
       for (int i = 0; i < 16; ++i) {
         const float p0 = ex2(fmaf(__uint_as_float(s[2 * i]), sl2, neg_l));
         const float p1 = ex2(fmaf(__uint_as_float(s[2 * i + 1]), sl2, neg_l));
-        s[i] = pack2<BF>(p0 * fmaf(sg, __uint_as_float(dp[2 * i]), -e), p1 * fmaf(sg, __uint_as_float(dp[2 * i + 1]), -e));
+        if constexpr (DROP) {
+          // dP reaches a probability only where it was kept, with the factor 1/(1-p)
+          const uint32_t hh = drop_hash(dkey, drow2, uint32_t(t * (SUB / 2) + half * 16 + i));
+          const float g0 = drop_keep(hh, 2 * drow_odd, args.drop_thresh) ? sgs : 0.f;
+          const float g1 = drop_keep(hh, 2 * drow_odd + 1, args.drop_thresh) ? sgs : 0.f;
+          s[i] = pack2<BF>(p0 * fmaf(g0, __uint_as_float(dp[2 * i]), -e), p1 * fmaf(g1, __uint_as_float(dp[2 * i + 1]), -e));
+        } else {
+          s[i] = pack2<BF>(p0 * fmaf(sg, __uint_as_float(dp[2 * i]), -e), p1 * fmaf(sg, __uint_as_float(dp[2 * i + 1]), -e));
+        }
       }
       DA_TS(3);
       tmem_st16(t_s, s);

@@ -40,7 +40,7 @@ struct Misc {
 
 // tm_x, tm_z: the branch's stationary / streamed [N, 128] operand (box rows 128 / 64);
 // tm_y, tm_w: the [N, 256] operands.  dA lives in the dense workspace and is addressed (col, row, b*h, 0).
-template <bool QSIDE, bool BF>
+template <bool QSIDE, bool BF, bool DROP>
 __global__ void __launch_bounds__(side128::NUM_THREADS, 1)
 diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__ CUtensorMap tm_x1,
                             const __grid_constant__ CUtensorMap tm_y, const __grid_constant__ CUtensorMap tm_z0,
@@ -162,6 +162,11 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
       neg_l = br ? -sv.y : -sv.x;
       e = br ? sv.w : sv.z;
     }
+    // dropout: `own` is this thread's fixed coordinate (query row on the query side, key column on the key side)
+    const uint32_t dkey = DROP ? drop_key(args.seed_lo, args.seed_hi, uint32_t(bh), uint32_t(br)) : 0u;
+    const uint32_t down2 = uint32_t(tile * BM + row) >> 1;
+    const int down_odd = row & 1;
+    const float sgs = DROP ? sg * args.drop_scale : sg;
     bool ok = true;
     int st = 0;
     for (int t = 0; t < nsub; ++t) {
@@ -197,6 +202,12 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         float v[2];
+        uint32_t hh = 0;
+        if constexpr (DROP) {
+          // streamed index of this pair: key columns on the query side, query rows on the key side
+          const uint32_t str2 = uint32_t((QSIDE ? t : t0 + t) * (SUB / 2) + g * 8 + i);
+          hh = QSIDE ? drop_hash(dkey, down2, str2) : drop_hash(dkey, str2, down2);
+        }
 #pragma unroll
         for (int w = 0; w < 2; ++w) {
           const int j = 2 * i + w;
@@ -207,7 +218,9 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
             ee = br ? sv.w : sv.z;
           }
           const float p = ex2(fmaf(__uint_as_float(s[j]), sl2, nl));
-          v[w] = p * fmaf(sg, __uint_as_float(tt[j]), -ee);
+          float sge = sg;
+          if constexpr (DROP) sge = drop_keep(hh, QSIDE ? 2 * down_odd + w : 2 * w + down_odd, args.drop_thresh) ? sgs : 0.f;
+          v[w] = p * fmaf(sge, __uint_as_float(tt[j]), -ee);
         }
         ds[i] = pack2<BF>(v[0], v[1]);
       }
@@ -275,7 +288,7 @@ struct Misc {
 };
 }  // namespace dv128
 
-template <bool BF>
+template <bool BF, bool DROP>
 __global__ void __launch_bounds__(dv128::NUM_THREADS, 1)
 diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
                           const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k2,
@@ -388,6 +401,10 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
     const uint32_t tb = tmem_base + lane_base;
     const float sl2 = args.sm_scale * 1.4426950408889634f;
     const float sg = load_lambda(args.lambda_ptr, args.lambda_dtype) < 0.f ? 1.f : -1.f;   // -sign(lambda)
+    const uint32_t dkey1 = DROP ? drop_key(args.seed_lo, args.seed_hi, uint32_t(bh), 0u) : 0u;
+    const uint32_t dkey2 = DROP ? drop_key(args.seed_lo, args.seed_hi, uint32_t(bh), 1u) : 0u;
+    const uint32_t dcol2 = uint32_t(kv_tile * BKV + row) >> 1;
+    const int dcol_odd = row & 1;
     bool ok = true;
     int st = 0;
     for (int i = 0; i < nq; ++i) {
@@ -410,11 +427,22 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
 #pragma unroll
       for (int jj = 0; jj < 8; ++jj) {
         float v[2];
+        uint32_t h1 = 0, h2 = 0;
+        if constexpr (DROP) {
+          const uint32_t drow2 = uint32_t((i0 + i) * (BQ / 2) + g * 8 + jj);
+          h1 = drop_hash(dkey1, drow2, dcol2);
+          h2 = drop_hash(dkey2, drow2, dcol2);
+        }
 #pragma unroll
         for (int w = 0; w < 2; ++w) {
           const int j = 2 * jj + w;
           const float4 sv = stats[j];
-          v[w] = fmaf(sg, ex2(fmaf(__uint_as_float(s2[j]), sl2, -sv.y)), ex2(fmaf(__uint_as_float(s1[j]), sl2, -sv.x)));
+          float k1 = 1.f, k2 = sg;
+          if constexpr (DROP) {
+            k1 = drop_keep(h1, 2 * w + dcol_odd, args.drop_thresh) ? args.drop_scale : 0.f;
+            k2 = drop_keep(h2, 2 * w + dcol_odd, args.drop_thresh) ? sg * args.drop_scale : 0.f;
+          }
+          v[w] = fmaf(k2, ex2(fmaf(__uint_as_float(s2[j]), sl2, -sv.y)), k1 * ex2(fmaf(__uint_as_float(s1[j]), sl2, -sv.x)));
         }
         pc[jj] = pack2<BF>(v[0], v[1]);
       }

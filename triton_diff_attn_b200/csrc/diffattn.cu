@@ -87,6 +87,8 @@ int check_common(const DiffAttnParams* p, bool bwd) {
     return fail(DIFFATTN_ERR_BAD_DTYPE, "lambda_dtype %d unknown", p->lambda_dtype);
   if (p->io_dtype != DIFFATTN_IO_F16 && p->io_dtype != DIFFATTN_IO_BF16)
     return fail(DIFFATTN_ERR_BAD_DTYPE, "io_dtype %d unknown", p->io_dtype);
+  if (p->dropout_threshold > 255)
+    return fail(DIFFATTN_ERR_BAD_SHAPE, "dropout_threshold %u exceeds 255", p->dropout_threshold);
   if ((long long)p->B * p->H > 65535)
     return fail(DIFFATTN_ERR_BAD_SHAPE, "B*H=%lld exceeds the grid limit 65535", (long long)p->B * p->H);
   if (p->B == 0 || p->H == 0 || p->N == 0) return 1;   // empty: nothing to do
@@ -150,7 +152,7 @@ uint64_t diffattn_workspace_bytes(const DiffAttnParams* p) {
 
 namespace {
 
-template <bool BF>
+template <bool BF, bool DROP>
 int fwd_impl(const DiffAttnParams* p) {
   int rc = 0;
   DA_CUDA(cudaSetDevice(p->device));
@@ -170,10 +172,12 @@ int fwd_impl(const DiffAttnParams* p) {
   a.lambda_ptr = p->lambda_scale; a.lambda_dtype = p->lambda_dtype;
   a.sm_scale = p->sm_scale; a.out_scale = 1.f - p->lambda_init; a.eps = p->eps;
   a.rms_norm = p->rms_norm; a.n = p->N; a.h = p->H; a.d = p->D; a.causal = p->causal ? 1 : 0;
+  a.drop_thresh = p->dropout_threshold; a.seed_lo = uint32_t(p->dropout_seed); a.seed_hi = uint32_t(p->dropout_seed >> 32);
+  a.drop_scale = 256.f / float(256u - p->dropout_threshold);
   if (D == 128) {
-    if ((rc = set_smem(da::diffattn_fwd128_kernel<BF>, da::fwd128::SMEM_BYTES))) return rc;
+    if ((rc = set_smem(da::diffattn_fwd128_kernel<BF, DROP>, da::fwd128::SMEM_BYTES))) return rc;
     dim3 grid128((p->N + 127) / 128, p->B * p->H);
-    da::diffattn_fwd128_kernel<BF><<<grid128, da::fwd128::NUM_THREADS, da::fwd128::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, a);
+    da::diffattn_fwd128_kernel<BF, DROP><<<grid128, da::fwd128::NUM_THREADS, da::fwd128::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, a);
     DA_CUDA(cudaGetLastError());
     return DIFFATTN_OK;
   }
@@ -182,14 +186,14 @@ int fwd_impl(const DiffAttnParams* p) {
   const long long bh = (long long)p->B * p->H;
   if ((rc = make_map<BF>(&my, p->y, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 128, "y"))) return rc;
   if ((rc = make_map<BF>(&ma2, p->a2, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 128, "a2"))) return rc;
-  if ((rc = set_smem(da::diffattn_fwd64_kernel<BF>, da::fwd64::SMEM_BYTES))) return rc;
+  if ((rc = set_smem(da::diffattn_fwd64_kernel<BF, DROP>, da::fwd64::SMEM_BYTES))) return rc;
   dim3 grid((p->N + 127) / 128, p->B * p->H);
-  da::diffattn_fwd64_kernel<BF><<<grid, da::fwd64::NUM_THREADS, da::fwd64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, my, ma2, a);
+  da::diffattn_fwd64_kernel<BF, DROP><<<grid, da::fwd64::NUM_THREADS, da::fwd64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, my, ma2, a);
   DA_CUDA(cudaGetLastError());
   return DIFFATTN_OK;
 }
 
-template <bool BF>
+template <bool BF, bool DROP>
 int bwd_impl(const DiffAttnParams* p, int32_t stages) {
   int rc = 0;
   DA_CUDA(cudaSetDevice(p->device));
@@ -213,6 +217,8 @@ int bwd_impl(const DiffAttnParams* p, int32_t stages) {
   a.n = p->N; a.h = p->H; a.d = p->D; a.rows = (long long)rows;
   a.n_pad = (p->N + 127) & ~127;
   a.causal = p->causal ? 1 : 0;
+  a.drop_thresh = p->dropout_threshold; a.seed_lo = uint32_t(p->dropout_seed); a.seed_hi = uint32_t(p->dropout_seed >> 32);
+  a.drop_scale = 256.f / float(256u - p->dropout_threshold);
   const int n_tiles = a.n_pad / 128;
 
   // 1. preprocess (grid-stride; one atomic per CTA for d(lambda))
@@ -246,20 +252,20 @@ int bwd_impl(const DiffAttnParams* p, int32_t stages) {
     if ((rc = make_map<BF>(&da_64, a.da, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 64, "dA"))) return rc;
     if ((rc = make_map<BF>(&da_128, a.da, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 128, "dA"))) return rc;
     if (stages & DIFFATTN_STAGE_DKDV) {
-      if ((rc = set_smem(da::diffattn_bwd_dv128_kernel<BF>, da::dv128::SMEM_BYTES))) return rc;
+      if ((rc = set_smem(da::diffattn_bwd_dv128_kernel<BF, DROP>, da::dv128::SMEM_BYTES))) return rc;
       dim3 g1(n_tiles, (unsigned)bh);
-      da::diffattn_bwd_dv128_kernel<BF><<<g1, da::dv128::NUM_THREADS, da::dv128::SMEM_BYTES, stream>>>(q1_64, q2_64, k1_128, k2_128, da_64, a);
+      da::diffattn_bwd_dv128_kernel<BF, DROP><<<g1, da::dv128::NUM_THREADS, da::dv128::SMEM_BYTES, stream>>>(q1_64, q2_64, k1_128, k2_128, da_64, a);
       DA_CUDA(cudaGetLastError());
-      if ((rc = set_smem(da::diffattn_bwd_side128_kernel<false, BF>, da::side128::SMEM_BYTES))) return rc;
+      if ((rc = set_smem(da::diffattn_bwd_side128_kernel<false, BF, DROP>, da::side128::SMEM_BYTES))) return rc;
       dim3 g2(n_tiles, (unsigned)bh, 2);
-      da::diffattn_bwd_side128_kernel<false, BF><<<g2, da::side128::NUM_THREADS, da::side128::SMEM_BYTES, stream>>>(
+      da::diffattn_bwd_side128_kernel<false, BF, DROP><<<g2, da::side128::NUM_THREADS, da::side128::SMEM_BYTES, stream>>>(
           k1_128, k2_128, v_128, q1_64, q2_64, da_64, a);
       DA_CUDA(cudaGetLastError());
     }
     if (stages & DIFFATTN_STAGE_DQ) {
-      if ((rc = set_smem(da::diffattn_bwd_side128_kernel<true, BF>, da::side128::SMEM_BYTES))) return rc;
+      if ((rc = set_smem(da::diffattn_bwd_side128_kernel<true, BF, DROP>, da::side128::SMEM_BYTES))) return rc;
       dim3 g3(n_tiles, (unsigned)bh, 2);
-      da::diffattn_bwd_side128_kernel<true, BF><<<g3, da::side128::NUM_THREADS, da::side128::SMEM_BYTES, stream>>>(
+      da::diffattn_bwd_side128_kernel<true, BF, DROP><<<g3, da::side128::NUM_THREADS, da::side128::SMEM_BYTES, stream>>>(
           q1_128, q2_128, da_128, k1_64, k2_64, v_64, a);
       DA_CUDA(cudaGetLastError());
     }
@@ -281,20 +287,20 @@ int bwd_impl(const DiffAttnParams* p, int32_t stages) {
   if ((rc = grad_map(&mdk1, p->dk1, D, "dk1"))) return rc;
   if ((rc = grad_map(&mdk2, p->dk2, D, "dk2"))) return rc;
   if ((rc = grad_map(&mdv, p->dv, DV, "dv"))) return rc;
-  if ((rc = set_smem(da::diffattn_bwd_dkdv64_kernel<BF>, da::dkdv64::SMEM_BYTES))) return rc;
+  if ((rc = set_smem(da::diffattn_bwd_dkdv64_kernel<BF, DROP>, da::dkdv64::SMEM_BYTES))) return rc;
   if (stages & DIFFATTN_STAGE_DKDV) {
     dim3 grid(n_tiles, (unsigned)bh);
-    da::diffattn_bwd_dkdv64_kernel<BF><<<grid, da::dkdv64::NUM_THREADS, da::dkdv64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, mda, mdk1, mdk2, mdv, a);
+    da::diffattn_bwd_dkdv64_kernel<BF, DROP><<<grid, da::dkdv64::NUM_THREADS, da::dkdv64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, mda, mdk1, mdk2, mdv, a);
     DA_CUDA(cudaGetLastError());
   }
   // 3. dQ: query tiles of 128 rows resident, key/value tiles of 128 rows streamed
   if ((rc = make_map<BF>(&mq1, p->q1, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "q1"))) return rc;
   if ((rc = make_map<BF>(&mq2, p->q2, D, p->N, p->H, p->B, p->qk_stride_n, p->qk_stride_h, p->qk_stride_b, 128, "q2"))) return rc;
   if ((rc = make_map<BF>(&mda, a.da, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 128, "dA"))) return rc;
-  if ((rc = set_smem(da::diffattn_bwd_dq64_kernel<BF>, da::dq64::SMEM_BYTES))) return rc;
+  if ((rc = set_smem(da::diffattn_bwd_dq64_kernel<BF, DROP>, da::dq64::SMEM_BYTES))) return rc;
   if (stages & DIFFATTN_STAGE_DQ) {
     dim3 grid(n_tiles, (unsigned)bh);
-    da::diffattn_bwd_dq64_kernel<BF><<<grid, da::dq64::NUM_THREADS, da::dq64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, mda, a);
+    da::diffattn_bwd_dq64_kernel<BF, DROP><<<grid, da::dq64::NUM_THREADS, da::dq64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, mda, a);
     DA_CUDA(cudaGetLastError());
   }
   return DIFFATTN_OK;
@@ -308,7 +314,9 @@ int diffattn_fwd(const DiffAttnParams* p) {
   const int rc = check_common(p, false);
   if (rc < 0) return rc;
   if (rc == 1) return DIFFATTN_OK;
-  return p->io_dtype == DIFFATTN_IO_BF16 ? fwd_impl<true>(p) : fwd_impl<false>(p);
+  const bool bf = p->io_dtype == DIFFATTN_IO_BF16;
+  if (p->dropout_threshold) return bf ? fwd_impl<true, true>(p) : fwd_impl<false, true>(p);
+  return bf ? fwd_impl<true, false>(p) : fwd_impl<false, false>(p);
 }
 
 int diffattn_bwd(const DiffAttnParams* p) { return diffattn_bwd_stages(p, DIFFATTN_STAGE_ALL); }
@@ -317,7 +325,9 @@ int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages) {
   const int rc = check_common(p, true);
   if (rc < 0) return rc;
   if (rc == 1) return DIFFATTN_OK;
-  return p->io_dtype == DIFFATTN_IO_BF16 ? bwd_impl<true>(p, stages) : bwd_impl<false>(p, stages);
+  const bool bf = p->io_dtype == DIFFATTN_IO_BF16;
+  if (p->dropout_threshold) return bf ? bwd_impl<true, true>(p, stages) : bwd_impl<false, true>(p, stages);
+  return bf ? bwd_impl<true, false>(p, stages) : bwd_impl<false, false>(p, stages);
 }
 
 // ---- allocation-free backward: scratch in a file-scope device array -------------------------------

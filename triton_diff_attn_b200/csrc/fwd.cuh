@@ -34,6 +34,9 @@ struct FwdArgs {
   int h;              // heads
   int d;              // real head dim: 64, or 32 (then the 64-wide tiles are zero-filled by TMA beyond column 32 / 64)
   int causal;         // 1: query row i sees key columns j <= i only
+  uint32_t drop_thresh;   // dropout: 0 = off, else keep a probability iff its hash byte >= drop_thresh (see sm100.cuh)
+  uint32_t seed_lo, seed_hi;
+  float drop_scale;       // 256 / (256 - drop_thresh)
 };
 
 __device__ __forceinline__ float load_lambda(const void* p, int dtype) {
@@ -100,7 +103,7 @@ static_assert(sizeof(Misc) <= MISC_BYTES, "misc area too small");
 
 __device__ __forceinline__ float max3(float a, float b, float c) { return fmaxf(fmaxf(a, b), c); }
 
-template <bool BF>   // BF: tensors are bf16 instead of fp16
+template <bool BF, bool DROP>   // BF: tensors are bf16 instead of fp16; DROP: attention dropout on
 __global__ void __launch_bounds__(fwd64::NUM_THREADS, 1)
 diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
                       const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k2,
@@ -253,6 +256,10 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     const float sl2 = args.sm_scale * 1.4426950408889634f;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
+    // dropout: this row's half of every 2x2 block hash, keyed by (seed, batch*head, branch)
+    const uint32_t dkey = DROP ? drop_key(args.seed_lo, args.seed_hi, uint32_t(bh), uint32_t(br)) : 0u;
+    const uint32_t drow2 = uint32_t(q_tile * BM + row) >> 1;
+    const int drow_odd = row & 1;
 #ifdef DA_DEPHASE
     if (br == 1) { const long long c0 = clock64(); while (clock64() - c0 < DA_DEPHASE) { } }
 #endif
@@ -365,7 +372,12 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
           pk[i] = pack2<BF>(p0, p1);
         }
       }
-      l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+      l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);     // the softmax denominator is taken before dropout
+      if constexpr (DROP) {
+#pragma unroll
+        for (int i = 0; i < SUB / 2; ++i)
+          pk[i] &= drop_pair_mask(drop_hash(dkey, drow2, uint32_t(t * (SUB / 2) + i)), drow_odd, args.drop_thresh);
+      }
       DA_TS(4);
 #ifndef DA_NOST
       tmem_st32(t_s, pk);
@@ -388,7 +400,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
 #ifdef DA_TIMING
     if (life_on) g_timing[4096 + 6 * cta_lin + 4] = gtimer();
 #endif
-    const float inv_l = 1.f / l_run;
+    const float inv_l = (DROP ? args.drop_scale : 1.f) / l_run;      // kept probabilities are scaled by 1 / (1 - p)
     if (br == 0) misc->coef1[row] = inv_l; else misc->coef2[row] = inv_l;
     named_bar_sync(1, 256);
     const float lam = load_lambda(args.lambda_ptr, args.lambda_dtype);

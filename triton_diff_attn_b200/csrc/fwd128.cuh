@@ -39,7 +39,7 @@ struct Misc {
 static_assert(sizeof(Misc) <= MISC_BYTES, "misc area too small");
 }  // namespace fwd128
 
-template <bool BF>
+template <bool BF, bool DROP>
 __global__ void __launch_bounds__(fwd128::NUM_THREADS, 1)
 diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
                        const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k2,
@@ -165,6 +165,10 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
     const size_t grow = size_t(bh) * args.n + size_t(q_tile) * BM + row;
     bool ok = true;
     float ssq_total = 0.f;
+    // dropout (same decisions in both passes: they depend on the position only)
+    const uint32_t dkey = DROP ? drop_key(args.seed_lo, args.seed_hi, uint32_t(bh), uint32_t(br)) : 0u;
+    const uint32_t drow2 = uint32_t(q_tile * BM + row) >> 1;
+    const int drow_odd = row & 1;
     uint32_t parked[32];            // first-pass A (this thread's 64 columns) as fp16 pairs, used with rms_norm
 #pragma unroll
     for (int i = 0; i < 32; ++i) parked[i] = 0u;
@@ -241,7 +245,12 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
             pk[i] = pack2<BF>(p0, p1);
           }
         }
-        l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+        l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);     // the softmax denominator is taken before dropout
+        if constexpr (DROP) {
+#pragma unroll
+          for (int i = 0; i < SUB / 2; ++i)
+            pk[i] &= drop_pair_mask(drop_hash(dkey, drow2, uint32_t(t * (SUB / 2) + i)), drow_odd, args.drop_thresh);
+        }
         tmem_st32(t_s, pk);
         tc_wait_st();
         tc_fence_before();
@@ -251,7 +260,7 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
       // ---- epilogue of this pass (value columns [128 pass, 128 pass + 128)); every thread runs every barrier
       ok = ok && mbar_wait(&misc->o_full, pass & 1, abort_flag, 2311 + br, pass);
       tc_fence_after();
-      const float inv_l = 1.f / l_run;
+      const float inv_l = (DROP ? args.drop_scale : 1.f) / l_run;
       if (br == 0) misc->coef1[row] = inv_l; else misc->coef2[row] = inv_l;
       named_bar_sync(1, 256);
       const float c1 = misc->coef1[row], c2 = misc->coef2[row];

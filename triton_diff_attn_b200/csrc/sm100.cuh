@@ -296,4 +296,29 @@ __device__ __forceinline__ __half from_float16b(float x) {
   else return __float2half_rn(x);
 }
 
+// ------------------------------------------ attention dropout ------------------------------------------
+// Counter-based keep mask: nothing is stored, every kernel recomputes the decisions it needs.  One 32-bit hash
+// serves a 2 x 2 block of (query row, key column) positions, one byte per position, so that a thread walking
+// along a row (forward, dQ) and a thread walking down a column (dK/dV) both get two decisions per hash:
+//   h    = mix32( ((row >> 1) << 16 | (col >> 1)) ^ key ),  key = drop_key(seed, batch*head index, branch)
+//   keep = byte (row & 1) * 2 + (col & 1) of h  >=  threshold        (threshold = round(256 p), 1..255)
+// mix32 is the two-multiply xorshift finaliser "lowbias32" (C. Wellons, public domain).  Kept probabilities
+// are multiplied by 256 / (256 - threshold).  The CPU oracle restates exactly this.
+__host__ __device__ __forceinline__ uint32_t mix32(uint32_t h) {
+  h ^= h >> 16; h *= 0x7feb352dU; h ^= h >> 15; h *= 0x846ca68bU; h ^= h >> 16;
+  return h;
+}
+__host__ __device__ __forceinline__ uint32_t drop_key(uint32_t seed_lo, uint32_t seed_hi, uint32_t bh, uint32_t branch) {
+  return mix32(seed_lo ^ mix32(seed_hi + 0x9E3779B9U * (2u * bh + branch + 1u)));
+}
+__device__ __forceinline__ uint32_t drop_hash(uint32_t key, uint32_t row2, uint32_t col2) {
+  return mix32(((row2 << 16) | col2) ^ key);
+}
+__device__ __forceinline__ bool drop_keep(uint32_t h, int byte, uint32_t thresh) { return ((h >> (8 * byte)) & 0xffu) >= thresh; }
+// mask for one packed pair of 16-bit probabilities of ONE row (columns 2c, 2c+1): bytes 2*(row&1), 2*(row&1)+1
+__device__ __forceinline__ uint32_t drop_pair_mask(uint32_t h, int row_odd, uint32_t thresh) {
+  const uint32_t f = row_odd ? (h >> 16) : (h & 0xffffu);
+  return ((f & 0xffu) >= thresh ? 0x0000ffffu : 0u) | (f >= (thresh << 8) ? 0xffff0000u : 0u);
+}
+
 }  // namespace da

@@ -61,7 +61,18 @@ def _same_layout(ts):
     return ts
 
 
-def _fill_common(p, q1, q2, k1, k2, v, lam, lambda_init, rms_norm, saved, causal=False):
+def dropout_threshold(dropout_p: float) -> int:
+    """The kernels drop a probability when a hash byte is below round(256 p): p is quantised to 1/256 steps
+    (0 below 1/512) and must stay below 255.5/256."""
+    if not 0.0 <= float(dropout_p) < 1.0:
+        raise ValueError(f"dropout_p must be in [0, 1), got {dropout_p}")
+    t = int(round(float(dropout_p) * 256.0))
+    if t > 255:
+        raise ValueError(f"dropout_p {dropout_p} is too close to 1 (largest supported: 255/256)")
+    return t
+
+
+def _fill_common(p, q1, q2, k1, k2, v, lam, lambda_init, rms_norm, saved, causal=False, drop_threshold=0, drop_seed=0):
     b, h, n, d = q1.shape
     p.device = q1.device.index if q1.device.index is not None else torch.cuda.current_device()
     p.stream = torch.cuda.current_stream(q1.device).cuda_stream
@@ -74,6 +85,8 @@ def _fill_common(p, q1, q2, k1, k2, v, lam, lambda_init, rms_norm, saved, causal
     p.io_dtype = _lib.IO_BF16 if q1.dtype == torch.bfloat16 else _lib.IO_F16
     p.rms_norm = 1 if rms_norm else 0
     p.causal = 1 if causal else 0
+    p.dropout_threshold = int(drop_threshold)
+    p.dropout_seed = int(drop_seed) & 0xFFFFFFFFFFFFFFFF
     p.sm_scale = 1.0 / math.sqrt(d)          # reference src/layers.py:20-22 (D, not 2D)
     p.lambda_init = float(lambda_init)
     p.eps = EPS
@@ -86,7 +99,7 @@ class DiffAttnFunction(torch.autograd.Function):
     (reference src/kernel.py:461-575)."""
 
     @staticmethod
-    def forward(ctx, q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, causal=False):
+    def forward(ctx, q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, causal=False, drop_threshold=0, drop_seed=0):
         _check_inputs(q1, q2, k1, k2, v, lambda_scale)
         q1, q2, k1, k2 = _same_layout([q1, q2, k1, k2])
         if v.stride(-1) != 1:
@@ -100,12 +113,14 @@ class DiffAttnFunction(torch.autograd.Function):
             lse2 = torch.empty_like(lse1)
             rstd = torch.empty_like(lse1)
             p = _lib.new_params()
-            _fill_common(p, q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, (y, a2, lse1, lse2, rstd), causal)
+            _fill_common(p, q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, (y, a2, lse1, lse2, rstd), causal,
+                         drop_threshold, drop_seed)
             _lib.check(_lib.lib.diffattn_fwd(p), "diffattn_fwd")
         ctx.save_for_backward(q1, q2, k1, k2, v, lambda_scale, y, a2, lse1, lse2, rstd)
         ctx.lambda_init = float(lambda_init)
         ctx.rms_norm = bool(rms_norm)
         ctx.causal = bool(causal)
+        ctx.drop = (int(drop_threshold), int(drop_seed))
         return y
 
     @staticmethod
@@ -120,7 +135,8 @@ class DiffAttnFunction(torch.autograd.Function):
             dv = torch.empty((b, h, n, 2 * d), dtype=v.dtype, device=dev)
             dlam = torch.zeros(1, dtype=torch.float32, device=dev)
             p = _lib.new_params()
-            _fill_common(p, q1, q2, k1, k2, v, lam, ctx.lambda_init, ctx.rms_norm, (y, a2, lse1, lse2, rstd), ctx.causal)
+            _fill_common(p, q1, q2, k1, k2, v, lam, ctx.lambda_init, ctx.rms_norm, (y, a2, lse1, lse2, rstd), ctx.causal,
+                         *ctx.drop)
             nbytes = int(_lib.lib.diffattn_workspace_bytes(p))
             ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
             p.dy = dy.data_ptr()
@@ -131,13 +147,13 @@ class DiffAttnFunction(torch.autograd.Function):
         # fp32 partial kept for callers that shard (batch*head) and sum partials themselves
         DiffAttnFunction.last_dlambda_fp32 = dlam
         dlam_out = dlam.to(lam.dtype).reshape(lam.shape) if ctx.needs_input_grad[5] else None
-        return dq1, dq2, dk1, dk2, dv, dlam_out, None, None, None
+        return dq1, dq2, dk1, dk2, dv, dlam_out, None, None, None, None, None
 
     last_dlambda_fp32 = None
 
 
 def MultiheadDiffAttnKernel(q1, q2, k1, k2, v, lambda_scale=-0.5, lambda_init: float = 0.8, rms_norm: bool = False,
-                            causal: bool = False):
+                            causal: bool = False, dropout_p: float = 0.0, dropout_seed=None):
     """Fused differential attention, same signature as the reference (src/layers.py:10-26).
 
     q1,q2,k1,k2: fp16 CUDA [B,H,N,D]; v: fp16 CUDA [B,H,N,2D]; lambda_scale: 1-element fp16/fp32
@@ -148,8 +164,16 @@ def MultiheadDiffAttnKernel(q1, q2, k1, k2, v, lambda_scale=-0.5, lambda_init: f
     tile); the reference needs N to be a multiple of its block sizes (src/kernel.py:148,527).
     `causal=True` (keyword, after the reference's eight parameters) restricts query i to keys j <= i; the
     reference has no masking (README.md:2).
+    `dropout_p` > 0 (keyword; the reference has no dropout either) drops attention probabilities after the
+    softmax, independently in the two branches, and scales the kept ones by 1/(1-p); p is quantised to 1/256
+    steps (`dropout_threshold`).  The mask is a pure function of `dropout_seed` and the position, so the backward
+    recomputes it; without a seed one is drawn from torch's CPU generator (no device synchronisation).
     """
-    return DiffAttnFunction.apply(q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, causal)
+    thresh = dropout_threshold(dropout_p)
+    seed = 0
+    if thresh:
+        seed = int(torch.randint(0, 2 ** 62, (1,)).item()) if dropout_seed is None else int(dropout_seed)
+    return DiffAttnFunction.apply(q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, causal, thresh, seed)
 
 
 def device_status(device=None) -> None:
