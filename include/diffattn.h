@@ -75,6 +75,13 @@ typedef struct DiffAttnParams {
                                       below the threshold, kept ones are scaled by 256/(256 - threshold).  The
                                       backward must be given the forward's threshold and seed. */
   uint64_t dropout_seed;           /* the mask is a pure function of (seed, batch*head, branch, row, column) */
+  /* Learnable gain of the output norm (extension: the reference's norm has no weight, src/layers.py:75; the layer it
+   * adapts has one).  gain == NULL: off.  Otherwise gain is fp32 [2D] on the device; the forward writes y (without
+   * the gain, kept for the backward) AND y_gained = y * gain (same type and shape as y, the layer's output); the
+   * backward takes dy = d(loss)/d(y_gained) and ADDS sum over rows of dy * y into dgain (fp32 [2D]). */
+  const float* gain;
+  void* y_gained;
+  float* dgain;
 } DiffAttnParams;
 
 /* Forward.  Reads q1,q2,k1,k2,v,lambda_scale; writes y,a2,lse1,lse2,rstd.

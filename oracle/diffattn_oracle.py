@@ -79,7 +79,7 @@ def dropout_multipliers(b: int, h: int, n: int, threshold: int, seed: int, dtype
 
 def forward(q1, q2, k1, k2, v, lambda_scale, lambda_init: float = 0.8, rms_norm: bool = False,
             dtype=torch.float32, round_p_half: bool = False, eps: float = EPS, device="cpu",
-            causal: bool = False, dropout_threshold: int = 0, dropout_seed: int = 0) -> Dict[str, torch.Tensor]:
+            causal: bool = False, dropout_threshold: int = 0, dropout_seed: int = 0, gain=None) -> Dict[str, torch.Tensor]:
     """Forward pass; returns Y and the intermediates the backward kernels save (src/layers.py:60-80).
 
     Keys: y, a (pre-norm), a1, a2 (per-branch P_b V), lse1, lse2 (natural-log logsumexp of S_b,
@@ -122,15 +122,19 @@ def forward(q1, q2, k1, k2, v, lambda_scale, lambda_init: float = 0.8, rms_norm:
         y = (1.0 - lambda_init) * a * rstd[..., None]                  # layers.py:75-78
     else:
         y = a                                                          # layers.py:80
-    return {"y": y, "a": a, "a1": a1, "a2": a2, "lse1": lse1, "lse2": lse2, "rstd": rstd,
-            "p1": p1, "p2": p2, "m1": m1, "m2": m2}
+    out = {"y": y, "a": a, "a1": a1, "a2": a2, "lse1": lse1, "lse2": lse2, "rstd": rstd,
+           "p1": p1, "p2": p2, "m1": m1, "m2": m2}
+    if gain is not None:
+        # extension: learnable column gain of the output norm; "y" stays the un-gained value the backward keeps
+        out["y_gained"] = y * gain.detach().to(y.device, dtype)
+    return out
 
 
 def backward_closed_form(q1, q2, k1, k2, v, lambda_scale, dy, lambda_init: float = 0.8,
                          rms_norm: bool = False, dtype=torch.float32,
                          eps: float = EPS, device="cpu", causal: bool = False,
-                         dropout_threshold: int = 0, dropout_seed: int = 0) -> Dict[str, torch.Tensor]:
-    """Closed-form gradients (no autograd).  Same quantities the reference's backward kernel forms
+                         dropout_threshold: int = 0, dropout_seed: int = 0, gain=None) -> Dict[str, torch.Tensor]:
+    """Closed-form gradients (no autograd).  With `gain`, dy is the gradient of y * gain.  Same quantities the reference's backward kernel forms
     (src/kernel.py:283-299 preprocess, :410-436 main loop), with the division-free d(lambda).
 
         dA   = c (r dY - r^3 A (dY.A)/Dv)     (rms on; kernel.py:283-290)   |  dA = dY (rms off)
@@ -142,8 +146,12 @@ def backward_closed_form(q1, q2, k1, k2, v, lambda_scale, dy, lambda_init: float
         dlam = - sum E_2
     """
     f = forward(q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, dtype=dtype, eps=eps, device=device, causal=causal,
-                dropout_threshold=dropout_threshold, dropout_seed=dropout_seed)
+                dropout_threshold=dropout_threshold, dropout_seed=dropout_seed, gain=gain)
     q1, q2, k1, k2, v, dy = (t.detach().to(device, dtype) for t in (q1, q2, k1, k2, v, dy))
+    dgain = None
+    if gain is not None:
+        dgain = (dy * f["y"]).sum(dim=(0, 1, 2))
+        dy = dy * gain.detach().to(device, dtype)
     lam = _lam(lambda_scale, dtype, device)
     d = q1.shape[-1]
     dv_dim = v.shape[-1]
@@ -169,13 +177,15 @@ def backward_closed_form(q1, q2, k1, k2, v, lambda_scale, dy, lambda_init: float
         "dv": dvv, "dlambda": -e2.sum(), "da": da, "e1": e1[..., 0], "e2": e2[..., 0],
     }
     out.update({k: f[k] for k in ("y", "lse1", "lse2", "rstd", "a2")})
+    if gain is not None:
+        out["dgain"], out["y_gained"] = dgain, f["y_gained"]
     return out
 
 
 def forward_backward_autograd(q1, q2, k1, k2, v, lambda_scale, dy, lambda_init: float = 0.8,
                               rms_norm: bool = False, dtype=torch.float32, round_p_half: bool = False,
                               eps: float = EPS, num_threads: Optional[int] = None, causal: bool = False,
-                              dropout_threshold: int = 0, dropout_seed: int = 0) -> Dict[str, torch.Tensor]:
+                              dropout_threshold: int = 0, dropout_seed: int = 0, gain=None) -> Dict[str, torch.Tensor]:
     """Forward + autograd backward of the literal op sequence of src/layers.py:60-80.
 
     This is the independent check of `backward_closed_form` and the function the CPU baseline times.
@@ -208,9 +218,16 @@ def forward_backward_autograd(q1, q2, k1, k2, v, lambda_scale, dy, lambda_init: 
         y = (1.0 - lambda_init) * a * torch.rsqrt((a * a).mean(-1, keepdim=True) + eps)
     else:
         y = a
+    gl = None
+    if gain is not None:
+        gl = gain.detach().to("cpu", dtype).clone().requires_grad_(True)
+        y = y * gl
     y.backward(dy.detach().to("cpu", dtype))
-    return {"y": y.detach(), "dq1": lq1.grad, "dq2": lq2.grad, "dk1": lk1.grad, "dk2": lk2.grad,
-            "dv": lv.grad, "dlambda": lam.grad.reshape(())}
+    out = {"y": y.detach(), "dq1": lq1.grad, "dq2": lq2.grad, "dk1": lk1.grad, "dk2": lk2.grad,
+           "dv": lv.grad, "dlambda": lam.grad.reshape(())}
+    if gl is not None:
+        out["dgain"] = gl.grad
+    return out
 
 
 def error_metrics(got: torch.Tensor, want: torch.Tensor) -> Dict[str, float]:

@@ -109,3 +109,18 @@ def test_dropout_closed_form_matches_autograd_and_mask_statistics():
     assert oracle.dropout_keep_mask(77, 0, 0, 64, 0).all()                   # threshold 0 keeps everything
     # known answers (pin the hash against accidental edits; values computed from the definition in the docstring)
     assert [int(x) for x in oracle._mix32(np.array([0, 1, 0xdeadbeef], dtype=np.uint32))] == [0, 1753845952, 3861431939]
+
+
+def test_gain_closed_form_matches_autograd():
+    """Learnable gain of the output norm (extension): closed form (dY = dY_out * gain, dgain = sum dY_out * Y)
+    against autograd through y * gain."""
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(2, 2, 64, 32, 4)
+    gain = torch.linspace(-1.5, 2.0, 64, dtype=torch.float64)
+    lam = torch.tensor([0.3])
+    for rms in (True, False):
+        a = oracle.backward_closed_form(q1, q2, k1, k2, v, lam, dy, 0.8, rms, dtype=torch.float64, gain=gain)
+        b = oracle.forward_backward_autograd(q1, q2, k1, k2, v, lam, dy, 0.8, rms, dtype=torch.float64, gain=gain)
+        assert oracle.error_metrics(a["y_gained"], b["y"])["rel_l2"] < 1e-12
+        for k in ("dq1", "dq2", "dk1", "dk2", "dv", "dgain"):
+            assert oracle.error_metrics(a[k], b[k])["rel_l2"] < 1e-11, k
+        assert abs(float(a["dlambda"]) - float(b["dlambda"])) < 1e-9

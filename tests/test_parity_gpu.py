@@ -224,6 +224,50 @@ def test_dropout_seed_and_bf16(op):
     assert torch.equal(d1["y"], d2["y"])
 
 
+@pytest.mark.parametrize("b,h,n,d,rms,dt", [(1, 2, 256, 64, True, torch.float16), (2, 2, 200, 32, True, torch.float16),
+                                              (1, 2, 384, 128, True, torch.float16), (1, 2, 256, 128, False, torch.bfloat16),
+                                              (1, 2, 256, 64, False, torch.bfloat16)])
+def test_learnable_gain(op, b, h, n, d, rms, dt):
+    """Output-norm gain (extension): y * gain from the forward epilogue, d(gain) from the preprocess kernel."""
+    dev = torch.device("cuda", 0)
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(b, h, n, d, 101 + d, dtype=dt)
+    gain = torch.linspace(-1.5, 2.0, 2 * d)
+    want = oracle.backward_closed_form(q1, q2, k1, k2, v, torch.tensor([0.5]), dy, 0.8, rms, gain=gain)
+    leaves = [t.to(dev).clone().requires_grad_(True) for t in (q1, q2, k1, k2, v)]
+    lam_t = torch.tensor([0.5], device=dev, requires_grad=True)
+    gain_t = gain.to(dev).requires_grad_(True)
+    y = op.MultiheadDiffAttnKernel(*leaves, lam_t, 0.8, rms, gain=gain_t)
+    y.backward(dy.to(dev))
+    op.device_status(0)
+    loosen = 8.0 if dt == torch.bfloat16 else 1.0
+    got = {"y": y.detach().cpu(), "dlambda_fp32": float(op.DiffAttnFunction.last_dlambda_fp32.cpu())}
+    for nm, t in zip(GRADS, leaves):
+        got[nm] = t.grad.detach().cpu()
+    want_y = dict(want); want_y["y"] = want["y_gained"]
+    check(got, want_y, loosen=loosen)
+    m = oracle.error_metrics(gain_t.grad.cpu(), want["dgain"])
+    assert m["rel_l2"] <= loosen * REL_L2 and gain_t.grad.dtype == torch.float32, m
+
+
+def test_layer_core_runs_without_host_sync(op):
+    """`DiffAttnCore`: lambda from its re-parameterisation on the device, gain, one fwd+bwd; every parameter
+    gets a finite gradient and lambda matches the formula."""
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(3)
+    core = op.DiffAttnCore(64, lambda_init=0.8, device=dev)
+    q1, q2, k1, k2, v, dy = (t.to(dev) for t in oracle.make_inputs(1, 2, 256, 64, 111))
+    y = core(q1, q2, k1, k2, v)
+    y.backward(dy)
+    op.device_status(0)
+    for nm, prm in core.named_parameters():
+        assert prm.grad is not None and torch.isfinite(prm.grad).all(), nm
+    lam = op.lambda_from_reparam(core.lambda_q1, core.lambda_k1, core.lambda_q2, core.lambda_k2, 0.8)
+    ref = math.exp(float((core.lambda_q1 * core.lambda_k1).sum().detach())) - math.exp(float((core.lambda_q2 * core.lambda_k2).sum().detach())) + 0.8
+    assert abs(float(lam.detach()) - ref) < 1e-5
+    want = oracle.forward(q1, q2, k1, k2, v, lam.detach().cpu(), 0.8, True)
+    assert oracle.error_metrics(y.detach().cpu(), want["y"])["rel_l2"] <= REL_L2      # gain initialised to ones
+
+
 def test_mixed_dtypes_rejected(op):
     dev = torch.device("cuda", 0)
     q = torch.zeros(1, 1, 128, 64, dtype=torch.float16, device=dev)

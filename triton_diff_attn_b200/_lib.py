@@ -41,6 +41,7 @@ class DiffAttnParams(C.Structure):
         ("dq1", C.c_void_p), ("dq2", C.c_void_p), ("dk1", C.c_void_p), ("dk2", C.c_void_p), ("dv", C.c_void_p),
         ("dlambda", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64),
         ("io_dtype", C.c_int32), ("dropout_threshold", C.c_uint32), ("dropout_seed", C.c_uint64),
+        ("gain", C.c_void_p), ("y_gained", C.c_void_p), ("dgain", C.c_void_p),
     ]
 
 

@@ -41,6 +41,8 @@ struct BwdArgs {
   uint32_t drop_thresh; // dropout: 0 = off (see sm100.cuh); must equal the forward's
   uint32_t seed_lo, seed_hi;
   float drop_scale;     // 256 / (256 - drop_thresh)
+  const float* gain;    // NULL, or fp32 [2D]: then dy is the gradient of y * gain, and sum_rows(dy * y) is added to dgain
+  float* dgain;         // fp32 [2D]
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -57,6 +59,12 @@ __global__ void __launch_bounds__(256) diffattn_bwd_pre_kernel(const BwdArgs arg
   const float c = args.out_scale;
   float dl_acc = 0.f;
   __shared__ float red[8];
+  // learnable gain of the output norm: Y_out = Y * gain, so dY = dY_out * gain and d(gain) = sum over rows of dY_out * Y
+  const bool has_gain = args.gain != nullptr;
+  float gn[VPL], dg_acc[VPL];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) { gn[i] = has_gain ? args.gain[lane * VPL + i] : 1.f; dg_acc[i] = 0.f; }
+  __shared__ float dg_red[8][DV];
 
   for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + warp; row < args.rows; row += warps_total) {
     const size_t off = size_t(row) * DV + lane * VPL;
@@ -78,6 +86,10 @@ __global__ void __launch_bounds__(256) diffattn_bwd_pre_kernel(const BwdArgs arg
       }
 #pragma unroll
       for (int i = 0; i < VPL; ++i) { dy[i] = to_float16b<BF>(hd[i]); yv[i] = to_float16b<BF>(hy[i]); a2[i] = to_float16b<BF>(ha[i]); }
+    }
+    if (has_gain) {
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) { dg_acc[i] = fmaf(dy[i], yv[i], dg_acc[i]); dy[i] *= gn[i]; }
     }
     float da[VPL], av[VPL];
     if (args.rms_norm) {
@@ -125,11 +137,20 @@ __global__ void __launch_bounds__(256) diffattn_bwd_pre_kernel(const BwdArgs arg
     }
   }
   if (lane == 0) red[warp] = dl_acc;
+  if (has_gain) {
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) dg_red[warp][lane * VPL + i] = dg_acc[i];
+  }
   __syncthreads();
   if (threadIdx.x == 0) {
     float s = 0.f;
     for (int i = 0; i < (blockDim.x >> 5); ++i) s += red[i];
     atomicAdd(args.dlambda, s);
+  }
+  if (has_gain && threadIdx.x < DV) {
+    float s = 0.f;
+    for (int i = 0; i < (blockDim.x >> 5); ++i) s += dg_red[i][threadIdx.x];
+    atomicAdd(args.dgain + threadIdx.x, s);       // one atomic per column and CTA
   }
 }
 

@@ -87,6 +87,9 @@ int check_common(const DiffAttnParams* p, bool bwd) {
     return fail(DIFFATTN_ERR_BAD_DTYPE, "lambda_dtype %d unknown", p->lambda_dtype);
   if (p->io_dtype != DIFFATTN_IO_F16 && p->io_dtype != DIFFATTN_IO_BF16)
     return fail(DIFFATTN_ERR_BAD_DTYPE, "io_dtype %d unknown", p->io_dtype);
+  if (p->gain && (!p->y_gained || !aligned16(p->gain) || !aligned16(p->y_gained)))
+    return fail(p->y_gained ? DIFFATTN_ERR_MISALIGNED : DIFFATTN_ERR_NULL_PTR, "gain given: y_gained must be set, both 16-byte aligned");
+  if (p->gain && bwd && !p->dgain) return fail(DIFFATTN_ERR_NULL_PTR, "gain given: dgain is NULL");
   if (p->dropout_threshold > 255)
     return fail(DIFFATTN_ERR_BAD_SHAPE, "dropout_threshold %u exceeds 255", p->dropout_threshold);
   if ((long long)p->B * p->H > 65535)
@@ -174,6 +177,7 @@ int fwd_impl(const DiffAttnParams* p) {
   a.rms_norm = p->rms_norm; a.n = p->N; a.h = p->H; a.d = p->D; a.causal = p->causal ? 1 : 0;
   a.drop_thresh = p->dropout_threshold; a.seed_lo = uint32_t(p->dropout_seed); a.seed_hi = uint32_t(p->dropout_seed >> 32);
   a.drop_scale = 256.f / float(256u - p->dropout_threshold);
+  a.gain = p->gain; a.yg = static_cast<__half*>(p->y_gained);
   if (D == 128) {
     if ((rc = set_smem(da::diffattn_fwd128_kernel<BF, DROP>, da::fwd128::SMEM_BYTES))) return rc;
     dim3 grid128((p->N + 127) / 128, p->B * p->H);
@@ -186,9 +190,11 @@ int fwd_impl(const DiffAttnParams* p) {
   const long long bh = (long long)p->B * p->H;
   if ((rc = make_map<BF>(&my, p->y, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 128, "y"))) return rc;
   if ((rc = make_map<BF>(&ma2, p->a2, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 128, "a2"))) return rc;
+  CUtensorMap myg = my;      // only read by the kernel when a gain is given
+  if (p->gain && (rc = make_map<BF>(&myg, p->y_gained, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 128, "y_gained"))) return rc;
   if ((rc = set_smem(da::diffattn_fwd64_kernel<BF, DROP>, da::fwd64::SMEM_BYTES))) return rc;
   dim3 grid((p->N + 127) / 128, p->B * p->H);
-  da::diffattn_fwd64_kernel<BF, DROP><<<grid, da::fwd64::NUM_THREADS, da::fwd64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, my, ma2, a);
+  da::diffattn_fwd64_kernel<BF, DROP><<<grid, da::fwd64::NUM_THREADS, da::fwd64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, my, ma2, myg, a);
   DA_CUDA(cudaGetLastError());
   return DIFFATTN_OK;
 }
@@ -219,6 +225,7 @@ int bwd_impl(const DiffAttnParams* p, int32_t stages) {
   a.causal = p->causal ? 1 : 0;
   a.drop_thresh = p->dropout_threshold; a.seed_lo = uint32_t(p->dropout_seed); a.seed_hi = uint32_t(p->dropout_seed >> 32);
   a.drop_scale = 256.f / float(256u - p->dropout_threshold);
+  a.gain = p->gain; a.dgain = p->dgain;
   const int n_tiles = a.n_pad / 128;
 
   // 1. preprocess (grid-stride; one atomic per CTA for d(lambda))

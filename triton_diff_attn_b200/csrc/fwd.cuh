@@ -37,6 +37,8 @@ struct FwdArgs {
   uint32_t drop_thresh;   // dropout: 0 = off, else keep a probability iff its hash byte >= drop_thresh (see sm100.cuh)
   uint32_t seed_lo, seed_hi;
   float drop_scale;       // 256 / (256 - drop_thresh)
+  const float* gain;      // NULL, or fp32 [2D]: learnable gain of the output norm; then yg = y * gain is written too
+  __half* yg;             // [B*H, N, 2D] dense (only with gain)
 };
 
 __device__ __forceinline__ float load_lambda(const void* p, int dtype) {
@@ -74,7 +76,7 @@ constexpr int MISC_BYTES = 4096;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024; // +1024 for manual alignment
 constexpr int PRELOAD = 2;                               // key/value tiles requested before the setup barrier (<= KS, VS)
 constexpr int STORE_TILE_BYTES = BM * 128;               // epilogue staging: 128 rows x 64 columns x 2 bytes
-static_assert(4 * STORE_TILE_BYTES <= KS * 2 * K_BYTES, "the y / a2 staging tiles reuse the K ring");
+static_assert(6 * STORE_TILE_BYTES <= KS * 2 * K_BYTES, "the y / a2 / gained-y staging tiles reuse the K ring");
 // warps 0-7 softmax; 8 TMA producer; 9 S issuer (both branches); 10, 11 P V issuers of branch 1, 2: one role
 // warp per scheduler (warp % 4).  A single warp issuing every MMA slows the row quarter that shares its
 // scheduler by about 30 %, and every barrier waits for that quarter.  Twelve warps keep three per scheduler,
@@ -108,7 +110,8 @@ __global__ void __launch_bounds__(fwd64::NUM_THREADS, 1)
 diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_constant__ CUtensorMap tm_q2,
                       const __grid_constant__ CUtensorMap tm_k1, const __grid_constant__ CUtensorMap tm_k2,
                       const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_y,
-                      const __grid_constant__ CUtensorMap tm_a2, const FwdArgs args) {
+                      const __grid_constant__ CUtensorMap tm_a2, const __grid_constant__ CUtensorMap tm_yg,
+                      const FwdArgs args) {
   using namespace fwd64;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -435,21 +438,27 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     // [128 rows][64 columns] tile in the (now idle) K ring, and one thread per warpgroup stores the two tiles.
     // (Row-per-thread global stores of 16-byte pieces cost 3.6 us per CTA, 8 % of the kernel at N = 4096.)
     {
-      uint8_t* ytile = smem + OFF_K + br * (2 * STORE_TILE_BYTES);
+      uint8_t* ytile = smem + OFF_K + br * (3 * STORE_TILE_BYTES);
       uint8_t* atile = ytile + STORE_TILE_BYTES;
+      uint8_t* gtile = atile + STORE_TILE_BYTES;          // y * gain, only with a gain
+      const float4* gp = reinterpret_cast<const float4*>(args.gain + br * 64);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        uint4 yv, av;
-        yv.x = pack2<BF>(__uint_as_float(o1[8 * i + 0]) * yscale, __uint_as_float(o1[8 * i + 1]) * yscale);
-        yv.y = pack2<BF>(__uint_as_float(o1[8 * i + 2]) * yscale, __uint_as_float(o1[8 * i + 3]) * yscale);
-        yv.z = pack2<BF>(__uint_as_float(o1[8 * i + 4]) * yscale, __uint_as_float(o1[8 * i + 5]) * yscale);
-        yv.w = pack2<BF>(__uint_as_float(o1[8 * i + 6]) * yscale, __uint_as_float(o1[8 * i + 7]) * yscale);
+        float f[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) f[k] = __uint_as_float(o1[8 * i + k]) * yscale;
+        uint4 av;
         av.x = pack2<BF>(__uint_as_float(o2[8 * i + 0]), __uint_as_float(o2[8 * i + 1]));
         av.y = pack2<BF>(__uint_as_float(o2[8 * i + 2]), __uint_as_float(o2[8 * i + 3]));
         av.z = pack2<BF>(__uint_as_float(o2[8 * i + 4]), __uint_as_float(o2[8 * i + 5]));
         av.w = pack2<BF>(__uint_as_float(o2[8 * i + 6]), __uint_as_float(o2[8 * i + 7]));
-        st_swizzled_chunk(ytile, row, i, yv);
+        st_swizzled_chunk(ytile, row, i, make_uint4(pack2<BF>(f[0], f[1]), pack2<BF>(f[2], f[3]), pack2<BF>(f[4], f[5]), pack2<BF>(f[6], f[7])));
         st_swizzled_chunk(atile, row, i, av);
+        if (args.gain && br * 64 + 8 * i < dv_real) {
+          const float4 g0 = __ldg(gp + 2 * i), g1 = __ldg(gp + 2 * i + 1);
+          st_swizzled_chunk(gtile, row, i, make_uint4(pack2<BF>(f[0] * g0.x, f[1] * g0.y), pack2<BF>(f[2] * g0.z, f[3] * g0.w),
+                                                      pack2<BF>(f[4] * g1.x, f[5] * g1.y), pack2<BF>(f[6] * g1.z, f[7] * g1.w)));
+        }
       }
       fence_proxy_async_smem();
       named_bar_sync(2 + br, 128);
@@ -457,6 +466,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
         if (!*abort_flag && br * 64 < dv_real) {
           tma_store_4d(ytile, &tm_y, br * 64, q_tile * BM, bh, 0);
           tma_store_4d(atile, &tm_a2, br * 64, q_tile * BM, bh, 0);
+          if (args.gain) tma_store_4d(gtile, &tm_yg, br * 64, q_tile * BM, bh, 0);
           tma_store_commit();
           tma_store_wait_read();
         }

@@ -299,17 +299,26 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
           ap[i] = av;
         }
       }
+      // eight consecutive output columns of this row: y, and y * gain when a gain is given
+      auto put_y = [&](int col, const float (&f)[8]) {
+        *reinterpret_cast<uint4*>(args.y + grow * DV + col) =
+            make_uint4(pack2<BF>(f[0], f[1]), pack2<BF>(f[2], f[3]), pack2<BF>(f[4], f[5]), pack2<BF>(f[6], f[7]));
+        if (args.gain) {
+          const float4 g0 = __ldg(reinterpret_cast<const float4*>(args.gain + col));
+          const float4 g1 = __ldg(reinterpret_cast<const float4*>(args.gain + col + 4));
+          *reinterpret_cast<uint4*>(args.yg + grow * DV + col) =
+              make_uint4(pack2<BF>(f[0] * g0.x, f[1] * g0.y), pack2<BF>(f[2] * g0.z, f[3] * g0.w),
+                         pack2<BF>(f[4] * g1.x, f[5] * g1.y), pack2<BF>(f[6] * g1.z, f[7] * g1.w));
+        }
+      };
       if (!args.rms_norm) {
         if (live) {
-          uint4* yp = reinterpret_cast<uint4*>(args.y + grow * DV + col0);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            uint4 yv;
-            yv.x = pack2<BF>(__uint_as_float(o1[8 * i + 0]), __uint_as_float(o1[8 * i + 1]));
-            yv.y = pack2<BF>(__uint_as_float(o1[8 * i + 2]), __uint_as_float(o1[8 * i + 3]));
-            yv.z = pack2<BF>(__uint_as_float(o1[8 * i + 4]), __uint_as_float(o1[8 * i + 5]));
-            yv.w = pack2<BF>(__uint_as_float(o1[8 * i + 6]), __uint_as_float(o1[8 * i + 7]));
-            yp[i] = yv;
+            float f[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) f[k] = __uint_as_float(o1[8 * i + k]);
+            put_y(col0 + 8 * i, f);
           }
         }
       } else if (pass == 0) {
@@ -319,23 +328,19 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
         const float rstd = rsqrtf(ssq_total * (1.f / DV) + args.eps);
         const float ys = args.out_scale * rstd;
         if (live) {
-          uint4* y0 = reinterpret_cast<uint4*>(args.y + grow * DV + br * 64);
-          uint4* y1 = reinterpret_cast<uint4*>(args.y + grow * DV + col0);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            uint32_t w[4];
+            float f[8];
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-              const float2 f = unpack2<BF>(parked[4 * i + c]);
-              w[c] = pack2<BF>(f.x * ys, f.y * ys);
+              const float2 w = unpack2<BF>(parked[4 * i + c]);
+              f[2 * c] = w.x * ys;
+              f[2 * c + 1] = w.y * ys;
             }
-            y0[i] = make_uint4(w[0], w[1], w[2], w[3]);
-            uint4 yv;
-            yv.x = pack2<BF>(__uint_as_float(o1[8 * i + 0]) * ys, __uint_as_float(o1[8 * i + 1]) * ys);
-            yv.y = pack2<BF>(__uint_as_float(o1[8 * i + 2]) * ys, __uint_as_float(o1[8 * i + 3]) * ys);
-            yv.z = pack2<BF>(__uint_as_float(o1[8 * i + 4]) * ys, __uint_as_float(o1[8 * i + 5]) * ys);
-            yv.w = pack2<BF>(__uint_as_float(o1[8 * i + 6]) * ys, __uint_as_float(o1[8 * i + 7]) * ys);
-            y1[i] = yv;
+            put_y(br * 64 + 8 * i, f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) f[k] = __uint_as_float(o1[8 * i + k]) * ys;
+            put_y(col0 + 8 * i, f);
           }
         }
       }

@@ -72,7 +72,8 @@ def dropout_threshold(dropout_p: float) -> int:
     return t
 
 
-def _fill_common(p, q1, q2, k1, k2, v, lam, lambda_init, rms_norm, saved, causal=False, drop_threshold=0, drop_seed=0):
+def _fill_common(p, q1, q2, k1, k2, v, lam, lambda_init, rms_norm, saved, causal=False, drop_threshold=0, drop_seed=0,
+                 gain=None, y_gained=None):
     b, h, n, d = q1.shape
     p.device = q1.device.index if q1.device.index is not None else torch.cuda.current_device()
     p.stream = torch.cuda.current_stream(q1.device).cuda_stream
@@ -87,6 +88,8 @@ def _fill_common(p, q1, q2, k1, k2, v, lam, lambda_init, rms_norm, saved, causal
     p.causal = 1 if causal else 0
     p.dropout_threshold = int(drop_threshold)
     p.dropout_seed = int(drop_seed) & 0xFFFFFFFFFFFFFFFF
+    if gain is not None:
+        p.gain, p.y_gained = gain.data_ptr(), y_gained.data_ptr()
     p.sm_scale = 1.0 / math.sqrt(d)          # reference src/layers.py:20-22 (D, not 2D)
     p.lambda_init = float(lambda_init)
     p.eps = EPS
@@ -99,8 +102,12 @@ class DiffAttnFunction(torch.autograd.Function):
     (reference src/kernel.py:461-575)."""
 
     @staticmethod
-    def forward(ctx, q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, causal=False, drop_threshold=0, drop_seed=0):
+    def forward(ctx, q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, causal=False, drop_threshold=0, drop_seed=0,
+                gain=None):
         _check_inputs(q1, q2, k1, k2, v, lambda_scale)
+        if gain is not None:
+            if not torch.is_tensor(gain) or gain.device != q1.device or tuple(gain.shape) != (v.shape[-1],):
+                raise ValueError("gain must be a tensor of shape [2*D] on the inputs' device")
         q1, q2, k1, k2 = _same_layout([q1, q2, k1, k2])
         if v.stride(-1) != 1:
             v = v.contiguous()
@@ -112,16 +119,20 @@ class DiffAttnFunction(torch.autograd.Function):
             lse1 = torch.empty((b, h, n), dtype=torch.float32, device=dev)
             lse2 = torch.empty_like(lse1)
             rstd = torch.empty_like(lse1)
+            gain32 = gain.detach().to(torch.float32).contiguous() if gain is not None else None
+            y_gained = torch.empty_like(y) if gain is not None else None
             p = _lib.new_params()
             _fill_common(p, q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, (y, a2, lse1, lse2, rstd), causal,
-                         drop_threshold, drop_seed)
+                         drop_threshold, drop_seed, gain32, y_gained)
             _lib.check(_lib.lib.diffattn_fwd(p), "diffattn_fwd")
         ctx.save_for_backward(q1, q2, k1, k2, v, lambda_scale, y, a2, lse1, lse2, rstd)
+        ctx.gain32 = gain32
+        ctx.gain_dtype = gain.dtype if gain is not None else None
         ctx.lambda_init = float(lambda_init)
         ctx.rms_norm = bool(rms_norm)
         ctx.causal = bool(causal)
         ctx.drop = (int(drop_threshold), int(drop_seed))
-        return y
+        return y_gained if gain is not None else y
 
     @staticmethod
     def backward(ctx, dy):
@@ -135,8 +146,11 @@ class DiffAttnFunction(torch.autograd.Function):
             dv = torch.empty((b, h, n, 2 * d), dtype=v.dtype, device=dev)
             dlam = torch.zeros(1, dtype=torch.float32, device=dev)
             p = _lib.new_params()
+            dgain = torch.zeros(2 * d, dtype=torch.float32, device=dev) if ctx.gain32 is not None else None
             _fill_common(p, q1, q2, k1, k2, v, lam, ctx.lambda_init, ctx.rms_norm, (y, a2, lse1, lse2, rstd), ctx.causal,
-                         *ctx.drop)
+                         *ctx.drop, ctx.gain32, y)     # y_gained is not read by the backward
+            if dgain is not None:
+                p.dgain = dgain.data_ptr()
             nbytes = int(_lib.lib.diffattn_workspace_bytes(p))
             ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=dev)
             p.dy = dy.data_ptr()
@@ -147,13 +161,14 @@ class DiffAttnFunction(torch.autograd.Function):
         # fp32 partial kept for callers that shard (batch*head) and sum partials themselves
         DiffAttnFunction.last_dlambda_fp32 = dlam
         dlam_out = dlam.to(lam.dtype).reshape(lam.shape) if ctx.needs_input_grad[5] else None
-        return dq1, dq2, dk1, dk2, dv, dlam_out, None, None, None, None, None
+        dgain_out = dgain.to(ctx.gain_dtype) if (dgain is not None and ctx.needs_input_grad[11]) else None
+        return dq1, dq2, dk1, dk2, dv, dlam_out, None, None, None, None, None, dgain_out
 
     last_dlambda_fp32 = None
 
 
 def MultiheadDiffAttnKernel(q1, q2, k1, k2, v, lambda_scale=-0.5, lambda_init: float = 0.8, rms_norm: bool = False,
-                            causal: bool = False, dropout_p: float = 0.0, dropout_seed=None):
+                            causal: bool = False, dropout_p: float = 0.0, dropout_seed=None, gain=None):
     """Fused differential attention, same signature as the reference (src/layers.py:10-26).
 
     q1,q2,k1,k2: fp16 CUDA [B,H,N,D]; v: fp16 CUDA [B,H,N,2D]; lambda_scale: 1-element fp16/fp32
@@ -168,12 +183,46 @@ def MultiheadDiffAttnKernel(q1, q2, k1, k2, v, lambda_scale=-0.5, lambda_init: f
     softmax, independently in the two branches, and scales the kept ones by 1/(1-p); p is quantised to 1/256
     steps (`dropout_threshold`).  The mask is a pure function of `dropout_seed` and the position, so the backward
     recomputes it; without a seed one is drawn from torch's CPU generator (no device synchronisation).
+    `gain` (keyword, a [2D] tensor, normally a learnable parameter): the output is multiplied column-wise by it
+    inside the forward epilogue and its gradient comes out of the backward's preprocess kernel -- the weight of
+    the output norm in the layer the reference adapts (src/layers.py:114), which the reference's own norm
+    (elementwise_affine=False, src/layers.py:75) does not have.
     """
     thresh = dropout_threshold(dropout_p)
     seed = 0
     if thresh:
         seed = int(torch.randint(0, 2 ** 62, (1,)).item()) if dropout_seed is None else int(dropout_seed)
-    return DiffAttnFunction.apply(q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, causal, thresh, seed)
+    return DiffAttnFunction.apply(q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, causal, thresh, seed, gain)
+
+
+def lambda_from_reparam(lambda_q1, lambda_k1, lambda_q2, lambda_k2, lambda_init: float):
+    """lambda = exp(<lambda_q1, lambda_k1>) - exp(<lambda_q2, lambda_k2>) + lambda_init as a 1-element fp32
+    tensor on the parameters' device: the re-parameterisation of the layer the reference adapts
+    (src/layers.py:114; the reference itself takes lambda_scale ready-made, src/layers.py:16).  Plain device-side
+    torch ops, differentiable, no host synchronisation: together with the operator's device-side d(lambda) the
+    whole layer runs without a sync (the reference's backward calls .item(), src/kernel.py:573)."""
+    l1 = torch.exp(torch.sum(lambda_q1.float() * lambda_k1.float()))
+    l2 = torch.exp(torch.sum(lambda_q2.float() * lambda_k2.float()))
+    return (l1 - l2 + float(lambda_init)).reshape(1)
+
+
+class DiffAttnCore(torch.nn.Module):
+    """The attention core of a differential-attention layer around the operator: owns the four lambda vectors
+    and the output norm's gain, forms lambda on the device and calls `MultiheadDiffAttnKernel` with rms_norm on.
+    Projections and head reshapes stay with the caller."""
+
+    def __init__(self, head_dim: int, lambda_init: float = 0.8, causal: bool = False, dropout_p: float = 0.0,
+                 device=None, dtype=torch.float32):
+        super().__init__()
+        mk = lambda: torch.nn.Parameter(torch.zeros(head_dim, device=device, dtype=dtype).normal_(mean=0.0, std=0.1))
+        self.lambda_q1, self.lambda_k1, self.lambda_q2, self.lambda_k2 = mk(), mk(), mk(), mk()
+        self.gain = torch.nn.Parameter(torch.ones(2 * head_dim, device=device, dtype=dtype))
+        self.lambda_init, self.causal, self.dropout_p = float(lambda_init), bool(causal), float(dropout_p)
+
+    def forward(self, q1, q2, k1, k2, v):
+        lam = lambda_from_reparam(self.lambda_q1, self.lambda_k1, self.lambda_q2, self.lambda_k2, self.lambda_init)
+        return MultiheadDiffAttnKernel(q1, q2, k1, k2, v, lam, self.lambda_init, True, causal=self.causal,
+                                       dropout_p=self.dropout_p if self.training else 0.0, gain=self.gain)
 
 
 def device_status(device=None) -> None:
