@@ -14,6 +14,7 @@
 #include "bwd.cuh"
 #include "bwd128.cuh"
 #include "fwd.cuh"
+#include "fwd64.cuh"
 #include "fwd128.cuh"
 #include "sm100.cuh"
 
@@ -192,8 +193,8 @@ int fwd_impl(const DiffAttnParams* p) {
   if ((rc = make_map<BF>(&ma2, p->a2, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 128, "a2"))) return rc;
   CUtensorMap myg = my;      // only read by the kernel when a gain is given
   if (p->gain && (rc = make_map<BF>(&myg, p->y_gained, DV, p->N, (int)bh, 1, DV, (int64_t)p->N * DV, (int64_t)p->N * DV * bh, 128, "y_gained"))) return rc;
-  if ((rc = set_smem(da::diffattn_fwd64_kernel<BF, DROP>, da::fwd64::SMEM_BYTES))) return rc;
   dim3 grid((p->N + 127) / 128, p->B * p->H);
+  if ((rc = set_smem(da::diffattn_fwd64_kernel<BF, DROP>, da::fwd64::SMEM_BYTES))) return rc;
   da::diffattn_fwd64_kernel<BF, DROP><<<grid, da::fwd64::NUM_THREADS, da::fwd64::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, my, ma2, myg, a);
   DA_CUDA(cudaGetLastError());
   return DIFFATTN_OK;

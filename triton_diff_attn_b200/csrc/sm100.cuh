@@ -90,6 +90,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// (Polling with mbarrier.test_wait instead of the parking try_wait was measured on the forward's hand-overs:
+// no gain, the polling warps take issue slots from the working ones.)
+
 // Same wait executed by a whole converged warp; the result is made warp-uniform so that the warp
 // stays converged (elect.sync below needs all 32 lanes) even when a wait gives up.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int site,
@@ -263,6 +266,12 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// the same, pinned in program order relative to other volatile statements (barrier arrivals between two groups of them)
+__device__ __forceinline__ float ex2v(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
