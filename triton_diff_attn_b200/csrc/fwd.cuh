@@ -1,15 +1,11 @@
-// Differential-attention forward for sm_100a, head dim D = 64 (value width 128).
+// Differential-attention forward for sm_100a: what the forward kernels share (arguments, tile geometry of the
+// D <= 64 kernel).  The kernels themselves: fwd64.cuh (head dims 32 and 64), fwd128.cuh (head dim 128).
 //
-// One CTA owns one tile of 128 query rows of one (batch, head).  Roles (12 warps):
-//   warps 0-3   softmax of branch 1 (thread = query row; S1/P1/O1 in TMEM)
-//   warps 4-7   softmax of branch 2
-//   warp  8     TMA producer: Q1,Q2 once; K1,K2 and V tiles through two mbarrier rings
-//   warp  9     tcgen05.mma issuer of S1, S2 (one elected thread; owns TMEM)
-//   warps 10,11 tcgen05.mma issuers of P1 V, P2 V
-// TMEM (512 columns of 128 lanes x 32 bit): S1 two 64-column buffers [0,128), S2 likewise [128,256),
-// O1 [256,384), O2 [384,512).  Scores are produced in sub-tiles of 64 key rows into alternating buffers, so
-// the MMA for sub-tile t+1 runs while the softmax warpgroup works on sub-tile t.  P_b (fp16, two per
-// column) overwrites the first 32 columns of its S buffer and is the TMEM A-operand of P_b V.
+// One CTA owns one tile of 128 query rows of one (batch, head).  TMEM (512 columns of 128 lanes x 32 bit) at
+// D <= 64: S1 two 64-column buffers [0,128), S2 likewise [128,256), O1 [256,384), O2 [384,512).  Scores are
+// produced in sub-tiles of 64 key rows into alternating buffers, so the MMA for sub-tile t+1 runs while the
+// softmax warps work on sub-tile t.  P_b (16-bit, two per column) overwrites the first 32 columns of its S
+// buffer and is the TMEM A-operand of P_b V.
 // Replaces the reference's Triton forward (src/kernel.py:21-207): same math (two online softmaxes,
 // O = O1/l1 - lambda O2/l2, RMSNorm * (1 - lambda_init)), but saves lse1, lse2, rstd and A2 = P2 V
 // instead of O1/O2.
@@ -25,7 +21,7 @@ struct FwdArgs {
   float* lse2;
   float* rstd;        // [B*H, N] rsqrt(mean(A^2) + eps)   (written also when rms_norm is off)
   const void* lambda_ptr;
-  int lambda_dtype;   // 0 = fp16, 1 = fp32
+  int lambda_dtype;   // 0 = fp16, 1 = fp32, 2 = bf16
   float sm_scale;
   float out_scale;    // 1 - lambda_init
   float eps;
