@@ -268,6 +268,10 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// (2^x on the FMA and integer pipes -- round-to-nearest split by the 1.5*2^23 trick, degree-3 minimax of 2^f on
+// [-0.5, 0.5] with relative error 7.5e-5, exponent added as an integer -- was measured in place of every 2nd, 3rd,
+// 4th and 8th exponential of the forward: 1.17, 1.08, 1.04, 0.99 ms against 0.975 ms with the exp unit alone.  The
+// kernels are bound by instruction issue around the exp unit, not by the unit's rate; the routine is not kept.)
 // the same, pinned in program order relative to other volatile statements (barrier arrivals between two groups of them)
 __device__ __forceinline__ float ex2v(float x) {
   float y;
