@@ -192,6 +192,7 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
 
     for (int pass = 0; pass < 2; ++pass) {
       float m_run = -INFINITY, l_run = 0.f;          // running maximum (same in both halves), own share of the denominator
+      int synced = 0;                                // pair barriers passed in this pass
       for (int t = 0; t < nsub; ++t) {
         const int gt = pass * nsub + t;
         const int u = gt & 1;
@@ -244,6 +245,7 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
         const float m_loc = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
         misc->xmax[u][br][half][row] = m_loc;
         named_bar_sync(pair_bar, 64);
+        ++synced;
         const float m_new = fmaxf(m_loc, misc->xmax[u][br][half ^ 1][row]);
         const bool need = (t == 0) || ((m_new - m_run) * sl2 > 8.f);
         if (__any_sync(0xffffffffu, need)) {          // same outcome in both warps of the pair
@@ -278,6 +280,9 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
         tc_fence_before();
         mbar_arrive(&misc->p_full[br][u]);
       }
+
+      // a warp that left the loop early stands in, without blocking, for the pair barriers it skipped (see fwd64.cuh)
+      for (; synced < nsub; ++synced) named_bar_arrive(pair_bar, 64);
 
       // ---- epilogue of this pass (value columns [128 pass, 128 pass + 128)); every thread runs every barrier
       ok = ok && mbar_wait(&misc->o_full, pass & 1, abort_flag, 2311 + br, pass);

@@ -220,6 +220,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     const uint32_t drow2 = uint32_t(q_tile * BM + row) >> 1;
     const int drow_odd = row & 1;
 
+    int synced = 0;                                  // pair barriers passed so far
     for (int t = 0; t < nsub; ++t) {
       const int u = t & 1;
       const uint32_t t_s = t_s0 + u * SUB;
@@ -288,6 +289,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
       DA_TS(3);
       misc->xmax[u][br][half][row] = m_loc;
       named_bar_sync(pair_bar, 64);
+      ++synced;
       DA_TS(4);
       const float m_new = fmaxf(m_loc, misc->xmax[u][br][half ^ 1][row]);
       const bool need = (t == 0) || ((m_new - m_run) * sl2 > 8.f);
@@ -327,6 +329,10 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
       mbar_arrive(&misc->p_full[br][u]);
       DA_TS(6);
     }
+
+    // A warp that left the loop early (a bounded wait expired) arrives, without blocking, on the pair barriers it
+    // skipped: its partner may have got past the same wait a moment earlier and would otherwise sit in bar.sync.
+    for (; synced < nsub; ++synced) named_bar_arrive(pair_bar, 64);
 
     // ---- epilogue: every thread runs every barrier; only the global writes depend on `ok`
     ok = ok && mbar_wait(&misc->o_full, 0, abort_flag, 311 + br);

@@ -104,6 +104,11 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, v
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
+// non-blocking arrival on a named barrier: lets a warp that has given up (a bounded wait expired) stand in for the
+// bar.sync calls it will no longer make, so that a partner still running its loop is never left waiting on it
+__device__ __forceinline__ void named_bar_arrive(int id, int nthreads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 
 // --------------------------------------------- TMA -------------------------------------------
 // 4-D tiled load global -> shared, completion counted in bytes on an mbarrier.  No multicast.
