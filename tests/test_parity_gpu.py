@@ -51,9 +51,11 @@ def check(got, want, keys=("y",) + GRADS, loosen=1.0):
         # the absolute bound is stated for O(1) values; it scales with the tensor's own magnitude
         # when that exceeds 1 (peaky-softmax case: gradients reach several tens)
         bound = loosen * MAX_ABS * max(1.0, float(want[k].abs().max()))
-        assert m["max_abs"] <= bound and m["rel_l2"] <= loosen * REL_L2, (k, m)
+        # a tensor that is zero up to rounding noise (the score gradients of a one-token sequence) has no meaningful
+        # relative error: there an absolute 5e-4, well under one fp16 step of O(1) values, stands in for it
+        assert m["max_abs"] <= bound and (m["rel_l2"] <= loosen * REL_L2 or m["max_abs"] <= loosen * 5e-4), (k, m)
     e2_abs = float(want["e2"].abs().sum())
-    tol = loosen * 1e-2 * max(abs(float(want["dlambda"])), 1e-3 * e2_abs)
+    tol = max(loosen * 1e-2 * max(abs(float(want["dlambda"])), 1e-3 * e2_abs), 2e-3)
     assert abs(got["dlambda_fp32"] - float(want["dlambda"])) <= tol, (got["dlambda_fp32"], float(want["dlambda"]), tol)
 
 
@@ -117,6 +119,9 @@ RAGGED = [
     (1, 2, 328, 32, 0.5, 0.8, True, 65),
     (1, 1, 200, 128, 0.7, 0.2, False, 66),
     (1, 2, 456, 128, 0.5, 0.8, True, 67),
+    (1, 1, 1, 64, 0.5, 0.8, True, 68),          # a single token: every softmax is 1, A = (1 - lam) v
+    (2, 2, 8, 32, 0.5, 0.8, False, 69),
+    (1, 1, 127, 128, 0.5, 0.8, True, 70),
 ]
 
 
