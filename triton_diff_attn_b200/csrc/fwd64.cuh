@@ -18,7 +18,8 @@ constexpr int NUM_THREADS = 640;   // 16 softmax warps + 4 role warps, five per 
 constexpr int WARP_TMA = 16, WARP_S = 17, WARP_PV = 18;    // one role warp per scheduler (warp % 4)
 constexpr int MISC_BYTES = 12288;
 // pair index (of 16) of an exp pass after which the other branch may start its own pass; measured at c2:
-// 3 -> 1.05 ms, 7 -> 1.00, 9 and 11 -> 0.985, 13 -> 1.00, 15 (the end of the pass) -> 1.09 (no alternation: 1.06)
+// 3 -> 1.05 ms, 7 -> 1.00, 9 and 11 -> 0.985, 13 -> 1.00, 15 (the end of the pass) -> 1.09 (no alternation: 1.06).
+// Turns of two sub-tiles per branch instead of one: 1.23 ms (a branch's own hand-offs are no longer covered).
 constexpr int HANDOVER_AT = 11;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
 // named barriers: 1..8 the two warps of a (branch, row quarter); 9 all softmax threads; 10, 11 the 256 threads
