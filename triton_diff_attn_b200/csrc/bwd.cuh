@@ -189,8 +189,8 @@ constexpr int OFF_MISC = OFF_STAGE + ST * STAGE_BYTES;             // 195 KB
 constexpr int MISC_BYTES = 1024;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
 constexpr int NWG = 4;                      // elementwise warpgroups; warpgroup g owns query columns [16g, 16g+16)
-constexpr int NUM_THREADS = NWG * 128 + 64;
-constexpr int WARP_TMA = NWG * 4, WARP_MMA = NWG * 4 + 1;
+constexpr int NUM_THREADS = NWG * 128 + 128;                      // + TMA warp and three MMA-issuing warps, one per scheduler
+constexpr int WARP_TMA = NWG * 4, WARP_MMA = NWG * 4 + 1;         // issuers: WARP_MMA (S^T), +1 (dP^T), +2 (dV, dK)
 constexpr int T_DV = 0, T_DK1 = 128, T_DK2 = 192, T_S1 = 256, T_S2 = 320, T_DP = 384, T_DS1 = 448, T_DS2 = 480;
 struct Misc {
   uint64_t bar_kv;
@@ -229,7 +229,7 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
   if (warp == WARP_TMA && lane == 0) {
     mbar_init(&misc->bar_kv, 1);
     for (int i = 0; i < ST; ++i) { mbar_init(&misc->full[i], 1); mbar_init(&misc->empty[i], 1); }
-    mbar_init(&misc->s_full, 1);
+    mbar_init(&misc->s_full, 2);
     mbar_init(&misc->s_free, NWG * 128);
     mbar_init(&misc->e_done, NWG * 128);
     mbar_init(&misc->mma_done, 1);
@@ -265,29 +265,32 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
                      &misc->full[st]);
       }
     }
-  } else if (warp == WARP_MMA) {
-    // One elected thread issues every MMA; descriptors advance by 32-bit adds (see sm100.cuh).
+  } else if (warp == WARP_MMA || warp == WARP_MMA + 1) {
+    // ---- score issuers: warp WARP_MMA issues S1^T and S2^T of every tile, warp WARP_MMA + 1 issues dP^T.
+    // MMA issue is spread over three warps on three schedulers (these two and the output issuer below): one warp
+    // issuing all 32 MMAs of a tile takes ~300 clocks per tile from the elementwise warps of its scheduler, and
+    // every tile waits for that slowest quarter.  One elected thread per warp; descriptors advance by 32-bit adds.
     if (elect_one()) {
+      const bool is_dp = warp == WARP_MMA + 1;
       constexpr uint32_t IDESC_S = make_idesc(BKV, BQ, 0, 0, BF);     // S^T = K Q^T, dP^T = V dA^T
-      constexpr uint32_t IDESC_DV = make_idesc(BKV, DV, 0, 1, BF);    // dV += Pc^T dA   (Pc K-major smem, dA MN-major)
-      constexpr uint32_t IDESC_DK = make_idesc(BKV, HD, 0, 1, BF);    // dK += dS^T Q    (dS^T in TMEM, Q MN-major)
       const uint32_t k1_lo = sdesc_lo(smem_u32(smem + OFF_K1)), k2_lo = sdesc_lo(smem_u32(smem + OFF_K2));
       const uint32_t v_lo = sdesc_lo(smem_u32(smem + OFF_V));
-      const uint32_t pc_lo0 = sdesc_lo(smem_u32(smem + OFF_PC));
       const uint32_t st_lo0 = sdesc_lo(smem_u32(smem + OFF_STAGE));
-      constexpr uint32_t DA_MN_LBO = ((DA_BYTES / 2) >> 4) << 16;   // dA as MN-major B: 64-column atoms 8 KB apart
       const uint32_t tb = tmem_base;
       auto issue_scores = [&](uint32_t sp_lo) {
+        if (!is_dp) {
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) mma_ss_lo(tb + T_S1, k1_lo + k * 2, sp_lo + k * 2, IDESC_S, k > 0);
+          for (int k = 0; k < HD / 16; ++k) mma_ss_lo(tb + T_S1, k1_lo + k * 2, sp_lo + k * 2, IDESC_S, k > 0);
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
-          mma_ss_lo(tb + T_S2, k2_lo + k * 2, sp_lo + (Q_BYTES >> 4) + k * 2, IDESC_S, k > 0);
+          for (int k = 0; k < HD / 16; ++k)
+            mma_ss_lo(tb + T_S2, k2_lo + k * 2, sp_lo + (Q_BYTES >> 4) + k * 2, IDESC_S, k > 0);
+        } else {
 #pragma unroll
-        for (int k = 0; k < DV / 16; ++k)
-          mma_ss_lo(tb + T_DP, v_lo + (k / 4) * ((V_BYTES / 2) >> 4) + (k % 4) * 2,
-                    sp_lo + ((2 * Q_BYTES) >> 4) + (k / 4) * ((DA_BYTES / 2) >> 4) + (k % 4) * 2, IDESC_S, k > 0);
-        mma_commit(&misc->s_full);
+          for (int k = 0; k < DV / 16; ++k)
+            mma_ss_lo(tb + T_DP, v_lo + (k / 4) * ((V_BYTES / 2) >> 4) + (k % 4) * 2,
+                      sp_lo + ((2 * Q_BYTES) >> 4) + (k / 4) * ((DA_BYTES / 2) >> 4) + (k % 4) * 2, IDESC_S, k > 0);
+        }
+        mma_commit(&misc->s_full);        // two arrivals per tile: this warp's and the other score issuer's
       };
       bool ok = mbar_wait(&misc->bar_kv, 0, abort_flag, 501);
       ok = ok && mbar_wait(&misc->full[0], 0, abort_flag, 502);
@@ -296,49 +299,51 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
         issue_scores(st_lo0);
         int st = 0;
         uint32_t st_par = 0;
-        for (int i = 0; i < nq; ++i) {
-          const uint32_t sp_lo = st_lo0 + st * (STAGE_BYTES >> 4);
-          const uint32_t pc_lo = pc_lo0 + (i & 1) * (PC_BYTES >> 4);
-          const uint32_t ph = i & 1;
+        for (int i = 0; i + 1 < nq; ++i) {
           int st_n = st + 1;
           uint32_t par_n = st_par;
           if (st_n == ST) { st_n = 0; par_n ^= 1; }
-#ifdef DA_TIMING
-          const bool tm_on = (blockIdx.x == 3 && blockIdx.y == 1) && i >= 16 && i < 32;
-          const int tm_base = 1024 + 512 + (i - 16) * 8;
-#endif
-          DA_TS(0);
-          if (i + 1 < nq) {
-            if (!mbar_wait(&misc->full[st_n], par_n, abort_flag, 503, i)) break;
-            DA_TS(1);
-            if (!mbar_wait(&misc->s_free, ph, abort_flag, 504, i)) break;    // scores(i) are in registers
-            tc_fence_after();
-            DA_TS(2);
-            issue_scores(st_lo0 + st_n * (STAGE_BYTES >> 4));
-            DA_TS(3);
-          }
-          if (!mbar_wait(&misc->e_done, ph, abort_flag, 505, i)) break;
+          if (!mbar_wait(&misc->full[st_n], par_n, abort_flag, 503, i)) break;
+          if (!mbar_wait(&misc->s_free, i & 1, abort_flag, 504, i)) break;    // scores(i) are in registers
           tc_fence_after();
-          DA_TS(4);
-          const uint32_t first = i > 0;
-#pragma unroll
-          for (int k = 0; k < BQ / 16; ++k)
-            mma_ss_lo(tb + T_DV, pc_lo + k * 2, sp_lo + ((2 * Q_BYTES) >> 4) + DA_MN_LBO - (1u << 16) + k * (2048 >> 4), IDESC_DV,
-                      k > 0 ? 1u : first);
-#pragma unroll
-          for (int k = 0; k < BQ / 16; ++k)
-            mma_ts_lo(tb + T_DK1, tb + T_DS1 + k * 8, sp_lo + k * (2048 >> 4), IDESC_DK, k > 0 ? 1u : first);
-#pragma unroll
-          for (int k = 0; k < BQ / 16; ++k)
-            mma_ts_lo(tb + T_DK2, tb + T_DS2 + k * 8, sp_lo + (Q_BYTES >> 4) + k * (2048 >> 4), IDESC_DK, k > 0 ? 1u : first);
-          mma_commit(&misc->mma_done);
-          mma_commit(&misc->empty[st]);
-          DA_TS(5);
+          issue_scores(st_lo0 + st_n * (STAGE_BYTES >> 4));
           st = st_n;
           st_par = par_n;
         }
-        mma_commit(&misc->acc_full);
       }
+    }
+  } else if (warp == WARP_MMA + 2) {
+    // ---- output issuer: dV += Pc^T dA, dK_b += dS_b^T Q_b of tile i once the warpgroups have written their operands
+    if (elect_one()) {
+      constexpr uint32_t IDESC_DV = make_idesc(BKV, DV, 0, 1, BF);    // dV += Pc^T dA   (Pc K-major smem, dA MN-major)
+      constexpr uint32_t IDESC_DK = make_idesc(BKV, HD, 0, 1, BF);    // dK += dS^T Q    (dS^T in TMEM, Q MN-major)
+      const uint32_t pc_lo0 = sdesc_lo(smem_u32(smem + OFF_PC));
+      const uint32_t st_lo0 = sdesc_lo(smem_u32(smem + OFF_STAGE));
+      constexpr uint32_t DA_MN_LBO = ((DA_BYTES / 2) >> 4) << 16;   // dA as MN-major B: 64-column atoms 8 KB apart
+      const uint32_t tb = tmem_base;
+      int st = 0;
+      for (int i = 0; i < nq; ++i) {
+        const uint32_t sp_lo = st_lo0 + st * (STAGE_BYTES >> 4);
+        const uint32_t pc_lo = pc_lo0 + (i & 1) * (PC_BYTES >> 4);
+        // e_done(i) implies that stage i was loaded and that the score MMAs reading it have completed
+        if (!mbar_wait(&misc->e_done, i & 1, abort_flag, 505, i)) break;
+        tc_fence_after();
+        const uint32_t first = i > 0;
+#pragma unroll
+        for (int k = 0; k < BQ / 16; ++k)
+          mma_ss_lo(tb + T_DV, pc_lo + k * 2, sp_lo + ((2 * Q_BYTES) >> 4) + DA_MN_LBO - (1u << 16) + k * (2048 >> 4), IDESC_DV,
+                    k > 0 ? 1u : first);
+#pragma unroll
+        for (int k = 0; k < BQ / 16; ++k)
+          mma_ts_lo(tb + T_DK1, tb + T_DS1 + k * 8, sp_lo + k * (2048 >> 4), IDESC_DK, k > 0 ? 1u : first);
+#pragma unroll
+        for (int k = 0; k < BQ / 16; ++k)
+          mma_ts_lo(tb + T_DK2, tb + T_DS2 + k * 8, sp_lo + (Q_BYTES >> 4) + k * (2048 >> 4), IDESC_DK, k > 0 ? 1u : first);
+        mma_commit(&misc->mma_done);
+        mma_commit(&misc->empty[st]);
+        if (++st == ST) st = 0;
+      }
+      mma_commit(&misc->acc_full);
     }
   } else {
     const int g = warp >> 2;                       // warpgroup: query columns [16g, 16g+16) of every tile
@@ -581,7 +586,10 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
       }
     }
   } else if (warp == WARP_MMA) {
-    // One elected thread issues every MMA; descriptors advance by 32-bit adds (see sm100.cuh).
+    // One elected thread issues every MMA; descriptors advance by 32-bit adds (see sm100.cuh).  (Three issuing warps
+    // as in the dK/dV kernel were measured here too: 8 % slower, 1.00 against 0.92 ms.  This kernel reuses a score
+    // buffer as soon as the tensor pipe, which executes in issue order, has run the dQ MMAs that read it; separate
+    // issuers have to wait for a commit on an mbarrier instead, which costs more than the scheduler time saved.)
     if (elect_one()) {
       constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0, BF);    // S = Q K^T, dP = dA V^T
       constexpr uint32_t IDESC_DQ = make_idesc(BM, HD, 0, 1, BF);    // dQ += dS K   (K MN-major)
