@@ -587,9 +587,10 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
     }
   } else if (warp == WARP_MMA) {
     // One elected thread issues every MMA; descriptors advance by 32-bit adds (see sm100.cuh).  (Three issuing warps
-    // as in the dK/dV kernel were measured here too: 8 % slower, 1.00 against 0.92 ms.  This kernel reuses a score
-    // buffer as soon as the tensor pipe, which executes in issue order, has run the dQ MMAs that read it; separate
-    // issuers have to wait for a commit on an mbarrier instead, which costs more than the scheduler time saved.)
+    // as in the dK/dV kernel were measured here in two forms: split by kind (S | dP | dQ, which needs a committed
+    // mbarrier between the dQ and the S issuer because the score buffers are recycled on the tensor pipe's issue
+    // order): 1.00 against 0.92 ms; split by branch (S_b and dQ_b | dP, which keeps that order): 0.98 ms.  Both
+    // slower: the single issuer stays.)
     if (elect_one()) {
       constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0, BF);    // S = Q K^T, dP = dA V^T
       constexpr uint32_t IDESC_DQ = make_idesc(BM, HD, 0, 1, BF);    // dQ += dS K   (K MN-major)
