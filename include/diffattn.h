@@ -73,7 +73,7 @@ typedef struct DiffAttnParams {
   uint32_t dropout_threshold;      /* attention dropout (extension; the reference has none, README.md:2): 0 = off,
                                       else 1..255 = round(256 p): a probability is dropped when its hash byte is
                                       below the threshold, kept ones are scaled by 256/(256 - threshold).  The
-                                      backward must be given the forward's threshold and seed. */
+                                      backward must be given the forward's threshold and seed.  N <= 131072 with dropout. */
   uint64_t dropout_seed;           /* the mask is a pure function of (seed, batch*head, branch, row, column) */
   /* Learnable gain of the output norm (extension: the reference's norm has no weight, src/layers.py:75; the layer it
    * adapts has one).  gain == NULL: off.  Otherwise gain is fp32 [2D] on the device; the forward writes y (without

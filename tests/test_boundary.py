@@ -68,6 +68,7 @@ def test_null_and_struct(L):
     (lambda p: setattr(p, "lambda_dtype", 9), -7),
     (lambda p: setattr(p, "io_dtype", 2), -7),
     (lambda p: setattr(p, "dropout_threshold", 256), -3),
+    (lambda p: (setattr(p, "dropout_threshold", 26), setattr(p, "N", 131200)), -3),
     (lambda p: setattr(p, "B", 70000), -3),
 ])
 def test_fwd_rejects(L, mutate, code):

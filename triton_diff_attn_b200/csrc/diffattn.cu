@@ -93,6 +93,8 @@ int check_common(const DiffAttnParams* p, bool bwd) {
   if (p->gain && bwd && !p->dgain) return fail(DIFFATTN_ERR_NULL_PTR, "gain given: dgain is NULL");
   if (p->dropout_threshold > 255)
     return fail(DIFFATTN_ERR_BAD_SHAPE, "dropout_threshold %u exceeds 255", p->dropout_threshold);
+  if (p->dropout_threshold && p->N > 131072)      // the mask's counter packs (row >> 1, column >> 1) into 16 + 16 bits
+    return fail(DIFFATTN_ERR_BAD_SHAPE, "dropout supports N <= 131072 (got %d)", p->N);
   if ((long long)p->B * p->H > 65535)
     return fail(DIFFATTN_ERR_BAD_SHAPE, "B*H=%lld exceeds the grid limit 65535", (long long)p->B * p->H);
   if (p->B == 0 || p->H == 0 || p->N == 0) return 1;   // empty: nothing to do
