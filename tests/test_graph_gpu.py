@@ -52,7 +52,7 @@ def test_capture_and_replay(d, causal):
         dl.zero_()
         _lib.check(_lib.lib.diffattn_fwd(p1), "fwd in capture")
         _lib.check(_lib.lib.diffattn_bwd(p1), "bwd in capture")
-    for round_ in range(2):
+    for _rep in range(2):
         for t in [y] + grads:
             t.zero_()
         g.replay()
