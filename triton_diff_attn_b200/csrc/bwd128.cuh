@@ -199,6 +199,11 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
             if (i < c0) s[i] = 0xff800000u;
         }
       }
+      float4 svb[DA_PF];                     // key side: statistics of the next DA_PF streamed columns
+      if (!QSIDE) {
+#pragma unroll
+        for (int j = 0; j < DA_PF; ++j) svb[j] = lds_v4(stats + j);
+      }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         float v[2];
@@ -213,7 +218,8 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
           const int j = 2 * i + w;
           float nl = neg_l, ee = e;
           if (!QSIDE) {
-            const float4 sv = stats[j];
+            const float4 sv = svb[j % DA_PF];
+            if (j + DA_PF < 16) svb[j % DA_PF] = lds_v4(stats + j + DA_PF);
             nl = br ? -sv.y : -sv.x;
             ee = br ? sv.w : sv.z;
           }
@@ -424,6 +430,9 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
             if (j < c0) { s1[j] = 0xff800000u; s2[j] = 0xff800000u; }
         }
       }
+      float4 svb[DA_PF];                     // statistics of the next DA_PF columns (see lds_v4 in bwd.cuh)
+#pragma unroll
+      for (int j = 0; j < DA_PF; ++j) svb[j] = lds_v4(stats + j);
 #pragma unroll
       for (int jj = 0; jj < 8; ++jj) {
         float v[2];
@@ -436,7 +445,8 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
 #pragma unroll
         for (int w = 0; w < 2; ++w) {
           const int j = 2 * jj + w;
-          const float4 sv = stats[j];
+          const float4 sv = svb[j % DA_PF];
+          if (j + DA_PF < 16) svb[j % DA_PF] = lds_v4(stats + j + DA_PF);
           float k1 = 1.f, k2 = sg;
           if constexpr (DROP) {
             k1 = drop_keep(h1, 2 * w + dcol_odd, args.drop_thresh) ? args.drop_scale : 0.f;
