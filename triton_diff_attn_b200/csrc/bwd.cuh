@@ -48,6 +48,7 @@ struct BwdArgs {
 // ------------------------------------------------------------------------------------------------
 // 1. preprocess: one warp per row, DV = 32 * VPL halves per row
 // ------------------------------------------------------------------------------------------------
+constexpr int PRE_ROWS = 4;
 template <int VPL, bool BF>   // 16-bit elements per lane: 2 (DV=64), 4 (DV=128), 8 (DV=256); BF: bf16 tensors
 __global__ void __launch_bounds__(256) diffattn_bwd_pre_kernel(const BwdArgs args) {
   constexpr int DV = 32 * VPL;
@@ -66,24 +67,43 @@ __global__ void __launch_bounds__(256) diffattn_bwd_pre_kernel(const BwdArgs arg
   for (int i = 0; i < VPL; ++i) { gn[i] = has_gain ? args.gain[lane * VPL + i] : 1.f; dg_acc[i] = 0.f; }
   __shared__ float dg_red[8][DV];
 
-  for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + warp; row < args.rows; row += warps_total) {
+  // PRE_ROWS rows per warp and trip: all their loads are issued before the first reduction, which keeps four times
+  // the bytes in flight per warp (one row per trip ran at 26 % of the DRAM rate: the shuffles of a row's two
+  // reductions sat between its loads and the next row's).
+  const long long first = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+  for (long long row0 = first; row0 < args.rows; row0 += warps_total * PRE_ROWS) {
+    __align__(16) __half hdr[PRE_ROWS][VPL], hyr[PRE_ROWS][VPL], har[PRE_ROWS][VPL];
+    float rsr[PRE_ROWS], l1r[PRE_ROWS], l2r[PRE_ROWS];
+#pragma unroll
+    for (int rr = 0; rr < PRE_ROWS; ++rr) {
+      const long long row = row0 + rr * warps_total;
+      if (row < args.rows) {
+        const size_t off = size_t(row) * DV + lane * VPL;
+        __half* hd = hdr[rr]; __half* hy = hyr[rr]; __half* ha = har[rr];
+        if constexpr (VPL == 8) {
+          *reinterpret_cast<uint4*>(hd) = *reinterpret_cast<const uint4*>(args.dy + off);
+          *reinterpret_cast<uint4*>(hy) = *reinterpret_cast<const uint4*>(args.y + off);
+          *reinterpret_cast<uint4*>(ha) = *reinterpret_cast<const uint4*>(args.a2 + off);
+        } else if constexpr (VPL == 4) {
+          *reinterpret_cast<uint2*>(hd) = *reinterpret_cast<const uint2*>(args.dy + off);
+          *reinterpret_cast<uint2*>(hy) = *reinterpret_cast<const uint2*>(args.y + off);
+          *reinterpret_cast<uint2*>(ha) = *reinterpret_cast<const uint2*>(args.a2 + off);
+        } else {
+          *reinterpret_cast<uint32_t*>(hd) = *reinterpret_cast<const uint32_t*>(args.dy + off);
+          *reinterpret_cast<uint32_t*>(hy) = *reinterpret_cast<const uint32_t*>(args.y + off);
+          *reinterpret_cast<uint32_t*>(ha) = *reinterpret_cast<const uint32_t*>(args.a2 + off);
+        }
+        rsr[rr] = args.rstd[row]; l1r[rr] = args.lse1[row]; l2r[rr] = args.lse2[row];
+      }
+    }
+#pragma unroll
+    for (int rr = 0; rr < PRE_ROWS; ++rr) {      // (body kept at the indentation of the one-row loop it came from)
+    const long long row = row0 + rr * warps_total;
+    if (row >= args.rows) break;
     const size_t off = size_t(row) * DV + lane * VPL;
+    const __half* hd = hdr[rr]; const __half* hy = hyr[rr]; const __half* ha = har[rr];
     float dy[VPL], yv[VPL], a2[VPL];
     {
-      __half hd[VPL], hy[VPL], ha[VPL];
-      if constexpr (VPL == 8) {
-        *reinterpret_cast<uint4*>(hd) = *reinterpret_cast<const uint4*>(args.dy + off);
-        *reinterpret_cast<uint4*>(hy) = *reinterpret_cast<const uint4*>(args.y + off);
-        *reinterpret_cast<uint4*>(ha) = *reinterpret_cast<const uint4*>(args.a2 + off);
-      } else if constexpr (VPL == 4) {
-        *reinterpret_cast<uint2*>(hd) = *reinterpret_cast<const uint2*>(args.dy + off);
-        *reinterpret_cast<uint2*>(hy) = *reinterpret_cast<const uint2*>(args.y + off);
-        *reinterpret_cast<uint2*>(ha) = *reinterpret_cast<const uint2*>(args.a2 + off);
-      } else {
-        *reinterpret_cast<uint32_t*>(hd) = *reinterpret_cast<const uint32_t*>(args.dy + off);
-        *reinterpret_cast<uint32_t*>(hy) = *reinterpret_cast<const uint32_t*>(args.y + off);
-        *reinterpret_cast<uint32_t*>(ha) = *reinterpret_cast<const uint32_t*>(args.a2 + off);
-      }
 #pragma unroll
       for (int i = 0; i < VPL; ++i) { dy[i] = to_float16b<BF>(hd[i]); yv[i] = to_float16b<BF>(hy[i]); a2[i] = to_float16b<BF>(ha[i]); }
     }
@@ -99,7 +119,7 @@ __global__ void __launch_bounds__(256) diffattn_bwd_pre_kernel(const BwdArgs arg
       for (int i = 0; i < VPL; ++i) t += dy[i] * yv[i];
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-      const float r = args.rstd[row];
+      const float r = rsr[rr];
       const float inv_c = c != 0.f ? 1.f / c : 0.f;
       const float k1 = r * c, k2 = r * inv_c * t * (1.f / DV), k3 = inv_c / r;
 #pragma unroll
@@ -132,9 +152,10 @@ __global__ void __launch_bounds__(256) diffattn_bwd_pre_kernel(const BwdArgs arg
       // -lam P2 = sg P2' and -lam P2 (dP - E2) = P2' (sg dP - w).  lam = 0 gives y = +inf, P2' = 0.
       const float sg = lam < 0.f ? 1.f : -1.f;
       const long long bh_i = row / args.n;
-      args.stats[bh_i * args.n_pad + (row - bh_i * args.n)] = make_float4(args.lse1[row] * LOG2E, args.lse2[row] * LOG2E - log2f(fabsf(lam)), ea + lam * e2, sg * e2);
+      args.stats[bh_i * args.n_pad + (row - bh_i * args.n)] = make_float4(l1r[rr] * LOG2E, l2r[rr] * LOG2E - log2f(fabsf(lam)), ea + lam * e2, sg * e2);
       dl_acc -= e2;
     }
+  }
   }
   if (lane == 0) red[warp] = dl_acc;
   if (has_gain) {
