@@ -6,11 +6,10 @@
 // identical in both, and the RMSNorm sum of squares is accumulated over the two passes.  With rms_norm the first
 // half of A waits as 16-bit pairs in registers until the second pass has produced rstd.  Streamed tiles are 64
 // rows: {K1, K2, V half}, one ring slot per score sub-tile.
-// Warp roles as in fwd64.cuh: sixteen softmax warps (each row of a sub-tile split between two threads), a TMA warp,
+// Sixteen softmax warps (each row of a sub-tile split between two threads), a TMA warp,
 // an S issuer and one P V issuer per branch; the two branches take turns on the exp unit.
 #pragma once
 #include "fwd.cuh"
-#include "fwd64.cuh"   // fwd64_rescale_o
 #include "sm100.cuh"
 
 namespace da {
@@ -28,7 +27,7 @@ constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
 constexpr int NUM_THREADS = 640;
 constexpr int WARP_TMA = 16, WARP_S = 17, WARP_PV = 18;
 constexpr int T_O = 256;
-constexpr int HANDOVER_AT = 11;    // as fwd64::HANDOVER_AT
+constexpr int HANDOVER_AT = 11;    // pair (of 16) of an exp pass after which the other branch may start (see fwd64.cuh)
 
 struct Misc {
   uint64_t bar_q;
@@ -281,7 +280,7 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
         mbar_arrive(&misc->p_full[br][u]);
       }
 
-      // a warp that left the loop early stands in, without blocking, for the pair barriers it skipped (see fwd64.cuh)
+      // a warp that left the loop early stands in, without blocking, for the pair barriers it skipped (its partner may have got past the same wait a moment earlier)
       for (; synced < nsub; ++synced) named_bar_arrive(pair_bar, 64);
 
       // ---- epilogue of this pass (value columns [128 pass, 128 pass + 128)); every thread runs every barrier
