@@ -78,18 +78,4 @@ constexpr int T_O = 256;
 
 __device__ __forceinline__ float max3(float a, float b, float c) { return fmaxf(fmaxf(a, b), c); }
 
-// O_b[:, 64 columns from t_o] *= scale for this thread's row.  Rare (the running maximum grew by more than 2^8): kept
-// out of line where the exp loop's register budget is tight (the sixteen-warp D = 128 forward, 96 registers).
-__device__ __noinline__ void fwd64_rescale_o(uint32_t t_o, float scale) {
-#pragma unroll 1
-  for (int c = 0; c < 2; ++c) {
-    uint32_t o[32];
-    tmem_ld32(t_o + c * 32, o);
-    tc_wait_ld();
-#pragma unroll
-    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * scale);
-    tmem_st32(t_o + c * 32, o);
-  }
-}
-
 }  // namespace da

@@ -1,13 +1,13 @@
 // Differential-attention forward for head dim D = 128 (value width 256), sm_100a.
 //
-// TMEM map as at D <= 64 (fwd.cuh): S1/S2 in two 64-column buffers each, O1 and O2 128 columns each.  Two 256-wide
-// accumulators do not fit in TMEM, so one CTA makes two passes over the key/value sequence, one per 128-column half
-// of V: the scores and probabilities are recomputed in the second pass (same values), the row statistics are
-// identical in both, and the RMSNorm sum of squares is accumulated over the two passes.  With rms_norm the first
-// half of A waits as 16-bit pairs in registers until the second pass has produced rstd.  Streamed tiles are 64
-// rows: {K1, K2, V half}, one ring slot per score sub-tile.
-// Sixteen softmax warps (each row of a sub-tile split between two threads), a TMA warp,
-// an S issuer and one P V issuer per branch; the two branches take turns on the exp unit.
+// Same roles and TMEM map as the D <= 64 kernel (fwd.cuh, fwd64.cuh): S1/S2 in two 64-column buffers each, O1 and
+// O2 128 columns each; eight softmax warps whose two branches take turns on the exp unit; here one warp issues every
+// MMA.  Two 256-wide accumulators do not fit in TMEM, so one CTA makes two passes over the key/value sequence, one per
+// 128-column half of V: the scores and probabilities are recomputed in the second pass (same values), the row
+// statistics are identical in both, and the RMSNorm sum of squares is accumulated over the two passes.  With rms_norm
+// the first half of A is parked as 16-bit pairs in registers until the second pass has produced rstd.  Streamed tiles
+// are 64 rows: {K1, K2, V half}.  (A sixteen-softmax-warp form with per-branch P V issuers and turns measured 1.31 ms
+// against this form's 1.16 ms at B=4 H=8 N=4096; this form without turns ran config 4's forward in 9.06 ms.)
 #pragma once
 #include "fwd.cuh"
 #include "sm100.cuh"
@@ -22,27 +22,23 @@ constexpr int V_BYTES = SUB * 128 * 2;          // 16 KB: the pass's 128 value c
 constexpr int STAGE_BYTES = 2 * K_BYTES + V_BYTES;   // 48 KB
 constexpr int OFF_Q1 = 0, OFF_Q2 = Q_BYTES, OFF_STAGE = 2 * Q_BYTES;   // 64 KB
 constexpr int OFF_MISC = OFF_STAGE + ST * STAGE_BYTES;                 // 208 KB
-constexpr int MISC_BYTES = 12288;
+constexpr int MISC_BYTES = 4096;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
-constexpr int NUM_THREADS = 640;
-constexpr int WARP_TMA = 16, WARP_S = 17, WARP_PV = 18;
+constexpr int NUM_THREADS = 320;
 constexpr int T_O = 256;
-constexpr int HANDOVER_AT = 11;    // pair (of 16) of an exp pass after which the other branch may start (see fwd64.cuh)
+constexpr int HANDOVER_AT = 22;   // element pair (of 32) of an exp pass after which the other branch may start (see fwd64.cuh)
 
 struct Misc {
   uint64_t bar_q;
-  uint64_t full[ST];         // stage loaded (TMA bytes)
-  uint64_t empty[ST];        // stage consumed: S issuer and both P V issuers have committed (3 arrivals)
-  uint64_t s_full[2][2];     // [branch][buffer]
-  uint64_t p_full[2][2];     // [branch][buffer], 256 arrivals
-  uint64_t pv_done[2][2];    // [branch][buffer]
-  uint64_t o_full;           // a pass's accumulators complete (2 arrivals: one per P V issuer)
-  uint64_t turn[2];          // [branch]: that branch may run its next exp pass (8 arrivals)
+  uint64_t full[ST], empty[ST];
+  uint64_t s_full[2][2], p_full[2][2];
+  uint64_t o_done[2];
+  uint64_t o_full;
+  uint64_t turn[2];
   uint32_t tmem_slot;
   int abort_flag;
-  float xmax[2][2][2][BM];   // [sub-tile parity][branch][half][row]
-  float lpart[2][2][BM];     // [branch][half][row]
-  float ssq[4][BM];
+  float coef1[BM], coef2[BM];
+  float ssq[2][BM];
 };
 static_assert(sizeof(Misc) <= MISC_BYTES, "misc area too small");
 }  // namespace fwd128
@@ -64,29 +60,26 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
   const int nsub = (args.causal && 2 * (q_tile + 1) < nsub_all) ? 2 * (q_tile + 1) : nsub_all;   // causal: stop at the diagonal tile
   const int ntot = 2 * nsub;          // sub-tiles over both passes
 
-  if (warp == WARP_TMA && lane == 0) {
+  if (warp == 8 && lane == 0) {
     mbar_init(&misc->bar_q, 1);
-    for (int i = 0; i < ST; ++i) { mbar_init(&misc->full[i], 1); mbar_init(&misc->empty[i], 3); }
-    for (int b = 0; b < 2; ++b)
-      for (int u = 0; u < 2; ++u) {
-        mbar_init(&misc->s_full[b][u], 1);
-        mbar_init(&misc->p_full[b][u], 256);
-        mbar_init(&misc->pv_done[b][u], 1);
-      }
-    mbar_init(&misc->o_full, 2);
-    mbar_init(&misc->turn[0], 8);
-    mbar_init(&misc->turn[1], 8);
+    for (int i = 0; i < ST; ++i) { mbar_init(&misc->full[i], 1); mbar_init(&misc->empty[i], 1); }
+    for (int b = 0; b < 2; ++b) {
+      for (int u = 0; u < 2; ++u) { mbar_init(&misc->s_full[b][u], 1); mbar_init(&misc->p_full[b][u], 128); }
+      mbar_init(&misc->o_done[b], 1);
+    }
+    mbar_init(&misc->o_full, 1);
+    mbar_init(&misc->turn[0], 4);
+    mbar_init(&misc->turn[1], 4);
     misc->abort_flag = 0;
     mbar_init_fence();
   }
-  if (warp == WARP_S) tmem_alloc(&misc->tmem_slot, 512);
+  if (warp == 9) tmem_alloc(&misc->tmem_slot, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&misc->tmem_slot);
 
-  if (warp == WARP_TMA) {
-    // ------------------------------- TMA producer -------------------------------
+  if (warp == 8) {
     if (elect_one()) {
       mbar_expect_tx(&misc->bar_q, 2 * Q_BYTES);
       for (int c = 0; c < 2; ++c) {
@@ -108,159 +101,152 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
         if (++st == ST) { st = 0; par ^= 1; }
       }
     }
-  } else if (warp == WARP_S) {
-    // ------------------- S issuer: S_b(gt) = Q_b K_b(sub-tile)^T, both branches, buffer gt & 1 -------------------
+  } else if (warp == 9) {
     if (elect_one()) {
       constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0, BF);
+      constexpr uint32_t IDESC_O = make_idesc(BM, 128, 0, 1, BF);
       const uint32_t q1_lo = sdesc_lo(smem_u32(smem + OFF_Q1)), q2_lo = sdesc_lo(smem_u32(smem + OFF_Q2));
       const uint32_t st_lo0 = sdesc_lo(smem_u32(smem + OFF_STAGE));
-      bool ok = mbar_wait(&misc->bar_q, 0, abort_flag, 2201);
-      int st = 0;
-      uint32_t par = 0;
-      for (int gt = 0; ok && gt < ntot; ++gt) {
-        const int u = gt & 1;
-        const uint32_t sp_lo = st_lo0 + st * (STAGE_BYTES >> 4);
-        if (!mbar_wait(&misc->full[st], par, abort_flag, 2202, gt)) break;
+      const uint32_t tb = tmem_base;
+      auto issue_s = [&](uint32_t sp_lo, int u) {
 #pragma unroll
-        for (int br = 0; br < 2; ++br) {
-          // the buffer is free once P_b V of the sub-tile two back (which read P from it) has completed
-          if (gt >= 2) {
-            if (!mbar_wait(&misc->pv_done[br][u], ((gt - 2) >> 1) & 1, abort_flag, 2203 + br, gt)) { ok = false; break; }
+        for (int k = 0; k < HD / 16; ++k)
+          mma_ss_lo(tb + u * SUB, q1_lo + (k / 4) * (16384 >> 4) + (k % 4) * 2, sp_lo + (k / 4) * (8192 >> 4) + (k % 4) * 2, IDESC_S, k > 0);
+        mma_commit(&misc->s_full[0][u]);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          mma_ss_lo(tb + 128 + u * SUB, q2_lo + (k / 4) * (16384 >> 4) + (k % 4) * 2,
+                    sp_lo + (K_BYTES >> 4) + (k / 4) * (8192 >> 4) + (k % 4) * 2, IDESC_S, k > 0);
+        mma_commit(&misc->s_full[1][u]);
+      };
+      bool ok = mbar_wait(&misc->bar_q, 0, abort_flag, 2201);
+      ok = ok && mbar_wait(&misc->full[0], 0, abort_flag, 2202);
+      if (ok) {
+        tc_fence_after();
+        issue_s(st_lo0, 0);
+        int st = 0;
+        uint32_t par = 0;
+        for (int gt = 0; gt < ntot; ++gt) {
+          const int u = gt & 1;
+          const int t = gt >= nsub ? gt - nsub : gt;
+          const uint32_t sp_lo = st_lo0 + st * (STAGE_BYTES >> 4);
+          // V half-tile as MN-major B: 128 columns = two atoms 8 KB apart
+          const uint32_t v_lo = sp_lo + ((2 * K_BYTES) >> 4) + ((8192u >> 4) << 16) - (1u << 16);
+          int st_n = st + 1;
+          uint32_t par_n = par;
+          if (st_n == ST) { st_n = 0; par_n ^= 1; }
+          if (gt + 1 < ntot) {
+            if (!mbar_wait(&misc->full[st_n], par_n, abort_flag, 2203, gt)) break;
+            tc_fence_after();
+            issue_s(st_lo0 + st_n * (STAGE_BYTES >> 4), u ^ 1);
           }
+          const uint32_t ph = (gt >> 1) & 1;
+          if (!mbar_wait(&misc->p_full[0][u], ph, abort_flag, 2204, gt)) break;
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < HD / 16; ++k)      // K = 128: two 64-column atoms of Q (16 KB apart) and of K (8 KB apart)
-            mma_ss_lo(tmem_base + br * 128 + u * SUB, (br ? q2_lo : q1_lo) + (k / 4) * (16384 >> 4) + (k % 4) * 2,
-                      sp_lo + br * (K_BYTES >> 4) + (k / 4) * (8192 >> 4) + (k % 4) * 2, IDESC_S, k > 0);
-          mma_commit(&misc->s_full[br][u]);
-        }
-        if (!ok) break;
-        mma_commit(&misc->empty[st]);
-        if (++st == ST) { st = 0; par ^= 1; }
-      }
-    }
-  } else if (warp == WARP_PV || warp == WARP_PV + 1) {
-    // ------------------- P V issuer of one branch: O_b += P_b(gt) V_half(sub-tile) -------------------
-    if (elect_one()) {
-      const int br = warp - WARP_PV;
-      constexpr uint32_t IDESC_O = make_idesc(BM, 128, 0, 1, BF);
-      const uint32_t st_lo0 = sdesc_lo(smem_u32(smem + OFF_STAGE));
-      const uint32_t t_o = tmem_base + T_O + br * 128, t_p = tmem_base + br * 128;
-      int st = 0;
-      uint32_t par = 0;
-      for (int gt = 0; gt < ntot; ++gt) {
-        const int u = gt & 1;
-        const int t = gt >= nsub ? gt - nsub : gt;
-        // V half-tile as MN-major B: 128 columns = two atoms 8 KB apart
-        const uint32_t v_lo = st_lo0 + st * (STAGE_BYTES >> 4) + ((2 * K_BYTES) >> 4) + ((8192u >> 4) << 16) - (1u << 16);
-        if (!mbar_wait(&misc->full[st], par, abort_flag, 2205, gt)) break;
-        if (!mbar_wait(&misc->p_full[br][u], (gt >> 1) & 1, abort_flag, 2206 + br, gt)) break;
-        tc_fence_after();
+          for (int k = 0; k < SUB / 16; ++k)
+            mma_ts_lo(tb + T_O, tb + u * SUB + k * 8, v_lo + k * (2048 >> 4), IDESC_O, (t > 0 || k > 0));
+          mma_commit(&misc->o_done[0]);
+          if (!mbar_wait(&misc->p_full[1][u], ph, abort_flag, 2205, gt)) break;
+          tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < SUB / 16; ++k)
-          mma_ts_lo(t_o, t_p + u * SUB + k * 8, v_lo + k * (2048 >> 4), IDESC_O, (t > 0 || k > 0));
-        mma_commit(&misc->pv_done[br][u]);
-        mma_commit(&misc->empty[st]);
-        if (t == nsub - 1) mma_commit(&misc->o_full);
-        if (++st == ST) { st = 0; par ^= 1; }
+          for (int k = 0; k < SUB / 16; ++k)
+            mma_ts_lo(tb + T_O + 128, tb + 128 + u * SUB + k * 8, v_lo + k * (2048 >> 4), IDESC_O, (t > 0 || k > 0));
+          mma_commit(&misc->o_done[1]);
+          mma_commit(&misc->empty[st]);
+          if (t == nsub - 1) mma_commit(&misc->o_full);
+          st = st_n;
+          par = par_n;
+        }
       }
     }
   } else {
-    // ------------------------- softmax warps + per-pass epilogue -------------------------
-    const int br = warp >> 3;                        // branch
-    const int half = (warp >> 2) & 1;                // which 32 of a sub-tile's 64 columns
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;             // query row inside the tile = TMEM lane
-    const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+    const int br = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
     const uint32_t t_s0 = tmem_base + lane_base + br * 128;
-    const uint32_t t_o = tmem_base + lane_base + T_O + br * 128 + half * 64;   // the 64 columns of O_b this thread rescales
+    const uint32_t t_o = tmem_base + lane_base + T_O + br * 128;
     const float sl2 = args.sm_scale * 1.4426950408889634f;
     const float lam = load_lambda(args.lambda_ptr, args.lambda_dtype);
-    const int pair_bar = 1 + br * 4 + quarter;       // the two warps that share these 32 rows of this branch
     const size_t grow = size_t(bh) * args.n + size_t(q_tile) * BM + row;
-    const int w4 = br * 2 + half;                    // epilogue: owns value columns [32 w4, 32 w4 + 32) of a pass's 128
     bool ok = true;
     float ssq_total = 0.f;
     // dropout (same decisions in both passes: they depend on the position only)
     const uint32_t dkey = DROP ? drop_key(args.seed_lo, args.seed_hi, uint32_t(bh), uint32_t(br)) : 0u;
     const uint32_t drow2 = uint32_t(q_tile * BM + row) >> 1;
     const int drow_odd = row & 1;
-    uint32_t parked[16];            // first-pass A (this thread's 32 columns) as 16-bit pairs, used with rms_norm
+    uint32_t parked[32];            // first-pass A (this thread's 64 columns) as fp16 pairs, used with rms_norm
 #pragma unroll
-    for (int i = 0; i < 16; ++i) parked[i] = 0u;
+    for (int i = 0; i < 32; ++i) parked[i] = 0u;
 
     for (int pass = 0; pass < 2; ++pass) {
-      float m_run = -INFINITY, l_run = 0.f;          // running maximum (same in both halves), own share of the denominator
-      int synced = 0;                                // pair barriers passed in this pass
+      float m_run = -INFINITY, l_run = 0.f;
       for (int t = 0; t < nsub; ++t) {
         const int gt = pass * nsub + t;
-        const int u = gt & 1;
-        const uint32_t t_s = t_s0 + u * SUB;
-        if (!mbar_wait(&misc->s_full[br][u], (gt >> 1) & 1, abort_flag, 2301 + br, gt)) { ok = false; break; }
+        const uint32_t t_s = t_s0 + (gt & 1) * SUB;
+        if (!mbar_wait(&misc->s_full[br][gt & 1], (gt >> 1) & 1, abort_flag, 2301 + br, gt)) { ok = false; break; }
         tc_fence_after();
-        uint32_t sr[32];
-        tmem_ld32(t_s + half * 32, sr);
+        uint32_t sr[SUB];
+        tmem_ld32(t_s + 0, sr);
+        tmem_ld32(t_s + 32, sr + 32);
         tc_wait_ld();
         {
-          const int c_first = t * SUB + half * 32;   // key columns past the end or (causal) right of the diagonal: -inf
-          int nv = args.n - c_first;
-          if (args.causal) nv = min(nv, q_tile * BM + row - c_first + 1);
-          if (nv < 32) {
+          int nv = args.n - t * SUB;             // visible key columns of this row in this sub-tile; the rest get -inf
+          if (args.causal) nv = min(nv, q_tile * BM + row - t * SUB + 1);
+          if (nv < SUB) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
+            for (int i = 0; i < SUB; ++i)
               if (i >= nv) sr[i] = 0xff800000u;
           }
         }
         float neg = -m_run * sl2;
         float sum[4] = {0.f, 0.f, 0.f, 0.f};
         float mx[4];
-        uint32_t pk[16];
+        uint32_t pk[SUB / 2];
 #pragma unroll
         for (int c = 0; c < 4; ++c) mx[c] = __uint_as_float(sr[c]);
-        // the two branches take turns on the exp unit (see fwd64.cuh)
         if (!mbar_wait(&misc->turn[br], (gt + 1 + br) & 1, abort_flag, 2321 + br, gt)) { ok = false; break; }
         if (t > 0) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
+          for (int i = 0; i < SUB / 2; ++i) {
+            if (i == HANDOVER_AT) { __syncwarp(); if (lane == 0) mbar_arrive(&misc->turn[br ^ 1]); }
             const float p0 = ex2v(fmaf(__uint_as_float(sr[2 * i]), sl2, neg));
             const float p1 = ex2v(fmaf(__uint_as_float(sr[2 * i + 1]), sl2, neg));
             sum[(2 * i) & 3] += p0;
             sum[(2 * i + 1) & 3] += p1;
             pk[i] = pack2<BF>(p0, p1);
             mx[i & 3] = max3(mx[i & 3], __uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]));
-            if (i == HANDOVER_AT) {
-              __syncwarp();
-              if (lane == 0) mbar_arrive(&misc->turn[br ^ 1]);
-            }
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
+          for (int i = 0; i < SUB / 2; ++i)
             mx[i & 3] = max3(mx[i & 3], __uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]));
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&misc->turn[br ^ 1]);
+          __syncwarp(); if (lane == 0) mbar_arrive(&misc->turn[br ^ 1]);
         }
-        // the row's maximum over all 64 columns: exchange with the thread that holds the other 32
-        const float m_loc = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-        misc->xmax[u][br][half][row] = m_loc;
-        named_bar_sync(pair_bar, 64);
-        ++synced;
-        const float m_new = fmaxf(m_loc, misc->xmax[u][br][half ^ 1][row]);
+        const float m_new = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
         const bool need = (t == 0) || ((m_new - m_run) * sl2 > 8.f);
-        if (__any_sync(0xffffffffu, need)) {          // same outcome in both warps of the pair
+        if (__any_sync(0xffffffffu, need)) {
           if (t > 0) {
-            if (!mbar_wait(&misc->pv_done[br][(gt - 1) & 1], ((gt - 1) >> 1) & 1, abort_flag, 2305 + br, gt)) { ok = false; break; }
+            if (!mbar_wait(&misc->o_done[br], (gt - 1) & 1, abort_flag, 2305 + br, gt)) { ok = false; break; }
             tc_fence_after();
             const float scale = need ? ex2((m_run - m_new) * sl2) : 1.f;
             l_run *= scale;
-            fwd64_rescale_o(t_o, scale);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t o[32];
+              tmem_ld32(t_o + c * 32, o);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * scale);
+              tmem_st32(t_o + c * 32, o);
+            }
           }
           if (need) m_run = m_new;
           neg = -m_run * sl2;
 #pragma unroll
           for (int c = 0; c < 4; ++c) sum[c] = 0.f;
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
+          for (int i = 0; i < SUB / 2; ++i) {
             const float p0 = ex2(fmaf(__uint_as_float(sr[2 * i]), sl2, neg));
             const float p1 = ex2(fmaf(__uint_as_float(sr[2 * i + 1]), sl2, neg));
             sum[(2 * i) & 3] += p0;
@@ -271,51 +257,49 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
         l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);     // the softmax denominator is taken before dropout
         if constexpr (DROP) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            pk[i] &= drop_pair_mask(drop_hash(dkey, drow2, uint32_t(t * (SUB / 2) + half * 16 + i)), drow_odd, args.drop_thresh);
+          for (int i = 0; i < SUB / 2; ++i)
+            pk[i] &= drop_pair_mask(drop_hash(dkey, drow2, uint32_t(t * (SUB / 2) + i)), drow_odd, args.drop_thresh);
         }
-        tmem_st16(t_s + half * 16, pk);
+        tmem_st32(t_s, pk);
         tc_wait_st();
         tc_fence_before();
-        mbar_arrive(&misc->p_full[br][u]);
+        mbar_arrive(&misc->p_full[br][gt & 1]);
       }
-
-      // a warp that left the loop early stands in, without blocking, for the pair barriers it skipped (its partner may have got past the same wait a moment earlier)
-      for (; synced < nsub; ++synced) named_bar_arrive(pair_bar, 64);
 
       // ---- epilogue of this pass (value columns [128 pass, 128 pass + 128)); every thread runs every barrier
       ok = ok && mbar_wait(&misc->o_full, pass & 1, abort_flag, 2311 + br, pass);
       tc_fence_after();
-      misc->lpart[br][half][row] = l_run;
-      named_bar_sync(9, 512);
-      const float dsc = DROP ? args.drop_scale : 1.f;
-      const float l1 = misc->lpart[0][0][row] + misc->lpart[0][1][row];
-      const float l2 = misc->lpart[1][0][row] + misc->lpart[1][1][row];
-      const float c1 = dsc / l1, c2 = dsc / l2;
-      uint32_t o1[32], o2[32];
-      tmem_ld32(tmem_base + lane_base + T_O + w4 * 32, o1);
-      tmem_ld32(tmem_base + lane_base + T_O + 128 + w4 * 32, o2);
+      const float inv_l = (DROP ? args.drop_scale : 1.f) / l_run;
+      if (br == 0) misc->coef1[row] = inv_l; else misc->coef2[row] = inv_l;
+      named_bar_sync(1, 256);
+      const float c1 = misc->coef1[row], c2 = misc->coef2[row];
+      const uint32_t t_o1 = tmem_base + lane_base + T_O + br * 64;
+      const uint32_t t_o2 = tmem_base + lane_base + T_O + 128 + br * 64;
+      uint32_t o1[64], o2[64];
+      tmem_ld32(t_o1, o1);
+      tmem_ld32(t_o1 + 32, o1 + 32);
+      tmem_ld32(t_o2, o2);
+      tmem_ld32(t_o2 + 32, o2 + 32);
       tc_wait_ld();
       float ssq = 0.f;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
+      for (int i = 0; i < 64; ++i) {
         const float a2v = __uint_as_float(o2[i]) * c2;
         const float av = __uint_as_float(o1[i]) * c1 - lam * a2v;
         ssq += av * av;
         o1[i] = __float_as_uint(av);
         o2[i] = __float_as_uint(a2v);
       }
-      misc->ssq[w4][row] = ssq;
+      misc->ssq[br][row] = ssq;
       tc_fence_before();
-      named_bar_sync(9, 512);          // all O reads are complete here: the next pass may overwrite O (and lpart, ssq)
-      ssq_total += (misc->ssq[0][row] + misc->ssq[1][row]) + (misc->ssq[2][row] + misc->ssq[3][row]);
-      named_bar_sync(9, 512);          // ... and every thread has read the partial sums before they are rewritten
+      named_bar_sync(1, 256);          // all O reads are complete here: the next pass may overwrite O
+      ssq_total += misc->ssq[0][row] + misc->ssq[1][row];
       const bool live = ok && !*abort_flag && (q_tile * BM + row < args.n);
-      const int col0 = pass * 128 + w4 * 32;
+      const int col0 = pass * 128 + br * 64;
       if (live) {
         uint4* ap = reinterpret_cast<uint4*>(args.a2 + grow * DV + col0);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < 8; ++i) {
           uint4 av;
           av.x = pack2<BF>(__uint_as_float(o2[8 * i + 0]), __uint_as_float(o2[8 * i + 1]));
           av.y = pack2<BF>(__uint_as_float(o2[8 * i + 2]), __uint_as_float(o2[8 * i + 3]));
@@ -339,7 +323,7 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
       if (!args.rms_norm) {
         if (live) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
+          for (int i = 0; i < 8; ++i) {
             float f[8];
 #pragma unroll
             for (int k = 0; k < 8; ++k) f[k] = __uint_as_float(o1[8 * i + k]);
@@ -348,13 +332,13 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
         }
       } else if (pass == 0) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) parked[i] = pack2<BF>(__uint_as_float(o1[2 * i]), __uint_as_float(o1[2 * i + 1]));
+        for (int i = 0; i < 32; ++i) parked[i] = pack2<BF>(__uint_as_float(o1[2 * i]), __uint_as_float(o1[2 * i + 1]));
       } else {
         const float rstd = rsqrtf(ssq_total * (1.f / DV) + args.eps);
         const float ys = args.out_scale * rstd;
         if (live) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
+          for (int i = 0; i < 8; ++i) {
             float f[8];
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -362,15 +346,15 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
               f[2 * c] = w.x * ys;
               f[2 * c + 1] = w.y * ys;
             }
-            put_y(w4 * 32 + 8 * i, f);
+            put_y(br * 64 + 8 * i, f);
 #pragma unroll
             for (int k = 0; k < 8; ++k) f[k] = __uint_as_float(o1[8 * i + k]) * ys;
             put_y(col0 + 8 * i, f);
           }
         }
       }
-      if (pass == 1 && live && half == 0) {
-        const float lse = m_run * args.sm_scale + logf(br ? l2 : l1);
+      if (pass == 1 && live) {
+        const float lse = m_run * args.sm_scale + logf(l_run);
         if (br == 0) {
           args.lse1[grow] = lse;
           args.rstd[grow] = rsqrtf(ssq_total * (1.f / DV) + args.eps);
@@ -383,7 +367,7 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
 
   tc_fence_before();
   __syncthreads();
-  if (warp == WARP_S) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }

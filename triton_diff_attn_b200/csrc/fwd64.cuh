@@ -7,7 +7,7 @@
 // tcgen05.ld, exp pass, tcgen05.st, arrive) together, since their scores complete together, and the exp unit idles
 // during the hand-offs.  History at config 2: without turns 1.04-1.06 ms; sixteen softmax warps (each row split
 // between two threads, exchanging the row maximum through shared memory) without turns 1.06, with turns 0.985-1.00;
-// this form 0.94-0.96.  The D = 128 forward (fwd128.cuh) still uses the sixteen-warp form.
+// this form 0.94-0.96.
 #pragma once
 #include "fwd.cuh"
 
