@@ -39,8 +39,8 @@ WORKLOADS = {
 }
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
 # profiles/c2_kernels_ncu_full.md (workload c2); other workloads report null.
-NCU_TRAFFIC_BYTES = {"c2": {"diffattn_fwd64_kernel": 307.2e6, "diffattn_bwd_pre_kernel": 256.1e6,
-                            "diffattn_bwd_dkdv64_kernel": 380.9e6, "diffattn_bwd_dq64_kernel": 325.5e6}}
+NCU_TRAFFIC_BYTES = {"c2": {"diffattn_fwd64_kernel": 309.9e6, "diffattn_bwd_pre_kernel": 257.1e6,
+                            "diffattn_bwd_dkdv64_kernel": 383.2e6, "diffattn_bwd_dq64_kernel": 326.0e6}}
 METRIC = "diff-attn fwd+bwd TFLOP/s (credited 28*B*H*N^2*D), fp16"
 NOMINAL_TFLOPS = 2250.0
 
