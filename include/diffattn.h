@@ -4,10 +4,14 @@
  * reference's autograd Function launches its Triton kernels:
  *   diffattn_fwd  <->  _diff_attention.forward  (reference src/kernel.py:463-514, kernel :21-207)
  *   diffattn_bwd  <->  _diff_attention.backward (reference src/kernel.py:516-575, kernel :221-458)
- * The caller owns every buffer; the library allocates nothing on the device.  All device work is
- * enqueued on `stream`; no call synchronises the host with the device except diffattn_status().
- * Every function returns 0 on success or a negative DIFFATTN_ERR_* code; nothing is launched after a
- * failed check.  diffattn_last_error() gives the message of the calling thread's last failure.
+ * The caller owns every buffer; the library never calls an allocator.  (Its image does carry one fixed
+ * DIFFATTN_STATIC_SCRATCH_BYTES array per GPU, resident on every GPU that loads the library and used only
+ * by diffattn_bwd_static.)  All device work is enqueued on `stream`; no call synchronises the host with the
+ * device except diffattn_status().  Every entry point leaves the calling thread's current CUDA device as it
+ * found it.  Every function returns 0 on success or a negative DIFFATTN_ERR_* code; nothing is launched
+ * after a failed check.  diffattn_last_error() gives the message of the calling thread's last failure.
+ * Host-side state: a mutex-protected cache of encoded TMA descriptors (keyed by base pointer, shape, strides,
+ * box and type), of per-kernel launch attributes and of the device each base pointer was found on.
  */
 #ifndef DIFFATTN_H_
 #define DIFFATTN_H_
@@ -19,7 +23,7 @@
 extern "C" {
 #endif
 
-#define DIFFATTN_VERSION 1
+#define DIFFATTN_VERSION 2
 
 enum {
   DIFFATTN_OK = 0,
@@ -32,7 +36,8 @@ enum {
   DIFFATTN_ERR_BAD_DTYPE = -7,      /* lambda dtype tag unknown */
   DIFFATTN_ERR_WORKSPACE = -8,      /* workspace missing or too small */
   DIFFATTN_ERR_CUDA = -9,           /* a CUDA runtime/driver call failed */
-  DIFFATTN_ERR_TIMEOUT = -10        /* a device-side wait gave up (reported by diffattn_status) */
+  DIFFATTN_ERR_TIMEOUT = -10,       /* a device-side wait gave up (reported by diffattn_status) */
+  DIFFATTN_ERR_WRONG_DEVICE = -11   /* a tensor pointer is not device memory of `device` (host memory, another GPU) */
 };
 
 enum { DIFFATTN_LAMBDA_F16 = 0, DIFFATTN_LAMBDA_F32 = 1, DIFFATTN_LAMBDA_BF16 = 2 };
@@ -82,6 +87,14 @@ typedef struct DiffAttnParams {
   const float* gain;
   void* y_gained;
   float* dgain;
+  /* Backward for head dims 32 and 64.  0 (default): two tensor-core kernels, the second of which recomputes the
+   * scores per query block (as the reference's second loop does, src/kernel.py:426-436); every output tile has one
+   * owner, the gradients are bit-reproducible.  1: ONE pass over the score tiles; every key block adds its share of
+   * dQ1, dQ2 to an fp32 workspace with atomic adds, so dq1/dq2 can differ in the last bit between two runs (the
+   * order of the adds is not fixed; dk1, dk2, dv are unaffected).  Measured on B200 the single pass is the slower
+   * of the two (both forms move the same number of shared-memory bytes per score tile, which is what bounds them,
+   * and the atomic adds come on top); it is kept as an option.  Ignored for head dim 128. */
+  int32_t single_pass;
 } DiffAttnParams;
 
 /* Forward.  Reads q1,q2,k1,k2,v,lambda_scale; writes y,a2,lse1,lse2,rstd.
@@ -93,11 +106,15 @@ int diffattn_fwd(const DiffAttnParams* p);
  * Replaces _diff_attention.backward + diff_attn_bwd (reference src/kernel.py:516-575, :221-458). */
 int diffattn_bwd(const DiffAttnParams* p);
 
-/* The backward is three kernels (row preprocess, dK/dV, dQ).  This entry runs a subset, for timing
- * each kernel on its own; DKDV and DQ read what PRE wrote to the workspace.  diffattn_bwd(p) is
- * diffattn_bwd_stages(p, DIFFATTN_STAGE_ALL).  (The reference's backward is one kernel,
- * src/kernel.py:221-458: stage 1 at :273-299, the dK/dV half at :410-424, the dQ half at :426-436.) */
-enum { DIFFATTN_STAGE_PRE = 1, DIFFATTN_STAGE_DKDV = 2, DIFFATTN_STAGE_DQ = 4, DIFFATTN_STAGE_ALL = 7 };
+/* The backward is a few kernels; this entry runs a subset, for timing each kernel on its own.  Every later
+ * stage reads what PRE wrote to the workspace (with single_pass = 1 PRE also zeroes the dQ partial sums).
+ *   single_pass = 0 or head dim 128:  PRE, DKDV, DQ
+ *   single_pass = 1, head dim <= 64:  PRE, FUSED (dK, dV and the dQ partial sums in one pass), DQ_FINISH
+ * diffattn_bwd(p) runs the stages of p's form in that order; a stage that does not belong to p's form is
+ * DIFFATTN_ERR_BAD_SHAPE.  (The reference's backward is one kernel, src/kernel.py:221-458: stage 1 at
+ * :273-299, the dK/dV half at :410-424, the dQ half at :426-436.) */
+enum { DIFFATTN_STAGE_PRE = 1, DIFFATTN_STAGE_DKDV = 2, DIFFATTN_STAGE_DQ = 4, DIFFATTN_STAGE_FUSED = 8,
+       DIFFATTN_STAGE_DQ_FINISH = 16 };
 int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages);
 
 /* Backward without a caller-provided workspace and without any allocation.  (No counterpart in the
@@ -111,11 +128,13 @@ int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages);
  *
  * The scratch (dA and the per-row statistics) lives in one array of DIFFATTN_STATIC_SCRATCH_BYTES that
  * is part of the library image: every GPU that loads the library holds it until the process exits.
- * Limit: diffattn_workspace_bytes(p) must not exceed it (B*H*N <= 123361 rows at D = 64), otherwise
- * DIFFATTN_ERR_WORKSPACE is returned and nothing is launched.
+ * Limit: diffattn_workspace_bytes(p) must not exceed it (at D = 64: B*H*N <= 123361 rows; 42799 with
+ * single_pass = 1), otherwise DIFFATTN_ERR_WORKSPACE is returned and nothing is launched.
  * The first call on each device looks the array's device address up (one cudaGetSymbolAddress, no
- * allocation); make that first call outside any stream capture.  The call itself uses no cudaMalloc,
- * cudaFree or allocating library routine.
+ * allocation) and keeps it; make that first call outside any stream capture.  The kept address is void
+ * after cudaDeviceReset() of that device: do not reset a device between calls.  The call itself uses no
+ * cudaMalloc, cudaFree or allocating library routine.  An empty shape (B, H or N = 0) returns 0 without
+ * touching the device.
  * All calls on a device share the one array and it keeps what the previous call left there.  Nothing
  * in it has to start at zero (the preprocess kernel rewrites every byte the other kernels read), but
  * two calls whose kernels overlap on the GPU (different streams, no ordering) race on it: order
@@ -123,8 +142,8 @@ int diffattn_bwd_stages(const DiffAttnParams* p, int32_t stages);
 #define DIFFATTN_STATIC_SCRATCH_BYTES (32u << 20)
 int diffattn_bwd_static(const DiffAttnParams* p);
 
-/* Scratch bytes diffattn_bwd needs for these shapes (the reference allocates its D1/D2 and
- * dLambda partial buffers itself, src/kernel.py:522-529).  The forward needs none. */
+/* Scratch bytes diffattn_bwd needs for these shapes and p->single_pass (the reference allocates its
+ * D1/D2 and dLambda partial buffers itself, src/kernel.py:522-529).  The forward needs none. */
 uint64_t diffattn_workspace_bytes(const DiffAttnParams* p);
 
 /* Synchronises `device` and reads the device-side status word: 0, or DIFFATTN_ERR_TIMEOUT with the

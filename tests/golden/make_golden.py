@@ -30,7 +30,7 @@ from oracle import diffattn_oracle as oracle  # noqa: E402
 
 CASES = [
     # name, B, H, N, D, scale, lambda, lambda_init, rms_norm, dy_uniform, seed
-    ("c1_b2h16n512d32", 2, 16, 512, 32, 1.0, 0.5, 0.8, True, False, 1234),     # BASELINE config 1
+    ("c1_b2h16n512d32", 2, 16, 512, 32, 1.0, 0.5, 0.8, True, False, 1234),     # the CPU-runnable benchmark shape (fp32 on the host)
     ("selftest_b2h2n256d32", 2, 2, 256, 32, 0.5, 0.5, 0.8, True, True, 77),    # src/kernel.py:581-596
     ("small_d64_rms", 1, 2, 256, 64, 1.0, 0.5, 0.8, True, False, 5),
     ("small_d64_norms_neg", 1, 2, 128, 64, 1.0, -0.5, 0.2, False, False, 6),

@@ -39,7 +39,8 @@ def test_exports_match_header(L):
     raw = ctypes.CDLL(L.LIB_PATH)
     for name in declared:
         assert hasattr(raw, name), name
-    assert L.lib.diffattn_version() == 1
+    assert L.lib.diffattn_version() == 2
+    assert "DIFFATTN_ERR_WRONG_DEVICE = -11" in hdr and L.ERR_NAMES[-11] == "WRONG_DEVICE"
 
 
 def test_supports(L):
@@ -47,6 +48,7 @@ def test_supports(L):
     assert L.lib.diffattn_supports(32, 0) == 1 and L.lib.diffattn_supports(32, 1) == 1
     assert L.lib.diffattn_supports(128, 0) == 1 and L.lib.diffattn_supports(128, 1) == 1
     assert L.lib.diffattn_supports(48, 0) == 0 and L.lib.diffattn_supports(256, 0) == 0
+    assert L.lib.diffattn_supports(64, 2) == 0          # directions are 0 (forward) and 1 (backward)
 
 
 def test_null_and_struct(L):
@@ -86,13 +88,27 @@ def test_bwd_rejects_missing_workspace_and_grads(L):
     assert L.lib.diffattn_bwd(p) == -8             # no workspace
     need = L.lib.diffattn_workspace_bytes(p)
     rows = 2 * 2 * 256
-    assert need == rows * 128 * 2 + rows * 16
+    assert need == rows * 128 * 2 + rows * 16        # dA + statistics
+    p.single_pass = 1                                # + fp32 partial sums of dQ1, dQ2: [2][B*H][N_pad][64]
+    assert L.lib.diffattn_workspace_bytes(p) == rows * 128 * 2 + rows * 16 + 2 * rows * 64 * 4
+    p.single_pass = 0
     q = _good(L, n=200)      # ragged length: the statistics rows are padded to a multiple of 128 per (batch, head)
     assert L.lib.diffattn_workspace_bytes(q) == 2 * 2 * 200 * 128 * 2 + 2 * 2 * 256 * 16
+    q.single_pass = 1
+    assert L.lib.diffattn_workspace_bytes(q) == 2 * 2 * 200 * 128 * 2 + 2 * 2 * 256 * 16 + 2 * 2 * 2 * 256 * 64 * 4
+    q128 = _good(L, n=256, d=128)
+    q128.single_pass = 1
+    assert L.lib.diffattn_workspace_bytes(q128) == rows * 256 * 2 + rows * 16      # head dim 128 has no single-pass form
     p.workspace, p.workspace_bytes = 0x10010, need
     assert L.lib.diffattn_bwd_stages(p, L.STAGE_PRE) == -6   # workspace not 256-byte aligned
     p.workspace, p.workspace_bytes = 0x10100, need - 1
     assert L.lib.diffattn_bwd(p) == -8
+    # a stage that does not belong to the call's form is refused before anything touches the device
+    p.workspace_bytes = need
+    assert L.lib.diffattn_bwd_stages(p, L.STAGE_FUSED | L.STAGE_PRE) == -3 and "form" in L.last_error()
+    p.single_pass = 1
+    p.workspace_bytes = L.lib.diffattn_workspace_bytes(p)
+    assert L.lib.diffattn_bwd_stages(p, L.STAGE_DQ) == -3
 
 
 def test_empty_is_ok_without_device(L):
@@ -100,6 +116,7 @@ def test_empty_is_ok_without_device(L):
     p.B = 0
     assert L.lib.diffattn_fwd(p) == 0
     assert L.lib.diffattn_workspace_bytes(p) == 0
+    assert L.lib.diffattn_bwd(p) == 0 and L.lib.diffattn_bwd_static(p) == 0
 
 
 def test_python_wrapper_has_no_cpu_path():

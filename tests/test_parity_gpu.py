@@ -72,9 +72,9 @@ CASES = [
     (1, 1, 1024, 64, 0.5, 0.3, 0.8, True, 18),
     # head dim 32: the reference's own test and benchmark shapes (src/kernel.py:581-584, src/benchmark.py:19-25)
     (2, 2, 256, 32, 0.5, 0.5, 0.8, True, 31),
-    (2, 16, 512, 32, 1.0, 0.5, 0.8, True, 32),      # BASELINE config 1 / README.md example shape
+    (2, 16, 512, 32, 1.0, 0.5, 0.8, True, 32),      # the CPU-runnable benchmark shape / README.md example shape
     (1, 2, 384, 32, 1.0, -0.4, 0.2, False, 33),
-    # head dim 128 (value width 256): BASELINE config 4 family (rms_norm off, lambda 0.7, lambda_init 0.2) and rms on
+    # head dim 128 (value width 256): rms_norm off with lambda 0.7, lambda_init 0.2 (the wide-head benchmark's settings) and rms on
     (1, 1, 256, 128, 1.0, 0.7, 0.2, False, 41),
     (2, 2, 512, 128, 1.0, 0.7, 0.2, False, 42),
     (1, 2, 384, 128, 1.0, 0.5, 0.8, True, 43),
@@ -390,6 +390,62 @@ def test_deterministic_repeat(op):
     for k in ("y",) + GRADS:
         assert torch.equal(a[k], b[k]), k
     assert abs(a["dlambda_fp32"] - b["dlambda_fp32"]) <= 1e-4 * max(1.0, abs(a["dlambda_fp32"]))
+    # single_pass=True sums the key blocks' shares of dq1/dq2 with fp32 atomic adds in arrival order: dq1/dq2 agree
+    # with the default form to the rounding of that fp32 sum (far inside the parity tolerance); dv, dk1, dk2 are
+    # accumulated over the query tiles in another order, and agree likewise
+    c = run_gpu(op, q1, q2, k1, k2, v, dy, 0.5, 0.8, True, single_pass=True)
+    assert torch.equal(c["y"], a["y"])
+    for k in GRADS:
+        m = oracle.error_metrics(c[k], a[k].float())
+        assert m["rel_l2"] <= 2e-4 and m["max_abs"] <= 2e-3 * max(1.0, float(a[k].abs().max())), (k, m)
+
+
+@pytest.mark.parametrize("b,h,n,d,lam,lam_init,rms,causal,seed", [
+    (2, 2, 512, 64, 0.5, 0.8, True, False, 121), (1, 2, 200, 64, -0.3, 0.8, True, False, 122),
+    (1, 2, 384, 32, 0.5, 0.8, False, False, 123), (1, 2, 328, 64, 0.5, 0.8, True, True, 124),
+    (1, 1, 1, 64, 0.5, 0.8, True, False, 125), (2, 1, 129, 32, 0.5, 0.2, True, True, 126),
+    (1, 2, 1000, 64, 0.5, 0.8, True, False, 127)])
+def test_single_pass_backward_matches_oracle(op, b, h, n, d, lam, lam_init, rms, causal, seed):
+    """The one-pass backward (single_pass=True: dK, dV and atomic partial sums of dQ from one kernel) against the
+    oracle; every other test runs the default two-kernel form."""
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(b, h, n, d, seed)
+    want = oracle.backward_closed_form(q1, q2, k1, k2, v, torch.tensor([lam]), dy, lam_init, rms, causal=causal)
+    got = run_gpu(op, q1, q2, k1, k2, v, dy, lam, lam_init, rms, causal=causal, single_pass=True)
+    check(got, want)
+
+
+def test_single_pass_backward_with_dropout_and_bf16(op):
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(1, 2, 328, 64, 128, dtype=torch.bfloat16)
+    th = op.layers.dropout_threshold(0.25)
+    want = oracle.backward_closed_form(q1, q2, k1, k2, v, torch.tensor([0.5]), dy, 0.8, True, dropout_threshold=th, dropout_seed=77)
+    got = run_gpu(op, q1, q2, k1, k2, v, dy, 0.5, 0.8, True, dropout_p=0.25, dropout_seed=77, single_pass=True)
+    check(got, want, loosen=8.0)
+
+
+def test_expanded_and_odd_layouts(op):
+    """Layouts the reference's pointer arithmetic accepts but TMA cannot address as they lie: keys broadcast over
+    heads with stride 0 (`expand`), and a slice whose base is not 16-byte aligned.  The wrapper copies them."""
+    b, h, n, d = 1, 2, 256, 64
+    q1, q2, k1, k2, v, dy = oracle.make_inputs(b, h, n, d, 131)
+    k1e = k1[:, :1].expand(b, h, n, d)
+    k2e = k2[:, :1].expand(b, h, n, d)
+    want = oracle.backward_closed_form(q1, q2, k1e.contiguous(), k2e.contiguous(), v, torch.tensor([0.5]), dy, 0.8, True)
+    dev = torch.device("cuda", 0)
+    big = torch.zeros(b * h * n * d + 4, dtype=torch.float16, device=dev)
+    q1_odd = big[4:].view(b, h, n, d)                       # base pointer 8 bytes past a 16-byte boundary
+    q1_odd.copy_(q1.to(dev))
+    assert q1_odd.data_ptr() % 16 != 0
+    leaves = [q1_odd.requires_grad_(True), q2.to(dev).requires_grad_(True), k1.to(dev)[:, :1].expand(b, h, n, d).requires_grad_(True),
+              k2.to(dev)[:, :1].expand(b, h, n, d).requires_grad_(True), v.to(dev).requires_grad_(True)]
+    assert leaves[2].stride(1) == 0
+    lam_t = torch.tensor([0.5], device=dev, requires_grad=True)
+    y = op.MultiheadDiffAttnKernel(*leaves, lam_t, 0.8, True)
+    y.backward(dy.to(dev))
+    op.device_status(0)
+    got = {"y": y.detach().cpu(), "dlambda_fp32": float(op.DiffAttnFunction.last_dlambda_fp32.cpu())}
+    for nm, t in zip(GRADS, leaves):
+        got[nm] = t.grad.detach().cpu()
+    check(got, want)
 
 
 def test_reference_golden_selfcheck_tolerance(op, golden_dir):
@@ -409,7 +465,7 @@ def test_reference_golden_selfcheck_tolerance(op, golden_dir):
 @pytest.mark.parametrize("name", ["selftest_b2h2n256d32", "c1_b2h16n512d32"])
 def test_reference_golden_d32(op, golden_dir, name):
     """Head dim 32 against the vectors produced by the reference's own PyTorch path at the reference's
-    self-test shape (src/kernel.py:581-596: N(0, 0.5^2) inputs, uniform dY) and at BASELINE config 1, with the
+    self-test shape (src/kernel.py:581-596: N(0, 0.5^2) inputs, uniform dY) and at B2 H16 N512 D32, with the
     reference's acceptance test allclose(atol=1e-2, rtol=0) (src/kernel.py:624-635, src/benchmark.py:293)."""
     z = np.load(os.path.join(golden_dir, name + ".npz"))
     b, h, n, d, seed = (int(x) for x in z["meta"])
@@ -422,8 +478,27 @@ def test_reference_golden_d32(op, golden_dir, name):
     assert abs(got["dlambda_fp32"] - float(z["dlambda"][0])) <= 1e-2 * max(abs(float(z["dlambda"][0])), 1.0)
 
 
-def test_full_size_properties_config2(op):
-    """BASELINE config 2 (B4 H16 N4096 D64): size-independent properties instead of a full oracle
+def _check_full_batch_dlambda(op, q1, q2, k1, k2, v, dy, lam, lam_init, rms, dl_got):
+    """d(lambda) of the WHOLE call (the fp32 scalar that every CTA of the preprocess kernel added its share to)
+    against -sum(E2) from the fp32 oracle run on the GPU one head at a time (TF32 off) and summed in fp64 on the
+    host.  Tolerance: max(1e-2 |dlambda|, 1e-4 sum|E2|)."""
+    dev = torch.device("cuda", 0)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    total, mag = 0.0, 0.0
+    b, h = q1.shape[:2]
+    for bi in range(b):
+        for hi in range(h):
+            sl = lambda t: t[bi:bi + 1, hi:hi + 1].contiguous()
+            w = oracle.backward_closed_form(sl(q1), sl(q2), sl(k1), sl(k2), sl(v), torch.tensor([lam]), sl(dy), lam_init, rms,
+                                            device=dev)
+            total += float(w["dlambda"])
+            mag += float(w["e2"].double().abs().sum())
+    tol = max(1e-2 * abs(total), 1e-4 * mag)
+    assert abs(dl_got - total) <= tol, (dl_got, total, tol)
+
+
+def test_full_size_properties_b4_h16_n4096_d64(op):
+    """B4 H16 N4096 D64 (the headline shape): size-independent properties instead of a full oracle
     pass, plus the oracle on one sampled (batch, head).
       * heads are independent: the sampled head computed alone equals its slice of the full run;
       * linearity in dY: backward(2 dY) = 2 backward(dY) up to fp16 subnormal rounding of dS."""
@@ -439,6 +514,7 @@ def test_full_size_properties_config2(op):
     y = op.MultiheadDiffAttnKernel(*leaves, lam_t, 0.8, True)
     y.backward(dy.to(dev), retain_graph=True)
     op.device_status(0)
+    dl_full = float(op.DiffAttnFunction.last_dlambda_fp32.cpu())
     full = {"y": y.detach().cpu()}
     for nm, t in zip(GRADS, leaves):
         full[nm] = t.grad.detach().cpu().clone()
@@ -457,10 +533,11 @@ def test_full_size_properties_config2(op):
     alone = run_gpu(op, sl(q1), sl(q2), sl(k1), sl(k2), sl(v), sl(dy), 0.5, 0.8, True)
     for k in ("y",) + GRADS:
         assert torch.equal(alone[k], sl(full[k])), k
+    _check_full_batch_dlambda(op, q1, q2, k1, k2, v, dy, 0.5, 0.8, True, dl_full)
 
 
 def _full_size_case(op, b, h, n, d, scale, lam, lam_init, rms, seed, bi, hi):
-    """Run the operator at a BASELINE size; check one sampled (batch, head) against the fp32 restatement
+    """Run the operator at a full benchmark size; check one sampled (batch, head) against the fp32 restatement
     evaluated by torch on the GPU (TF32 off; the N x N matrices are too slow on the host at these N),
     head independence bit for bit, and d(lambda) of the sampled head alone."""
     dev = torch.device("cuda", 0)
@@ -476,6 +553,7 @@ def _full_size_case(op, b, h, n, d, scale, lam, lam_init, rms, seed, bi, hi):
     y = op.MultiheadDiffAttnKernel(*leaves, lam_t, lam_init, rms)
     y.backward(dy)
     op.device_status(0)
+    dl_full = float(op.DiffAttnFunction.last_dlambda_fp32.cpu())
     sl = lambda t: t[bi:bi + 1, hi:hi + 1].contiguous()
     full = {"y": sl(y.detach())}
     for nm, t in zip(GRADS, leaves):
@@ -497,20 +575,22 @@ def _full_size_case(op, b, h, n, d, scale, lam, lam_init, rms, seed, bi, hi):
     dl = float(op.DiffAttnFunction.last_dlambda_fp32.cpu())
     tol = 1e-2 * max(abs(float(want["dlambda"])), 1e-3 * float(want["e2"].abs().sum()))
     assert abs(dl - float(want["dlambda"])) <= tol, (dl, float(want["dlambda"]))
+    # and d(lambda) of the whole batch, every head
+    _check_full_batch_dlambda(op, q1, q2, k1, k2, v, dy, lam, lam_init, rms, dl_full)
 
 
-def test_full_size_config3_long_sequence(op):
-    """BASELINE config 3: B=1 H=32 N=16384 D=64, inputs scaled by 0.5, lambda 0.3, rms_norm on."""
+def test_full_size_b1_h32_n16384_d64_long_sequence(op):
+    """B=1 H=32 N=16384 D=64, inputs scaled by 0.5, lambda 0.3, rms_norm on."""
     _full_size_case(op, 1, 32, 16384, 64, 0.5, 0.3, 0.8, True, seed=333, bi=0, hi=17)
 
 
-def test_full_size_config5_one_gpu_share(op):
-    """BASELINE config 5 as one of 8 GPUs sees it: B=8 H=32 N=4096 D=64 (B*H = 256 of the 2048 heads)."""
+def test_full_size_b8_h32_n4096_d64_one_gpu_share(op):
+    """B=64 H=32 N=4096 D=64 as one of 8 GPUs sees it: B=8 H=32 (B*H = 256 of the 2048 heads)."""
     _full_size_case(op, 8, 32, 4096, 64, 1.0, 0.5, 0.8, True, seed=555, bi=5, hi=9)
 
 
-def test_full_size_config4_wide_head(op):
-    """BASELINE config 4: B=8 H=8 N=8192 D=128 (v width 256), rms_norm off, lambda 0.7, lambda_init 0.2."""
+def test_full_size_b8_h8_n8192_d128_wide_head(op):
+    """B=8 H=8 N=8192 D=128 (v width 256), rms_norm off, lambda 0.7, lambda_init 0.2."""
     _full_size_case(op, 8, 8, 8192, 128, 1.0, 0.7, 0.2, False, seed=444, bi=3, hi=6)
 
 

@@ -9,20 +9,21 @@ import ctypes as C
 import os
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG_DIR, "libdiffattn.so")
+# DIFFATTN_LIBRARY names another build of the same library (for instance one compiled with other tuning macros)
+LIB_PATH = os.environ.get("DIFFATTN_LIBRARY") or os.path.join(PKG_DIR, "libdiffattn.so")
 
 EXPORTS = ("diffattn_fwd", "diffattn_bwd", "diffattn_bwd_stages", "diffattn_bwd_static", "diffattn_workspace_bytes", "diffattn_status",
            "diffattn_last_error", "diffattn_version", "diffattn_supports")
 
 ERR_NAMES = {
     0: "OK", -1: "NULL_PTR", -2: "BAD_STRUCT", -3: "BAD_SHAPE", -4: "UNSUPPORTED_D", -5: "BAD_STRIDE",
-    -6: "MISALIGNED", -7: "BAD_DTYPE", -8: "WORKSPACE", -9: "CUDA", -10: "TIMEOUT",
+    -6: "MISALIGNED", -7: "BAD_DTYPE", -8: "WORKSPACE", -9: "CUDA", -10: "TIMEOUT", -11: "WRONG_DEVICE",
 }
-VALUE_ERRORS = (-1, -2, -3, -4, -5, -6, -7, -8)   # caller mistakes -> ValueError; the rest RuntimeError
+VALUE_ERRORS = (-1, -2, -3, -4, -5, -6, -7, -8, -11)   # caller mistakes -> ValueError; the rest RuntimeError
 
 LAMBDA_F16, LAMBDA_F32, LAMBDA_BF16 = 0, 1, 2
 IO_F16, IO_BF16 = 0, 1
-STAGE_PRE, STAGE_DKDV, STAGE_DQ, STAGE_ALL = 1, 2, 4, 7
+STAGE_PRE, STAGE_DKDV, STAGE_DQ, STAGE_FUSED, STAGE_DQ_FINISH = 1, 2, 4, 8, 16
 STATIC_SCRATCH_BYTES = 32 << 20
 
 
@@ -42,6 +43,7 @@ class DiffAttnParams(C.Structure):
         ("dlambda", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64),
         ("io_dtype", C.c_int32), ("dropout_threshold", C.c_uint32), ("dropout_seed", C.c_uint64),
         ("gain", C.c_void_p), ("y_gained", C.c_void_p), ("dgain", C.c_void_p),
+        ("single_pass", C.c_int32),
     ]
 
 

@@ -15,7 +15,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libdiffattn.so")
 SOURCES = ["diffattn.cu"]
-HEADERS = ["sm100.cuh", "fwd.cuh", "fwd64.cuh", "fwd128.cuh", "bwd.cuh", "bwd128.cuh", os.path.join("..", "..", "include", "diffattn.h")]
+HEADERS = ["sm100.cuh", "fwd.cuh", "fwd64.cuh", "fwd128.cuh", "bwd.cuh", "bwd128.cuh", "bwd_fused64.cuh", os.path.join("..", "..", "include", "diffattn.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -1,6 +1,7 @@
 // Differential-attention backward for sm_100a, head dim D = 64 (value width 128).
 //
-// Three kernels replace the reference's single Triton backward (src/kernel.py:221-458):
+// Three kernels (the default form of the backward) replace the reference's single Triton backward
+// (src/kernel.py:221-458); bwd_fused64.cuh holds the optional form that merges 2 and 3:
 //   1. bwd_pre      per row: dA = RMSNorm-backward(dY) (src/kernel.py:283-290), E1, E2 row sums
 //                   (the reference's D1 and D2/(-lambda), :295-296), d(lambda) = -sum E2 with one
 //                   atomic per CTA (division-free; the reference divides by lambda+eps, :293).
@@ -43,6 +44,9 @@ struct BwdArgs {
   float drop_scale;     // 256 / (256 - drop_thresh)
   const float* gain;    // NULL, or fp32 [2D]: then dy is the gradient of y * gain, and sum_rows(dy * y) is added to dgain
   float* dgain;         // fp32 [2D]
+  float* dq_acc;        // NULL, or workspace fp32 [2][B*H][n_pad][64]: partial sums of dQ1, dQ2 of the single-pass kernel
+                        // (bwd_fused64.cuh); zeroed by the preprocess kernel, converted by the finishing kernel
+  long long dq_acc_f4;  // its size in float4 units
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -66,6 +70,12 @@ __global__ void __launch_bounds__(256) diffattn_bwd_pre_kernel(const BwdArgs arg
 #pragma unroll
   for (int i = 0; i < VPL; ++i) { gn[i] = has_gain ? args.gain[lane * VPL + i] : 1.f; dg_acc[i] = 0.f; }
   __shared__ float dg_red[8][DV];
+  // the dQ partial sums of the single-pass backward start from zero
+  if (args.dq_acc) {
+    float4* z = reinterpret_cast<float4*>(args.dq_acc);
+    for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < args.dq_acc_f4; t += (long long)gridDim.x * blockDim.x)
+      z[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
 
   // PRE_ROWS rows per warp and trip: all their loads are issued before the first reduction, which keeps four times
   // the bytes in flight per warp (one row per trip ran at 26 % of the DRAM rate: the shuffles of a row's two
@@ -196,8 +206,8 @@ __global__ void diffattn_bwd_padstats_kernel(const BwdArgs args, int bh_total) {
 // ------------------------------------------------------------------------------------------------
 // Per-column statistics are read from shared memory DA_PF columns ahead of their use, by volatile loads that keep
 // that order: every thread of a warp reads the same 16 bytes per column, and left to the compiler the loads sat
-// right before their consumers with the shared-memory pipe's loaded latency exposed 16 times per tile (dK/dV at
-// config 2: 1.33 ms; two columns ahead 1.22, four 1.23, six 1.26).
+// right before their consumers with the shared-memory pipe's loaded latency exposed 16 times per tile (at
+// B4 H16 N4096 D64 the dK/dV kernel took 1.33 ms that way; 1.22 ms with two columns ahead, 1.23 with four).
 #ifndef DA_PF
 #define DA_PF 2
 #endif
@@ -395,14 +405,8 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
     for (int i = 0; i < nq; ++i) {
       const int st = i % ST;
       const float4* stats = reinterpret_cast<const float4*>(smem + OFF_STAGE + st * STAGE_BYTES + 2 * Q_BYTES + DA_BYTES) + g * 16;
-#ifdef DA_TIMING
-      const bool tm_on = (blockIdx.x == 3 && blockIdx.y == 1 && lane == 0 && (warp & 3) == 0 && g < 2) && i >= 16 && i < 32;
-      const int tm_base = 1024 + g * 256 + (i - 16) * 8;
-#endif
-      DA_TS(0);
       if (!mbar_wait(&misc->s_full, i & 1, abort_flag, 601 + g, i)) { ok = false; break; }
       tc_fence_after();
-      DA_TS(1);
       uint32_t s1[16], s2[16], dp[16];
       tmem_ld16(tb + T_S1 + g * 16, s1);
       tmem_ld16(tb + T_S2 + g * 16, s2);
@@ -410,7 +414,6 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
       tc_wait_ld();
       tc_fence_before();
       mbar_arrive(&misc->s_free);
-      DA_TS(2);
       if (args.causal) {
         // this thread's key row sees query columns >= its own index only: the first c0 columns of its 16 are hidden
         const int c0 = kv_tile * BKV + row - ((i0 + i) * BQ + g * 16);
@@ -458,13 +461,11 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
         d1[jj] = pack2<BF>(d1v[0], d1v[1]);
         d2[jj] = pack2<BF>(d2v[0], d2v[1]);
       }
-      DA_TS(3);
       // operand buffers of tile i-1 (dS^T columns, and Pc buffer of tile i-2) must have been consumed
       if (i > 0) {
         if (!mbar_wait(&misc->mma_done, (i - 1) & 1, abort_flag, 605 + g, i)) { ok = false; break; }
         tc_fence_after();
       }
-      DA_TS(4);
       // 8 packed columns per warpgroup: the 32x32b.x8 shape
       asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
                    ::"r"(tb + T_DS1 + g * 8), "r"(d1[0]), "r"(d1[1]), "r"(d1[2]), "r"(d1[3]), "r"(d1[4]), "r"(d1[5]), "r"(d1[6]), "r"(d1[7]) : "memory");
@@ -483,7 +484,6 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&misc->e_done);
-      DA_TS(5);
     }
     ok = ok && mbar_wait(&misc->acc_full, 0, abort_flag, 611 + g);
     tc_fence_after();
@@ -670,24 +670,14 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
           int st_n = st + 1;
           uint32_t par_n = st_par;
           if (st_n == ST) { st_n = 0; par_n ^= 1; }
-#ifdef DA_TIMING
-          const bool tm_on = (blockIdx.x == 3 && blockIdx.y == 1) && j >= 8 && j < 16;
-          const int tm_base = 2048 + 512 + (j - 8) * 16;
-#endif
-          DA_TS(0);
           // ---- sub-tile 2j (buffer 0): scores of 2j+1 first
           issue_scores(sp_lo, 1);
-          DA_TS(1);
           if (!mbar_wait(&misc->ds_full[0][0], ph, abort_flag, 804, j)) break;
           tc_fence_after();
-          DA_TS(2);
           issue_dq(0, sp_lo, 0, j > 0);
-          DA_TS(3);
           if (!mbar_wait(&misc->ds_full[1][0], ph, abort_flag, 805, j)) break;
           tc_fence_after();
-          DA_TS(4);
           issue_dq(1, sp_lo, 0, j > 0);
-          DA_TS(5);
           // ---- sub-tile 2j+1 (buffer 1): scores of 2j+2 (next tile) first
           if (j + 1 < nkv) {
             if (!mbar_wait(&misc->full[st_n], par_n, abort_flag, 803, j)) break;
@@ -730,19 +720,12 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
       // own 32 columns; the fp16 result goes to the first 16 of them (the other warpgroup's columns are untouched)
       const uint32_t t_s = tb + (br ? T_S2 : T_S1) + u * SUB + half * 32;
       const uint32_t t_dp = tb + T_DP + u * SUB + half * 32;
-#ifdef DA_TIMING
-      const bool tm_on = (blockIdx.x == 3 && blockIdx.y == 1 && lane == 0) && t >= 18 && t < 20;
-      const int tm_base = 2048 + warp * 16 + (t - 18) * 8;
-#endif
-      DA_TS(0);
       if (!mbar_wait(&misc->s_full[br][u], (t >> 1) & 1, abort_flag, 901 + br, t)) { ok = false; break; }
       tc_fence_after();
-      DA_TS(1);
       uint32_t s[32], dp[32];
       tmem_ld32(t_s, s);
       tmem_ld32(t_dp, dp);
       tc_wait_ld();
-      DA_TS(2);
       {
         // key columns past the sequence end or (causal) right of the diagonal: score -inf, probability 0
         const int c_first = t * SUB + half * 32;
@@ -768,12 +751,10 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
           s[i] = pack2<BF>(p0 * fmaf(sg, __uint_as_float(dp[2 * i]), -e), p1 * fmaf(sg, __uint_as_float(dp[2 * i + 1]), -e));
         }
       }
-      DA_TS(3);
       tmem_st16(t_s, s);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&misc->ds_full[br][u]);
-      DA_TS(4);
     }
     ok = ok && mbar_wait(&misc->acc_full, 0, abort_flag, 911 + br);
     tc_fence_after();

@@ -43,14 +43,6 @@ __device__ __forceinline__ float load_lambda(const void* p, int dtype) {
   return *reinterpret_cast<const float*>(p);
 }
 
-#ifdef DA_TIMING
-__device__ long long g_timing[16384];
-__device__ __forceinline__ long long gtimer() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-__device__ __forceinline__ int smid() { int r; asm volatile("mov.u32 %0, %smid;" : "=r"(r)); return r; }
-#define DA_TS(slot) do { if (tm_on) g_timing[tm_base + (slot)] = clock64(); } while (0)
-#else
-#define DA_TS(slot) do { } while (0)
-#endif
 
 namespace fwd64 {
 constexpr int BM = 128;            // query rows per CTA

@@ -6,8 +6,7 @@
 // 128-column half of V: the scores and probabilities are recomputed in the second pass (same values), the row
 // statistics are identical in both, and the RMSNorm sum of squares is accumulated over the two passes.  With rms_norm
 // the first half of A is parked as 16-bit pairs in registers until the second pass has produced rstd.  Streamed tiles
-// are 64 rows: {K1, K2, V half}.  (A sixteen-softmax-warp form with per-branch P V issuers and turns measured 1.31 ms
-// against this form's 1.16 ms at B=4 H=8 N=4096; this form without turns ran config 4's forward in 9.06 ms.)
+// are 64 rows: {K1, K2, V half}.
 #pragma once
 #include "fwd.cuh"
 #include "sm100.cuh"
@@ -24,7 +23,14 @@ constexpr int OFF_Q1 = 0, OFF_Q2 = Q_BYTES, OFF_STAGE = 2 * Q_BYTES;   // 64 KB
 constexpr int OFF_MISC = OFF_STAGE + ST * STAGE_BYTES;                 // 208 KB
 constexpr int MISC_BYTES = 4096;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
-constexpr int NUM_THREADS = 320;
+// warps 0-7 softmax, 8 TMA, 9 MMA issuer, 10 and 11 idle: they complete the third warpgroup so that it can hand its
+// registers to the softmax warpgroups (setmaxnreg works on whole warpgroups): per scheduler up to 2 x 224 + 56 = 3 x 168
+// (184, 200 and 224 measured within 2 % of one another at B2 H8 N8192 D128; 168, i.e. no transfer, 2 % slower)
+constexpr int NUM_THREADS = 384;
+#ifndef DA_FWD128_SOFTMAX_REGS
+#define DA_FWD128_SOFTMAX_REGS 184
+#endif
+constexpr int REGS_SOFTMAX = DA_FWD128_SOFTMAX_REGS, REGS_ROLE = 56;
 constexpr int T_O = 256;
 constexpr int HANDOVER_AT = 22;   // element pair (of 32) of an exp pass after which the other branch may start (see fwd64.cuh)
 
@@ -80,6 +86,7 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&misc->tmem_slot);
 
   if (warp == 8) {
+    reg_dec<REGS_ROLE>();
     if (elect_one()) {
       mbar_expect_tx(&misc->bar_q, 2 * Q_BYTES);
       for (int c = 0; c < 2; ++c) {
@@ -102,6 +109,7 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
       }
     }
   } else if (warp == 9) {
+    reg_dec<REGS_ROLE>();
     if (elect_one()) {
       constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0, BF);
       constexpr uint32_t IDESC_O = make_idesc(BM, 128, 0, 1, BF);
@@ -160,7 +168,10 @@ diffattn_fwd128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_c
         }
       }
     }
+  } else if (warp >= 10) {
+    reg_dec<REGS_ROLE>();               // idle warps: only here to complete the warpgroup
   } else {
+    reg_inc<REGS_SOFTMAX>();
     const int br = warp >> 2;
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;

@@ -5,9 +5,7 @@
 // t, then branch 1, then branch 0 over t+1 ...; the token is released after 22 of a pass's 32 element pairs because
 // the parked waiter needs ~200 clocks to resume.  Left to themselves both branches reach every phase (wait,
 // tcgen05.ld, exp pass, tcgen05.st, arrive) together, since their scores complete together, and the exp unit idles
-// during the hand-offs.  History at config 2: without turns 1.04-1.06 ms; sixteen softmax warps (each row split
-// between two threads, exchanging the row maximum through shared memory) without turns 1.06, with turns 0.985-1.00;
-// this form 0.94-0.96.
+// during the hand-offs.
 #pragma once
 #include "fwd.cuh"
 
@@ -16,12 +14,19 @@ namespace fwd64 {
 constexpr int MISC_BYTES = 4096;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024; // +1024 for manual alignment
 // warps 0-7 softmax (branch = warp >> 2, thread = query row); 8 TMA producer; 9 S issuer (both branches); 10, 11 P V
-// issuers of branch 1, 2: one role warp per scheduler (warp % 4).  Twelve warps keep three per scheduler, which leaves
-// 168 registers per thread (a thirteenth warp would cap them at 128).
+// issuers of branch 1, 2: one role warp per scheduler (warp % 4).  Twelve warps, three per scheduler, are launched
+// with 168 registers per thread; the role warpgroup then hands registers to the softmax warpgroups (setmaxnreg),
+// which hold a whole 64-column sub-tile of scores plus its packed probabilities per thread.  Per scheduler up to
+// 2 x 224 + 56 = 3 x 168 are available; measured at B4 H16 N4096 D64, 224 (no spill) and 200 run 5 % slower than 184
+// and 168 (about 100 bytes spilled, on the rarely taken rescale path).
 constexpr int NUM_THREADS = 384;
+#ifndef DA_FWD64_SOFTMAX_REGS
+#define DA_FWD64_SOFTMAX_REGS 184
+#endif
+constexpr int REGS_SOFTMAX = DA_FWD64_SOFTMAX_REGS, REGS_ROLE = 56;
 constexpr int WARP_TMA = 8, WARP_S = 9, WARP_PV = 10;
-// element pair (of 32) of an exp pass after which the other branch may start its own pass; measured at config 2:
-// 16 -> 0.98 ms, 18 -> 0.97, 20 -> 0.98, 22 -> 0.95-0.96, 24 -> 0.97, 26 -> 1.00, 28 -> 1.05
+// element pair (of 32) of an exp pass after which the other branch may start its own pass (measured best of 16..28
+// at B4 H16 N4096 D64)
 constexpr int HANDOVER_AT = 22;
 struct Misc {
   uint64_t bar_q;
@@ -59,11 +64,6 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
   const int lane = threadIdx.x & 31;
   const int q_tile = blockIdx.x;
   const int bh = blockIdx.y;
-#ifdef DA_TIMING
-  const int cta_lin = blockIdx.y * gridDim.x + blockIdx.x;
-  const bool life_on = threadIdx.x == 0 && cta_lin < 2048;
-  if (life_on) { g_timing[4096 + 6 * cta_lin] = smid(); g_timing[4096 + 6 * cta_lin + 1] = gtimer(); }
-#endif
   const int b_idx = bh / args.h;
   const int h_idx = bh % args.h;
   // the last tile may reach past N (TMA fills those rows with zeros); with a causal mask the tiles right of
@@ -110,6 +110,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
 
   if (warp == WARP_TMA) {
     // ------------------------------- TMA producer -------------------------------
+    reg_dec<REGS_ROLE>();
     if (elect_one()) {
       for (int j = PRELOAD; j < nkv; ++j) {
         const int ks = j % KS, vs = j % VS;
@@ -129,6 +130,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     // issues tcgen05.mma about three times slower: 152 against 48 clocks per instruction, measured.)
     // Sub-tile t goes to buffer t & 1, which is free once P_b V of sub-tile t-2 has completed, so the
     // scores of the next sub-tile are ready while the softmax warpgroups work on the current one.
+    reg_dec<REGS_ROLE>();
     if (elect_one()) {
       constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0, BF);   // both operands K-major
       constexpr uint32_t HALF = (SUB * 128) >> 4;               // 64 rows of 128 bytes, in descriptor units
@@ -162,6 +164,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     }
   } else if (warp == WARP_PV || warp == WARP_PV + 1) {
     // ------------------- P V issuer of one branch: O_b += P_b(t) V(sub-tile t) -------------------
+    reg_dec<REGS_ROLE>();
     if (elect_one()) {
       const int br = warp - WARP_PV;
       constexpr uint32_t IDESC_O = make_idesc(BM, DV, 0, 1, BF);    // V is MN-major
@@ -190,6 +193,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     }
   } else {
     // ------------------------- softmax warpgroups + epilogue -------------------------
+    reg_inc<REGS_SOFTMAX>();
     const int br = warp >> 2;                       // branch handled by this warpgroup
     const int row = (warp & 3) * 32 + lane;         // query row inside the tile = TMEM lane
     const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
@@ -202,28 +206,15 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     const uint32_t dkey = DROP ? drop_key(args.seed_lo, args.seed_hi, uint32_t(bh), uint32_t(br)) : 0u;
     const uint32_t drow2 = uint32_t(q_tile * BM + row) >> 1;
     const int drow_odd = row & 1;
-#ifdef DA_TIMING
-    const bool tm_warp = (blockIdx.x == 3 && blockIdx.y == 1 && lane == 0 && (warp & 3) == 0);
-#endif
 
     for (int t = 0; t < nsub; ++t) {
       const uint32_t t_s = t_s0 + (t & 1) * SUB;
-#ifdef DA_TIMING
-      const bool tm_on = tm_warp && t >= 16 && t < 32;
-      const int tm_base = br * 256 + (t - 16) * 8;
-#endif
-      DA_TS(0);
       if (!mbar_wait(&misc->s_full[br][t & 1], (t >> 1) & 1, abort_flag, 301 + br, t)) { ok = false; break; }
       tc_fence_after();
-      DA_TS(1);
-#ifdef DA_TIMING
-      if (life_on && t == 0) g_timing[4096 + 6 * cta_lin + 2] = gtimer();
-#endif
       uint32_t sr[SUB];
       tmem_ld32(t_s + 0, sr);
       tmem_ld32(t_s + 32, sr + 32);
       tc_wait_ld();
-      DA_TS(2);
       {
         // key columns past the sequence end, or right of the diagonal under the causal mask, get a score of
         // -inf (probability 0); nv = number of visible columns of this row in this sub-tile
@@ -264,7 +255,6 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
           mx[i & 3] = max3(mx[i & 3], __uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]));
         __syncwarp(); if (lane == 0) mbar_arrive(&misc->turn[br ^ 1]);
       }
-      DA_TS(3);
       const float m_new = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       const bool need = (t == 0) || ((m_new - m_run) * sl2 > 8.f);
       if (__any_sync(0xffffffffu, need)) {
@@ -303,24 +293,15 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
         for (int i = 0; i < SUB / 2; ++i)
           pk[i] &= drop_pair_mask(drop_hash(dkey, drow2, uint32_t(t * (SUB / 2) + i)), drow_odd, args.drop_thresh);
       }
-      DA_TS(4);
       tmem_st32(t_s, pk);
       tc_wait_st();
-      DA_TS(5);
       tc_fence_before();
       mbar_arrive(&misc->p_full[br][t & 1]);
-      DA_TS(6);
     }
 
-#ifdef DA_TIMING
-    if (life_on) g_timing[4096 + 6 * cta_lin + 3] = gtimer();
-#endif
     // ---- epilogue: every thread runs every barrier; only the global writes depend on `ok`
     ok = ok && mbar_wait(&misc->o_full, 0, abort_flag, 311 + br);
     tc_fence_after();
-#ifdef DA_TIMING
-    if (life_on) g_timing[4096 + 6 * cta_lin + 4] = gtimer();
-#endif
     const float inv_l = (DROP ? args.drop_scale : 1.f) / l_run;      // kept probabilities are scaled by 1 / (1 - p)
     if (br == 0) misc->coef1[row] = inv_l; else misc->coef2[row] = inv_l;
     named_bar_sync(1, 256);
@@ -407,9 +388,6 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
-#ifdef DA_TIMING
-  if (life_on) g_timing[4096 + 6 * cta_lin + 5] = gtimer();
-#endif
 }
 
 }  // namespace da

@@ -36,6 +36,15 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// Register re-allocation between the roles of a warp-specialised CTA.  Every warp of a warpgroup (four consecutive
+// warps) must execute the same instruction.  Registers only move inside the pool the CTA was launched with, which
+// is kept per scheduler: for every scheduler, the sum over its warps of the new per-thread counts must not exceed
+// (warps on that scheduler) x (registers per thread at launch); an increase that cannot be satisfied blocks for ever.
+template <int N>
+__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
 // ------------------------------------------ mbarrier -----------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");

@@ -53,9 +53,21 @@ def _check_inputs(q1, q2, k1, k2, v, lambda_scale):
         raise RuntimeError("v is on another device")
 
 
+def _tma_ready(t):
+    """A tensor the TMA descriptors can address as it lies: unit stride in the last dimension, every other
+    stride a positive multiple of 8 elements (16 bytes), base pointer 16-byte aligned.  Anything else the
+    reference's pointer arithmetic would accept (expanded tensors with stride 0, odd slices of a packed
+    buffer) is copied into a dense tensor first."""
+    if t.data_ptr() % 16 != 0:
+        return t.clone(memory_format=torch.contiguous_format)      # a fresh allocation is aligned
+    if t.stride(-1) != 1 or any(stride <= 0 or stride % 8 != 0 for stride in t.stride()[:-1]):
+        return t.contiguous()
+    return t
+
+
 def _same_layout(ts):
     """q1,q2,k1,k2 must share strides (the reference reads them from Q1 only, src/kernel.py:487-490)."""
-    ts = [t if t.stride(-1) == 1 else t.contiguous() for t in ts]
+    ts = [_tma_ready(t) for t in ts]
     if any(t.stride() != ts[0].stride() for t in ts):
         ts = [t.contiguous() for t in ts]
     return ts
@@ -73,7 +85,7 @@ def dropout_threshold(dropout_p: float) -> int:
 
 
 def _fill_common(p, q1, q2, k1, k2, v, lam, lambda_init, rms_norm, saved, causal=False, drop_threshold=0, drop_seed=0,
-                 gain=None, y_gained=None):
+                 gain=None, y_gained=None, single_pass=False):
     b, h, n, d = q1.shape
     p.device = q1.device.index if q1.device.index is not None else torch.cuda.current_device()
     p.stream = torch.cuda.current_stream(q1.device).cuda_stream
@@ -88,6 +100,7 @@ def _fill_common(p, q1, q2, k1, k2, v, lam, lambda_init, rms_norm, saved, causal
     p.causal = 1 if causal else 0
     p.dropout_threshold = int(drop_threshold)
     p.dropout_seed = int(drop_seed) & 0xFFFFFFFFFFFFFFFF
+    p.single_pass = 1 if single_pass else 0
     if gain is not None:
         p.gain, p.y_gained = gain.data_ptr(), y_gained.data_ptr()
     p.sm_scale = 1.0 / math.sqrt(d)          # reference src/layers.py:20-22 (D, not 2D)
@@ -103,14 +116,13 @@ class DiffAttnFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, causal=False, drop_threshold=0, drop_seed=0,
-                gain=None):
+                gain=None, single_pass=False):
         _check_inputs(q1, q2, k1, k2, v, lambda_scale)
         if gain is not None:
             if not torch.is_tensor(gain) or gain.device != q1.device or tuple(gain.shape) != (v.shape[-1],):
                 raise ValueError("gain must be a tensor of shape [2*D] on the inputs' device")
         q1, q2, k1, k2 = _same_layout([q1, q2, k1, k2])
-        if v.stride(-1) != 1:
-            v = v.contiguous()
+        v = _tma_ready(v)
         b, h, n, d = q1.shape
         dev = q1.device
         with torch.cuda.device(dev):
@@ -132,6 +144,7 @@ class DiffAttnFunction(torch.autograd.Function):
         ctx.rms_norm = bool(rms_norm)
         ctx.causal = bool(causal)
         ctx.drop = (int(drop_threshold), int(drop_seed))
+        ctx.single_pass = bool(single_pass)
         return y_gained if gain is not None else y
 
     @staticmethod
@@ -148,7 +161,7 @@ class DiffAttnFunction(torch.autograd.Function):
             p = _lib.new_params()
             dgain = torch.zeros(2 * d, dtype=torch.float32, device=dev) if ctx.gain32 is not None else None
             _fill_common(p, q1, q2, k1, k2, v, lam, ctx.lambda_init, ctx.rms_norm, (y, a2, lse1, lse2, rstd), ctx.causal,
-                         *ctx.drop, ctx.gain32, y)     # y_gained is not read by the backward
+                         *ctx.drop, ctx.gain32, y, ctx.single_pass)     # y_gained is not read by the backward
             if dgain is not None:
                 p.dgain = dgain.data_ptr()
             nbytes = int(_lib.lib.diffattn_workspace_bytes(p))
@@ -162,13 +175,14 @@ class DiffAttnFunction(torch.autograd.Function):
         DiffAttnFunction.last_dlambda_fp32 = dlam
         dlam_out = dlam.to(lam.dtype).reshape(lam.shape) if ctx.needs_input_grad[5] else None
         dgain_out = dgain.to(ctx.gain_dtype) if (dgain is not None and ctx.needs_input_grad[11]) else None
-        return dq1, dq2, dk1, dk2, dv, dlam_out, None, None, None, None, None, dgain_out
+        return dq1, dq2, dk1, dk2, dv, dlam_out, None, None, None, None, None, dgain_out, None
 
     last_dlambda_fp32 = None
 
 
 def MultiheadDiffAttnKernel(q1, q2, k1, k2, v, lambda_scale=-0.5, lambda_init: float = 0.8, rms_norm: bool = False,
-                            causal: bool = False, dropout_p: float = 0.0, dropout_seed=None, gain=None):
+                            causal: bool = False, dropout_p: float = 0.0, dropout_seed=None, gain=None,
+                            single_pass: bool = False):
     """Fused differential attention, same signature as the reference (src/layers.py:10-26).
 
     q1,q2,k1,k2: fp16 CUDA [B,H,N,D]; v: fp16 CUDA [B,H,N,2D]; lambda_scale: 1-element fp16/fp32
@@ -187,12 +201,21 @@ def MultiheadDiffAttnKernel(q1, q2, k1, k2, v, lambda_scale=-0.5, lambda_init: f
     inside the forward epilogue and its gradient comes out of the backward's preprocess kernel -- the weight of
     the output norm in the layer the reference adapts (src/layers.py:114), which the reference's own norm
     (elementwise_affine=False, src/layers.py:75) does not have.
+    `single_pass=True` (keyword; head dims 32 and 64) selects the backward that visits every score tile once and
+    sums each key block's share of dq1/dq2 with fp32 atomic adds, so those two gradients can differ in the last
+    bit from run to run.  The default backward is two tensor-core kernels whose second recomputes the scores per
+    query block, as the reference's second loop does (src/kernel.py:426-436); it is bit-reproducible and, on
+    B200, the faster of the two.
+
+    A device-side wait that gives up (a kernel bug or a broken GPU, never a property of the inputs) leaves the
+    outputs undefined without raising here; `device_status()` synchronises and raises in that case.
     """
     thresh = dropout_threshold(dropout_p)
     seed = 0
     if thresh:
         seed = int(torch.randint(0, 2 ** 62, (1,)).item()) if dropout_seed is None else int(dropout_seed)
-    return DiffAttnFunction.apply(q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, causal, thresh, seed, gain)
+    return DiffAttnFunction.apply(q1, q2, k1, k2, v, lambda_scale, lambda_init, rms_norm, causal, thresh, seed, gain,
+                                  single_pass)
 
 
 def lambda_from_reparam(lambda_q1, lambda_k1, lambda_q2, lambda_k2, lambda_init: float):
