@@ -13,8 +13,7 @@ REQUIRED = ("impl", "metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_
 
 def _run(extra_env):
     env = dict(os.environ, **extra_env)
-    # a tiny workload keeps this test to a few seconds: patch the workload table through an env hook is not
-    # needed -- one step of the 2-head N=4096 sample takes a couple of seconds on 8 cores
+    # one step of the one-head N=4096 sample takes a couple of seconds on 8 cores
     res = subprocess.run([sys.executable, os.path.join(REPO, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0"],
                          capture_output=True, text=True, env=env, timeout=600)
     assert res.returncode == 0, res.stderr[-2000:]
@@ -29,7 +28,12 @@ def test_reference_arm_prints_one_json_line():
     for k in REQUIRED:
         assert k in j, k
     assert j["impl"] == "reference" and j["unit"] == "TFLOP/s" and j["vs_baseline"] is None
-    assert j["cpu_baseline"]["kind"] == "port" and j["cpu_baseline"]["cores"] >= 1
+    # the reference's own module when baseline/_ref holds it (installed where the reference checkout is present), else the port
+    from baseline import ref_loader
+    have_ref = ref_loader.installed() or os.path.isdir(os.path.join(ref_loader.default_checkout(), "src"))
+    assert j["cpu_baseline"]["kind"] == ("reference" if have_ref else "port") and j["cpu_baseline"]["cores"] >= 1
+    c1 = j["cpu_baseline"]["c1"]
+    assert c1["shape"].startswith("B=2 H=16 N=512 D=32") and c1["timed"] >= 7 and c1["fwd_bwd_ms"] > c1["fwd_ms"] > 0
     assert j["e2e"]["h2d_bytes_per_step"] == 0 and j["e2e"]["d2h_bytes_per_step"] == 0
     assert "workload" in j["config"] and "model" not in j["config"]
 
