@@ -45,6 +45,7 @@ WORKLOADS = {
     "b8h8n8192d128": (8, 8, 8192, 128, 1.0, 0.7, 0.2, False),       # wide head, RMSNorm off
     "b8h32n4096d64": (8, 32, 4096, 64, 1.0, 0.5, 0.8, True),        # one eighth of B=64 H=32
     "b4h16n4096d32": (4, 16, 4096, 32, 0.5, 0.5, 0.8, True),        # the reference's benchmark point H=16 D=32 N=4096 (src/benchmark.py:19-25)
+    "b1h4n4096d128": (1, 4, 4096, 128, 1.0, 0.7, 0.2, False),       # small wide-head case for profiler captures
 }
 DEFAULT_WORKLOAD = "b4h16n4096d64"
 SPLIT = (64, 32, 4096, 64, 1.0, 0.5, 0.8, True)                     # batch-sharded workload, split over the ranks
@@ -746,7 +747,8 @@ def main():
             gsel = torch.Generator().manual_seed(199 + rank)
             bi, hi2 = int(torch.randint(0, hi_ - lo, (1,), generator=gsel)), int(torch.randint(0, sh, (1,), generator=gsel))
             rel, mabs = ps.check_one_head(bi, hi2)
-            ok = rel <= 1e-3 and mabs <= 2e-2
+            loosen = 8.0 if args.io_dtype == "bf16" else 1.0
+            ok = rel <= loosen * 1e-3 and mabs <= loosen * 2e-2
             split["check"] = {"ranks_ok": int(all_sum(1.0 if ok else 0.0)), "ranks": world, "worst_rel_l2": all_max(rel),
                               "worst_max_abs_scaled": all_max(mabs)}
         del ps

@@ -10,8 +10,9 @@
  * device except diffattn_status().  Every entry point leaves the calling thread's current CUDA device as it
  * found it.  Every function returns 0 on success or a negative DIFFATTN_ERR_* code; nothing is launched
  * after a failed check.  diffattn_last_error() gives the message of the calling thread's last failure.
- * Host-side state: a mutex-protected cache of encoded TMA descriptors (keyed by base pointer, shape, strides,
- * box and type), of per-kernel launch attributes and of the device each base pointer was found on.
+ * Host-side state: per calling thread, a cache of encoded TMA descriptors (keyed by base pointer, shape, strides,
+ * box and type), of per-kernel launch attributes and of the device each base pointer was found on; nothing is
+ * shared between threads except the address of the static scratch array (mutex).
  */
 #ifndef DIFFATTN_H_
 #define DIFFATTN_H_

@@ -217,7 +217,8 @@ __device__ __forceinline__ float4 lds_v4(const float4* p) {
   return v;
 }
 namespace dkdv64 {
-constexpr int BKV = 128, BQ = 64, HD = 64, DV = 128, ST = 3;
+// (ring depth 4 with a single Pc buffer, and depth 3 with a single buffer, measured within noise of this setting)
+constexpr int BKV = 128, BQ = 64, HD = 64, DV = 128, ST = 3, PCBUF = 2;
 constexpr int K_BYTES = BKV * HD * 2;       // 16 KB
 constexpr int V_BYTES = BKV * DV * 2;       // 32 KB, two boxes of 16 KB
 constexpr int Q_BYTES = BQ * HD * 2;        // 8 KB
@@ -227,7 +228,7 @@ constexpr int STAGE_BYTES = 2 * Q_BYTES + DA_BYTES + STAT_BYTES;   // 33 KB
 constexpr int PC_BYTES = BKV * BQ * 2;      // 16 KB per buffer
 constexpr int OFF_K1 = 0, OFF_K2 = K_BYTES, OFF_V = 2 * K_BYTES;
 constexpr int OFF_PC = OFF_V + V_BYTES;                            // 64 KB
-constexpr int OFF_STAGE = OFF_PC + 2 * PC_BYTES;                   // 96 KB
+constexpr int OFF_STAGE = OFF_PC + PCBUF * PC_BYTES;                   // 96 KB
 constexpr int OFF_MISC = OFF_STAGE + ST * STAGE_BYTES;             // 195 KB
 constexpr int MISC_BYTES = 1024;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
@@ -239,8 +240,8 @@ struct Misc {
   uint64_t bar_kv;
   uint64_t full[ST], empty[ST];
   uint64_t s_full;      // scores of a tile written (MMA -> warpgroups)
-  uint64_t s_free;      // scores of a tile are in registers (256 arrivals)
-  uint64_t e_done;      // dS^T in TMEM and Pc in shared memory written (256 arrivals)
+  uint64_t s_free;      // scores of a tile are in registers (one arrival per elementwise thread)
+  uint64_t e_done;      // dS^T in TMEM and Pc in shared memory written (one arrival per elementwise thread)
   uint64_t mma_done;    // dV/dK MMAs of a tile completed (operand buffers reusable)
   uint64_t acc_full;
   uint32_t tmem_slot;
@@ -320,18 +321,21 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
       const uint32_t v_lo = sdesc_lo(smem_u32(smem + OFF_V));
       const uint32_t st_lo0 = sdesc_lo(smem_u32(smem + OFF_STAGE));
       const uint32_t tb = tmem_base;
+      const int kd = args.d >> 4;       // 16-deep MMA steps over the head dim (value width: twice as many): head dim 32 skips the zero padding
       auto issue_scores = [&](uint32_t sp_lo) {
         if (!is_dp) {
 #pragma unroll
-          for (int k = 0; k < HD / 16; ++k) mma_ss_lo(tb + T_S1, k1_lo + k * 2, sp_lo + k * 2, IDESC_S, k > 0);
+          for (int k = 0; k < HD / 16; ++k)
+            if (k < kd) mma_ss_lo(tb + T_S1, k1_lo + k * 2, sp_lo + k * 2, IDESC_S, k > 0);
 #pragma unroll
           for (int k = 0; k < HD / 16; ++k)
-            mma_ss_lo(tb + T_S2, k2_lo + k * 2, sp_lo + (Q_BYTES >> 4) + k * 2, IDESC_S, k > 0);
+            if (k < kd) mma_ss_lo(tb + T_S2, k2_lo + k * 2, sp_lo + (Q_BYTES >> 4) + k * 2, IDESC_S, k > 0);
         } else {
 #pragma unroll
           for (int k = 0; k < DV / 16; ++k)
-            mma_ss_lo(tb + T_DP, v_lo + (k / 4) * ((V_BYTES / 2) >> 4) + (k % 4) * 2,
-                      sp_lo + ((2 * Q_BYTES) >> 4) + (k / 4) * ((DA_BYTES / 2) >> 4) + (k % 4) * 2, IDESC_S, k > 0);
+            if (k < 2 * kd)
+              mma_ss_lo(tb + T_DP, v_lo + (k / 4) * ((V_BYTES / 2) >> 4) + (k % 4) * 2,
+                        sp_lo + ((2 * Q_BYTES) >> 4) + (k / 4) * ((DA_BYTES / 2) >> 4) + (k % 4) * 2, IDESC_S, k > 0);
         }
         mma_commit(&misc->s_full);        // two arrivals per tile: this warp's and the other score issuer's
       };
@@ -358,8 +362,9 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
   } else if (warp == WARP_MMA + 2) {
     // ---- output issuer: dV += Pc^T dA, dK_b += dS_b^T Q_b of tile i once the warpgroups have written their operands
     if (elect_one()) {
-      constexpr uint32_t IDESC_DV = make_idesc(BKV, DV, 0, 1, BF);    // dV += Pc^T dA   (Pc K-major smem, dA MN-major)
-      constexpr uint32_t IDESC_DK = make_idesc(BKV, HD, 0, 1, BF);    // dK += dS^T Q    (dS^T in TMEM, Q MN-major)
+      // head dim 32: only the real 64 value columns / 32 head columns are produced
+      const uint32_t IDESC_DV = make_idesc(BKV, 2 * args.d, 0, 1, BF);    // dV += Pc^T dA   (Pc K-major smem, dA MN-major)
+      const uint32_t IDESC_DK = make_idesc(BKV, args.d, 0, 1, BF);        // dK += dS^T Q    (dS^T in TMEM, Q MN-major)
       const uint32_t pc_lo0 = sdesc_lo(smem_u32(smem + OFF_PC));
       const uint32_t st_lo0 = sdesc_lo(smem_u32(smem + OFF_STAGE));
       constexpr uint32_t DA_MN_LBO = ((DA_BYTES / 2) >> 4) << 16;   // dA as MN-major B: 64-column atoms 8 KB apart
@@ -367,7 +372,7 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
       int st = 0;
       for (int i = 0; i < nq; ++i) {
         const uint32_t sp_lo = st_lo0 + st * (STAGE_BYTES >> 4);
-        const uint32_t pc_lo = pc_lo0 + (i & 1) * (PC_BYTES >> 4);
+        const uint32_t pc_lo = pc_lo0 + (i % PCBUF) * (PC_BYTES >> 4);
         // e_done(i) implies that stage i was loaded and that the score MMAs reading it have completed
         if (!mbar_wait(&misc->e_done, i & 1, abort_flag, 505, i)) break;
         tc_fence_after();
@@ -473,7 +478,7 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
                    ::"r"(tb + T_DS2 + g * 8), "r"(d2[0]), "r"(d2[1]), "r"(d2[2]), "r"(d2[3]), "r"(d2[4]), "r"(d2[5]), "r"(d2[6]), "r"(d2[7]) : "memory");
       // Pc tile [128 key rows][64 query columns] fp16, 128-byte rows, 16-byte chunks XOR-swizzled by row
       {
-        uint8_t* prow = smem + OFF_PC + (i & 1) * PC_BYTES + row * 128;
+        uint8_t* prow = smem + OFF_PC + (i % PCBUF) * PC_BYTES + row * 128;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           const int chunk = (g * 2 + c) ^ (row & 7);
@@ -630,7 +635,8 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
     // slower: the single issuer stays.)
     if (elect_one()) {
       constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0, BF);    // S = Q K^T, dP = dA V^T
-      constexpr uint32_t IDESC_DQ = make_idesc(BM, HD, 0, 1, BF);    // dQ += dS K   (K MN-major)
+      const uint32_t IDESC_DQ = make_idesc(BM, args.d, 0, 1, BF);    // dQ += dS K   (K MN-major); head dim 32: 32 columns
+      const int kd = args.d >> 4;       // 16-deep MMA steps over the head dim: head dim 32 skips the zero padding
       constexpr uint32_t HALF = (SUB * 128) >> 4;
       const uint32_t q1_lo = sdesc_lo(smem_u32(smem + OFF_Q1)), q2_lo = sdesc_lo(smem_u32(smem + OFF_Q2));
       const uint32_t da_lo = sdesc_lo(smem_u32(smem + OFF_DA));
@@ -640,15 +646,16 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
       auto issue_scores = [&](uint32_t sp_lo, int u) {
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          mma_ss_lo(tb + T_S1 + u * SUB, q1_lo + k * 2, sp_lo + u * HALF + k * 2, IDESC_S, k > 0);
+          if (k < kd) mma_ss_lo(tb + T_S1 + u * SUB, q1_lo + k * 2, sp_lo + u * HALF + k * 2, IDESC_S, k > 0);
 #pragma unroll
         for (int k = 0; k < DV / 16; ++k)
-          mma_ss_lo(tb + T_DP + u * SUB, da_lo + (k / 4) * ((DA_BYTES / 2) >> 4) + (k % 4) * 2,
-                    sp_lo + ((2 * K_BYTES) >> 4) + (k / 4) * ((V_BYTES / 2) >> 4) + u * HALF + (k % 4) * 2, IDESC_S, k > 0);
+          if (k < 2 * kd)
+            mma_ss_lo(tb + T_DP + u * SUB, da_lo + (k / 4) * ((DA_BYTES / 2) >> 4) + (k % 4) * 2,
+                      sp_lo + ((2 * K_BYTES) >> 4) + (k / 4) * ((V_BYTES / 2) >> 4) + u * HALF + (k % 4) * 2, IDESC_S, k > 0);
         mma_commit(&misc->s_full[0][u]);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          mma_ss_lo(tb + T_S2 + u * SUB, q2_lo + k * 2, sp_lo + (K_BYTES >> 4) + u * HALF + k * 2, IDESC_S, k > 0);
+          if (k < kd) mma_ss_lo(tb + T_S2 + u * SUB, q2_lo + k * 2, sp_lo + (K_BYTES >> 4) + u * HALF + k * 2, IDESC_S, k > 0);
         mma_commit(&misc->s_full[1][u]);
       };
       auto issue_dq = [&](int br, uint32_t sp_lo, int u, uint32_t first) {

@@ -71,11 +71,14 @@ PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
   return fn;
 }
 
-// ---- host-side caches (one mutex): encoded tensor maps, launch attributes already set, SM counts, and the
-// device every base pointer was found on.  A tensor map is a pure function of its key, so an entry never goes
-// stale; the pointer cache keeps only pointers that passed (a pointer freed and handed out again by another
-// device's allocator would be re-checked only after the cache was flushed: caches are flushed when they grow
-// past kCacheLimit entries).
+// ---- host-side caches, one set per calling thread (no lock, no shared mutable state): encoded tensor maps, launch
+// attributes already set, SM counts, and the device every base pointer was found on.  A tensor map is a pure
+// function of its key, so an entry never goes stale; the pointer cache keeps only pointers that passed (a pointer
+// freed and handed out again by another device's allocator would be re-checked only after the cache was flushed:
+// caches are flushed when they grow past kCacheLimit entries).  Measured at B2 H4 N128 (host clock around 1000
+// enqueues): the caches save nothing -- encoding a map costs about as much as finding one -- and a call costs
+// what its three or four launches cost; they are kept for the device check, which would otherwise query the
+// driver for every pointer of every call.
 struct MapKey {
   const void* base;
   int64_t s_row, s2, s3;
@@ -97,11 +100,10 @@ struct MapKeyHash {
   }
 };
 constexpr size_t kCacheLimit = 4096;
-std::mutex g_mu;
-std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
-std::unordered_map<const void*, uint64_t> g_attr_done;     // kernel -> bit per device: dynamic shared memory size set
-std::unordered_map<const void*, int> g_ptr_device;         // base pointer -> device ordinal it was verified on
-int g_sm_count[kMaxDevices] = {0};
+thread_local std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+thread_local std::unordered_map<const void*, uint64_t> g_attr_done;     // kernel -> bit per device: dynamic shared memory size set
+thread_local std::unordered_map<const void*, int> g_ptr_device;         // base pointer -> device ordinal it was verified on
+thread_local int g_sm_count[kMaxDevices] = {0};
 
 // 16-bit (fp16, or bf16 when BF) tensor [d3, d2, rows, cols] with element strides (s3, s2, s_row, 1); box = box_rows x 64 columns,
 // 128-byte swizzle (the layout the tcgen05 shared-memory descriptors in sm100.cuh describe).
@@ -110,7 +112,6 @@ int make_map(CUtensorMap* map, const void* base, int cols, int rows, int d2, int
              int box_rows, const char* what) {
   const MapKey key{base, s_row, s2, s3, cols, rows, d2, d3, box_rows, BF ? 1 : 0};
   {
-    std::lock_guard<std::mutex> lock(g_mu);
     auto it = g_maps.find(key);
     if (it != g_maps.end()) {
       *map = it->second;
@@ -133,7 +134,6 @@ int make_map(CUtensorMap* map, const void* base, int cols, int rows, int d2, int
                    CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(DIFFATTN_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, int(r));
-  std::lock_guard<std::mutex> lock(g_mu);
   if (g_maps.size() >= kCacheLimit) g_maps.clear();
   g_maps.emplace(key, *map);
   return DIFFATTN_OK;
@@ -143,25 +143,17 @@ int make_map(CUtensorMap* map, const void* base, int cols, int rows, int d2, int
 template <typename K>
 int set_smem(K kernel, int bytes, int device) {
   const void* key = reinterpret_cast<const void*>(kernel);
-  {
-    std::lock_guard<std::mutex> lock(g_mu);
-    auto it = g_attr_done.find(key);
-    if (it != g_attr_done.end() && ((it->second >> device) & 1ull)) return DIFFATTN_OK;
-  }
+  auto it = g_attr_done.find(key);
+  if (it != g_attr_done.end() && ((it->second >> device) & 1ull)) return DIFFATTN_OK;
   DA_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-  std::lock_guard<std::mutex> lock(g_mu);
   g_attr_done[key] |= 1ull << device;
   return DIFFATTN_OK;
 }
 
 int sm_count(int device) {
-  {
-    std::lock_guard<std::mutex> lock(g_mu);
-    if (g_sm_count[device] > 0) return g_sm_count[device];
-  }
+  if (g_sm_count[device] > 0) return g_sm_count[device];
   int sms = 0;
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 148;
-  std::lock_guard<std::mutex> lock(g_mu);
   g_sm_count[device] = sms;
   return sms;
 }
@@ -171,7 +163,6 @@ int sm_count(int device) {
 int check_on_device(const void* ptr, int device, const char* what) {
   if (!ptr) return DIFFATTN_OK;
   {
-    std::lock_guard<std::mutex> lock(g_mu);
     auto it = g_ptr_device.find(ptr);
     if (it != g_ptr_device.end() && it->second == device) return DIFFATTN_OK;
   }
@@ -186,7 +177,6 @@ int check_on_device(const void* ptr, int device, const char* what) {
     return fail(DIFFATTN_ERR_WRONG_DEVICE, "%s (%p) is not device memory (host or unregistered pointer)", what, ptr);
   if (attr.device != device)
     return fail(DIFFATTN_ERR_WRONG_DEVICE, "%s (%p) lives on device %d but the call names device %d", what, ptr, attr.device, device);
-  std::lock_guard<std::mutex> lock(g_mu);
   if (g_ptr_device.size() >= kCacheLimit) g_ptr_device.clear();
   g_ptr_device[ptr] = device;
   return DIFFATTN_OK;

@@ -134,6 +134,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     if (elect_one()) {
       constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0, BF);   // both operands K-major
       constexpr uint32_t HALF = (SUB * 128) >> 4;               // 64 rows of 128 bytes, in descriptor units
+      const int kd = args.d >> 4;                               // 16-deep MMA steps over the head dim: head dim 32 skips the zero padding
       const uint32_t q1_lo = sdesc_lo(smem_u32(smem + OFF_Q1)), q2_lo = sdesc_lo(smem_u32(smem + OFF_Q2));
       const uint32_t k_lo0 = sdesc_lo(smem_u32(smem + OFF_K));
       bool ok = mbar_wait(&misc->bar_q, 0, abort_flag, 201);
@@ -152,8 +153,9 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
             tc_fence_after();
 #pragma unroll
             for (int k = 0; k < HD / 16; ++k)
-              mma_ss_lo(tmem_base + br * 128 + u * SUB, (br ? q2_lo : q1_lo) + k * 2,
-                        k_lo + br * (K_BYTES >> 4) + u * HALF + k * 2, IDESC_S, k > 0);
+              if (k < kd)
+                mma_ss_lo(tmem_base + br * 128 + u * SUB, (br ? q2_lo : q1_lo) + k * 2,
+                          k_lo + br * (K_BYTES >> 4) + u * HALF + k * 2, IDESC_S, k > 0);
             mma_commit(&misc->s_full[br][u]);
           }
           if (!ok) break;
@@ -167,7 +169,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     reg_dec<REGS_ROLE>();
     if (elect_one()) {
       const int br = warp - WARP_PV;
-      constexpr uint32_t IDESC_O = make_idesc(BM, DV, 0, 1, BF);    // V is MN-major
+      const uint32_t IDESC_O = make_idesc(BM, 2 * args.d, 0, 1, BF);    // V is MN-major; head dim 32: the 64 real value columns only
       constexpr uint32_t HALF = (SUB * 128) >> 4;
       const uint32_t v_lo0 = sdesc_lo(smem_u32(smem + OFF_V), V_BYTES / 2);
       const uint32_t t_o = tmem_base + T_O + br * 128, t_p = tmem_base + br * 128;
@@ -318,10 +320,11 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     tmem_ld32(t_o2 + 32, o2 + 32);
     tc_wait_ld();
     float ssq = 0.f;
+    const bool pad_half = br * 64 >= 2 * args.d;      // head dim 32: columns 64..127 of the accumulators were never written
 #pragma unroll
     for (int i = 0; i < 64; ++i) {
-      const float a2v = __uint_as_float(o2[i]) * c2;
-      const float av = __uint_as_float(o1[i]) * c1 - lam * a2v;
+      const float a2v = pad_half ? 0.f : __uint_as_float(o2[i]) * c2;
+      const float av = pad_half ? 0.f : __uint_as_float(o1[i]) * c1 - lam * a2v;
       ssq += av * av;
       o1[i] = __float_as_uint(av);
       o2[i] = __float_as_uint(a2v);

@@ -58,6 +58,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// (One arrival per warp -- __syncwarp, then lane 0 arrives -- instead of one per thread was measured in every
+// kernel of the default path: forward +0.7 %, dK/dV -1 %, dQ +6 % at B4 H16 N4096 D64.  The converging step delays the
+// arrival of the warp's fastest threads; per-thread arrivals stay.)
 // Suspend-time hint: the hardware may park the waiting thread for up to this long (it is woken when the
 // phase completes) instead of returning at once to be polled again.
 static constexpr uint32_t kSuspendHintNs = 1000000u;
