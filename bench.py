@@ -53,7 +53,9 @@ CPU_SMALL = (2, 16, 512, 32, 1.0, 0.5, 0.8, True)                   # the CPU-ru
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture whose
 # summary (command, commit) is profiles/b4h16n4096d64_kernels_ncu.md; reported only for the workload and flags of
 # that capture.
-NCU_TRAFFIC = {"workload": DEFAULT_WORKLOAD, "source": "profiles/b4h16n4096d64_kernels_ncu.md", "bytes": {}}
+NCU_TRAFFIC = {"workload": DEFAULT_WORKLOAD, "source": "ncu capture summarised in profiles/b4h16n4096d64_kernels_ncu.md (kernels of commit ec0d096)",
+               "bytes": {"diffattn_fwd64_kernel": 308.5e6, "diffattn_bwd_pre_kernel": 254.9e6,
+                         "diffattn_bwd_dkdv64_kernel": 381.1e6, "diffattn_bwd_dq64_kernel": 325.3e6}}
 METRIC = "diff-attn fwd+bwd TFLOP/s (credited 28*B*H*N^2*D), fp16"
 NOMINAL_TFLOPS = 2250.0
 

@@ -15,15 +15,20 @@
 namespace da {
 
 namespace side128 {
-constexpr int BM = 128, SUB = 64, HD = 128, DV = 256, ST = 2, NWG = 4;
+// Two rings for the streamed operands, because their lifetimes differ: W feeds only the T scores and is free as soon
+// as those MMAs have completed; Z feeds the S scores AND the output MMAs of its sub-tile, one elementwise pass
+// later.  With one ring of {Z, W} stages the next load could only be requested after the output MMAs, and its whole
+// latency sat between two sub-tiles (the kernel ran at half the tensor pipe's pace).
+constexpr int BM = 128, SUB = 64, HD = 128, DV = 256, ZST = 3, WST = 2, NWG = 4;
 constexpr int X_BYTES = BM * HD * 2;        // 32 KB: two boxes [128 x 64]
 constexpr int Y_BYTES = BM * DV * 2;        // 64 KB: four boxes [128 x 64]
 constexpr int Z_BYTES = SUB * HD * 2;       // 16 KB: two boxes [64 x 64]
 constexpr int W_BYTES = SUB * DV * 2;       // 32 KB: four boxes [64 x 64]
 constexpr int STAT_BYTES = SUB * 16;        // 1 KB
-constexpr int STAGE_BYTES = Z_BYTES + W_BYTES + STAT_BYTES;   // 49 KB
-constexpr int OFF_X = 0, OFF_Y = X_BYTES, OFF_STAGE = X_BYTES + Y_BYTES;   // 96 KB
-constexpr int OFF_MISC = OFF_STAGE + ST * STAGE_BYTES;                     // 194 KB
+constexpr int ZSTAGE_BYTES = Z_BYTES + STAT_BYTES;            // 17 KB: the per-column statistics travel with Z
+constexpr int OFF_X = 0, OFF_Y = X_BYTES, OFF_W = X_BYTES + Y_BYTES;       // 96 KB
+constexpr int OFF_Z = OFF_W + WST * W_BYTES;                               // 160 KB
+constexpr int OFF_MISC = OFF_Z + ZST * ZSTAGE_BYTES;                       // 211 KB
 constexpr int MISC_BYTES = 1024;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
 constexpr int NUM_THREADS = NWG * 128 + 64;
@@ -31,7 +36,7 @@ constexpr int WARP_TMA = NWG * 4, WARP_MMA = NWG * 4 + 1;
 constexpr int T_S = 0, T_T = 128, T_OUT = 256;
 struct Misc {
   uint64_t bar_xy;
-  uint64_t full[ST], empty[ST];
+  uint64_t zfull[ZST], zempty[ZST], wfull[WST], wempty[WST];
   uint64_t s_full[2], ds_full[2], acc_full;
   uint32_t tmem_slot;
   int abort_flag;
@@ -67,7 +72,8 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
 
   if (warp == WARP_TMA && lane == 0) {
     mbar_init(&misc->bar_xy, 1);
-    for (int i = 0; i < ST; ++i) { mbar_init(&misc->full[i], 1); mbar_init(&misc->empty[i], 1); }
+    for (int i = 0; i < ZST; ++i) { mbar_init(&misc->zfull[i], 1); mbar_init(&misc->zempty[i], 1); }
+    for (int i = 0; i < WST; ++i) { mbar_init(&misc->wfull[i], 1); mbar_init(&misc->wempty[i], 1); }
     for (int u = 0; u < 2; ++u) { mbar_init(&misc->s_full[u], 1); mbar_init(&misc->ds_full[u], NWG * 128); }
     mbar_init(&misc->acc_full, 1);
     misc->abort_flag = 0;
@@ -84,17 +90,21 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
       mbar_expect_tx(&misc->bar_xy, X_BYTES + Y_BYTES);
       for (int c = 0; c < 2; ++c) tma_load_4d(smem + OFF_X + c * 16384, tm_x, &misc->bar_xy, c * 64, tile * BM, h_idx, b_idx);
       for (int c = 0; c < 4; ++c) tma_load_4d(smem + OFF_Y + c * 16384, &tm_y, &misc->bar_xy, c * 64, tile * BM, y_c2, y_c3);
-      int st = 0;
-      uint32_t par = 1;
+      int zs = 0, ws = 0;
+      uint32_t zpar = 1, wpar = 1;
       for (int t = 0; t < nsub; ++t) {
-        uint8_t* sp = smem + OFF_STAGE + st * STAGE_BYTES;
-        if (!mbar_wait(&misc->empty[st], par, abort_flag, 1101, t)) break;
-        mbar_expect_tx(&misc->full[st], QSIDE ? (Z_BYTES + W_BYTES) : STAGE_BYTES);
-        for (int c = 0; c < 2; ++c) tma_load_4d(sp + c * 8192, tm_z, &misc->full[st], c * 64, (t0 + t) * SUB, h_idx, b_idx);
-        for (int c = 0; c < 4; ++c) tma_load_4d(sp + Z_BYTES + c * 8192, &tm_w, &misc->full[st], c * 64, (t0 + t) * SUB, w_c2, w_c3);
+        uint8_t* zp = smem + OFF_Z + zs * ZSTAGE_BYTES;
+        uint8_t* wp = smem + OFF_W + ws * W_BYTES;
+        if (!mbar_wait(&misc->zempty[zs], zpar, abort_flag, 1101, t)) break;
+        mbar_expect_tx(&misc->zfull[zs], QSIDE ? Z_BYTES : ZSTAGE_BYTES);
+        for (int c = 0; c < 2; ++c) tma_load_4d(zp + c * 8192, tm_z, &misc->zfull[zs], c * 64, (t0 + t) * SUB, h_idx, b_idx);
         if (!QSIDE)
-          bulk_load_1d(sp + Z_BYTES + W_BYTES, args.stats + (size_t(bh) * args.n_pad + size_t(t0 + t) * SUB), STAT_BYTES, &misc->full[st]);
-        if (++st == ST) { st = 0; par ^= 1; }
+          bulk_load_1d(zp + Z_BYTES, args.stats + (size_t(bh) * args.n_pad + size_t(t0 + t) * SUB), STAT_BYTES, &misc->zfull[zs]);
+        if (!mbar_wait(&misc->wempty[ws], wpar, abort_flag, 1102, t)) break;
+        mbar_expect_tx(&misc->wfull[ws], W_BYTES);
+        for (int c = 0; c < 4; ++c) tma_load_4d(wp + c * 8192, &tm_w, &misc->wfull[ws], c * 64, (t0 + t) * SUB, w_c2, w_c3);
+        if (++zs == ZST) { zs = 0; zpar ^= 1; }
+        if (++ws == WST) { ws = 0; wpar ^= 1; }
       }
     }
   } else if (warp == WARP_MMA) {
@@ -102,36 +112,42 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
       constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0, BF);
       constexpr uint32_t IDESC_OUT = make_idesc(BM, HD, 0, 1, BF);     // OUT += dS Z, Z MN-major (two 64-column atoms)
       const uint32_t x_lo = sdesc_lo(smem_u32(smem + OFF_X)), y_lo = sdesc_lo(smem_u32(smem + OFF_Y));
-      const uint32_t st_lo0 = sdesc_lo(smem_u32(smem + OFF_STAGE));
+      const uint32_t z_lo0 = sdesc_lo(smem_u32(smem + OFF_Z)), w_lo0 = sdesc_lo(smem_u32(smem + OFF_W));
       const uint32_t tb = tmem_base;
-      auto issue_scores = [&](uint32_t sp_lo, int u) {
+      // scores of one sub-tile: S from the Z stage zs, T from the W stage ws; W is free once these MMAs have completed
+      auto issue_scores = [&](int zs, int ws, int u) {
+        const uint32_t z_lo = z_lo0 + zs * (ZSTAGE_BYTES >> 4), w_lo = w_lo0 + ws * (W_BYTES >> 4);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          mma_ss_lo(tb + T_S + u * SUB, x_lo + (k / 4) * (16384 >> 4) + (k % 4) * 2, sp_lo + (k / 4) * (8192 >> 4) + (k % 4) * 2,
+          mma_ss_lo(tb + T_S + u * SUB, x_lo + (k / 4) * (16384 >> 4) + (k % 4) * 2, z_lo + (k / 4) * (8192 >> 4) + (k % 4) * 2,
                     IDESC_S, k > 0);
 #pragma unroll
         for (int k = 0; k < DV / 16; ++k)
           mma_ss_lo(tb + T_T + u * SUB, y_lo + (k / 4) * (16384 >> 4) + (k % 4) * 2,
-                    sp_lo + (Z_BYTES >> 4) + (k / 4) * (8192 >> 4) + (k % 4) * 2, IDESC_S, k > 0);
+                    w_lo + (k / 4) * (8192 >> 4) + (k % 4) * 2, IDESC_S, k > 0);
         mma_commit(&misc->s_full[u]);
+        mma_commit(&misc->wempty[ws]);
       };
       bool ok = mbar_wait(&misc->bar_xy, 0, abort_flag, 1201);
-      ok = ok && mbar_wait(&misc->full[0], 0, abort_flag, 1202);
+      ok = ok && mbar_wait(&misc->zfull[0], 0, abort_flag, 1202);
+      ok = ok && mbar_wait(&misc->wfull[0], 0, abort_flag, 1202);
       if (ok) {
         tc_fence_after();
-        issue_scores(st_lo0, 0);
-        int st = 0;
-        uint32_t par = 0;
+        issue_scores(0, 0, 0);
+        int zs = 0, ws = 0;                 // stages of sub-tile t
+        uint32_t zpar = 0, wpar = 0;
         for (int t = 0; t < nsub; ++t) {
           const int u = t & 1;
-          const uint32_t sp_lo = st_lo0 + st * (STAGE_BYTES >> 4);
-          int st_n = st + 1;
-          uint32_t par_n = par;
-          if (st_n == ST) { st_n = 0; par_n ^= 1; }
+          const uint32_t sp_lo = z_lo0 + zs * (ZSTAGE_BYTES >> 4);
+          int zs_n = zs + 1, ws_n = ws + 1;
+          uint32_t zpar_n = zpar, wpar_n = wpar;
+          if (zs_n == ZST) { zs_n = 0; zpar_n ^= 1; }
+          if (ws_n == WST) { ws_n = 0; wpar_n ^= 1; }
           if (t + 1 < nsub) {
-            if (!mbar_wait(&misc->full[st_n], par_n, abort_flag, 1203, t)) break;
+            if (!mbar_wait(&misc->zfull[zs_n], zpar_n, abort_flag, 1203, t)) break;
+            if (!mbar_wait(&misc->wfull[ws_n], wpar_n, abort_flag, 1205, t)) break;
             tc_fence_after();
-            issue_scores(st_lo0 + st_n * (STAGE_BYTES >> 4), u ^ 1);
+            issue_scores(zs_n, ws_n, u ^ 1);
           }
           if (!mbar_wait(&misc->ds_full[u], (t >> 1) & 1, abort_flag, 1204, t)) break;
           tc_fence_after();
@@ -140,9 +156,9 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
           for (int k = 0; k < SUB / 16; ++k)
             mma_ts_lo(tb + T_OUT, tb + T_S + u * SUB + k * 16, sp_lo + ((8192u >> 4) << 16) - (1u << 16) + k * (2048 >> 4), IDESC_OUT,
                       (t > 0 || k > 0));
-          mma_commit(&misc->empty[st]);
-          st = st_n;
-          par = par_n;
+          mma_commit(&misc->zempty[zs]);
+          zs = zs_n; zpar = zpar_n;
+          ws = ws_n; wpar = wpar_n;
         }
         mma_commit(&misc->acc_full);
       }
@@ -172,7 +188,7 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
     for (int t = 0; t < nsub; ++t) {
       const int u = t & 1;
       const uint32_t t_s = tb + T_S + u * SUB + g * 16, t_t = tb + T_T + u * SUB + g * 16;
-      const float4* stats = reinterpret_cast<const float4*>(smem + OFF_STAGE + st * STAGE_BYTES + Z_BYTES + W_BYTES) + g * 16;
+      const float4* stats = reinterpret_cast<const float4*>(smem + OFF_Z + st * ZSTAGE_BYTES + Z_BYTES) + g * 16;
       if (!mbar_wait(&misc->s_full[u], (t >> 1) & 1, abort_flag, 1301 + g, t)) { ok = false; break; }
       tc_fence_after();
       uint32_t s[16], tt[16], ds[8];
@@ -235,7 +251,7 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&misc->ds_full[u]);
-      if (++st == ST) st = 0;
+      if (++st == ZST) st = 0;
     }
     ok = ok && mbar_wait(&misc->acc_full, 0, abort_flag, 1311 + g);
     tc_fence_after();
@@ -271,15 +287,18 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
 // (P1 - lam P2)^T goes through one K-major shared-memory tile (A operand of dV += Pc^T dA).
 // ------------------------------------------------------------------------------------------------
 namespace dv128 {
-constexpr int BKV = 128, BQ = 64, HD = 128, DV = 256, ST = 2, NWG = 4;
+// Two rings, as in the side kernel: {Q1, Q2, statistics} feed the score MMAs and are free once those have completed;
+// dA feeds the dV MMAs one elementwise pass later.
+constexpr int BKV = 128, BQ = 64, HD = 128, DV = 256, QST = 2, AST = 2, NWG = 4;
 constexpr int K_BYTES = BKV * HD * 2;       // 32 KB: two boxes [128 x 64]
 constexpr int Q_BYTES = BQ * HD * 2;        // 16 KB: two boxes [64 x 64]
 constexpr int DA_BYTES = BQ * DV * 2;       // 32 KB: four boxes [64 x 64]
 constexpr int STAT_BYTES = BQ * 16;
-constexpr int STAGE_BYTES = 2 * Q_BYTES + DA_BYTES + STAT_BYTES;   // 65 KB
+constexpr int QSTAGE_BYTES = 2 * Q_BYTES + STAT_BYTES;             // 33 KB
 constexpr int PC_BYTES = BKV * BQ * 2;      // 16 KB
-constexpr int OFF_K1 = 0, OFF_K2 = K_BYTES, OFF_PC = 2 * K_BYTES, OFF_STAGE = OFF_PC + PC_BYTES;   // 80 KB
-constexpr int OFF_MISC = OFF_STAGE + ST * STAGE_BYTES;                                             // 210 KB
+constexpr int OFF_K1 = 0, OFF_K2 = K_BYTES, OFF_PC = 2 * K_BYTES, OFF_QS = OFF_PC + PC_BYTES;      // 80 KB
+constexpr int OFF_DA = OFF_QS + QST * QSTAGE_BYTES;                                                // 146 KB
+constexpr int OFF_MISC = OFF_DA + AST * DA_BYTES;                                                  // 210 KB
 constexpr int MISC_BYTES = 1024;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
 constexpr int NUM_THREADS = NWG * 128 + 64;
@@ -287,7 +306,7 @@ constexpr int WARP_TMA = NWG * 4, WARP_MMA = NWG * 4 + 1;
 constexpr int T_DV = 0, T_S1 = 256, T_S2 = 384;
 struct Misc {
   uint64_t bar_kv;
-  uint64_t full[ST], empty[ST];
+  uint64_t qfull[QST], qempty[QST], afull[AST], aempty[AST];
   uint64_t s_full[2], e_done, mma_done, acc_full;
   uint32_t tmem_slot;
   int abort_flag;
@@ -313,7 +332,8 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
 
   if (warp == WARP_TMA && lane == 0) {
     mbar_init(&misc->bar_kv, 1);
-    for (int i = 0; i < ST; ++i) { mbar_init(&misc->full[i], 1); mbar_init(&misc->empty[i], 1); }
+    for (int i = 0; i < QST; ++i) { mbar_init(&misc->qfull[i], 1); mbar_init(&misc->qempty[i], 1); }
+    for (int i = 0; i < AST; ++i) { mbar_init(&misc->afull[i], 1); mbar_init(&misc->aempty[i], 1); }
     for (int u = 0; u < 2; ++u) mbar_init(&misc->s_full[u], 1);
     mbar_init(&misc->e_done, NWG * 128);
     mbar_init(&misc->mma_done, 1);
@@ -334,19 +354,23 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
         tma_load_4d(smem + OFF_K1 + c * 16384, &tm_k1, &misc->bar_kv, c * 64, kv_tile * BKV, h_idx, b_idx);
         tma_load_4d(smem + OFF_K2 + c * 16384, &tm_k2, &misc->bar_kv, c * 64, kv_tile * BKV, h_idx, b_idx);
       }
-      int st = 0;
-      uint32_t par = 1;
+      int qs = 0, as = 0;
+      uint32_t qpar = 1, apar = 1;
       for (int i = 0; i < nq; ++i) {
-        uint8_t* sp = smem + OFF_STAGE + st * STAGE_BYTES;
-        if (!mbar_wait(&misc->empty[st], par, abort_flag, 1401, i)) break;
-        mbar_expect_tx(&misc->full[st], STAGE_BYTES);
+        uint8_t* qp = smem + OFF_QS + qs * QSTAGE_BYTES;
+        uint8_t* ap = smem + OFF_DA + as * DA_BYTES;
+        if (!mbar_wait(&misc->qempty[qs], qpar, abort_flag, 1401, i)) break;
+        mbar_expect_tx(&misc->qfull[qs], QSTAGE_BYTES);
         for (int c = 0; c < 2; ++c) {
-          tma_load_4d(sp + c * 8192, &tm_q1, &misc->full[st], c * 64, (i0 + i) * BQ, h_idx, b_idx);
-          tma_load_4d(sp + Q_BYTES + c * 8192, &tm_q2, &misc->full[st], c * 64, (i0 + i) * BQ, h_idx, b_idx);
+          tma_load_4d(qp + c * 8192, &tm_q1, &misc->qfull[qs], c * 64, (i0 + i) * BQ, h_idx, b_idx);
+          tma_load_4d(qp + Q_BYTES + c * 8192, &tm_q2, &misc->qfull[qs], c * 64, (i0 + i) * BQ, h_idx, b_idx);
         }
-        for (int c = 0; c < 4; ++c) tma_load_4d(sp + 2 * Q_BYTES + c * 8192, &tm_da, &misc->full[st], c * 64, (i0 + i) * BQ, bh, 0);
-        bulk_load_1d(sp + 2 * Q_BYTES + DA_BYTES, args.stats + (size_t(bh) * args.n_pad + size_t(i0 + i) * BQ), STAT_BYTES, &misc->full[st]);
-        if (++st == ST) { st = 0; par ^= 1; }
+        bulk_load_1d(qp + 2 * Q_BYTES, args.stats + (size_t(bh) * args.n_pad + size_t(i0 + i) * BQ), STAT_BYTES, &misc->qfull[qs]);
+        if (!mbar_wait(&misc->aempty[as], apar, abort_flag, 1402, i)) break;
+        mbar_expect_tx(&misc->afull[as], DA_BYTES);
+        for (int c = 0; c < 4; ++c) tma_load_4d(ap + c * 8192, &tm_da, &misc->afull[as], c * 64, (i0 + i) * BQ, bh, 0);
+        if (++qs == QST) { qs = 0; qpar ^= 1; }
+        if (++as == AST) { as = 0; apar ^= 1; }
       }
     }
   } else if (warp == WARP_MMA) {
@@ -355,9 +379,10 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
       constexpr uint32_t IDESC_DV = make_idesc(BKV, DV, 0, 1, BF);     // N = 256: dA as MN-major B, four atoms 8 KB apart
       const uint32_t k1_lo = sdesc_lo(smem_u32(smem + OFF_K1)), k2_lo = sdesc_lo(smem_u32(smem + OFF_K2));
       const uint32_t pc_lo = sdesc_lo(smem_u32(smem + OFF_PC));
-      const uint32_t st_lo0 = sdesc_lo(smem_u32(smem + OFF_STAGE));
+      const uint32_t q_lo0 = sdesc_lo(smem_u32(smem + OFF_QS)), a_lo0 = sdesc_lo(smem_u32(smem + OFF_DA));
       const uint32_t tb = tmem_base;
-      auto issue_scores = [&](uint32_t sp_lo, int u) {
+      auto issue_scores = [&](int qs, int u) {
+        const uint32_t sp_lo = q_lo0 + qs * (QSTAGE_BYTES >> 4);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
           mma_ss_lo(tb + T_S1 + u * BQ, k1_lo + (k / 4) * (16384 >> 4) + (k % 4) * 2, sp_lo + (k / 4) * (8192 >> 4) + (k % 4) * 2,
@@ -369,33 +394,35 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
         mma_commit(&misc->s_full[u]);
       };
       bool ok = mbar_wait(&misc->bar_kv, 0, abort_flag, 1501);
-      ok = ok && mbar_wait(&misc->full[0], 0, abort_flag, 1502);
+      ok = ok && mbar_wait(&misc->qfull[0], 0, abort_flag, 1502);
       if (ok) {
         tc_fence_after();
-        issue_scores(st_lo0, 0);
-        int st = 0;
-        uint32_t par = 0;
+        issue_scores(0, 0);
+        int qs = 0, as = 0;
+        uint32_t qpar = 0, apar = 0;
         for (int i = 0; i < nq; ++i) {
           const int u = i & 1;
-          const uint32_t sp_lo = st_lo0 + st * (STAGE_BYTES >> 4);
-          int st_n = st + 1;
-          uint32_t par_n = par;
-          if (st_n == ST) { st_n = 0; par_n ^= 1; }
+          int qs_n = qs + 1;
+          uint32_t qpar_n = qpar;
+          if (qs_n == QST) { qs_n = 0; qpar_n ^= 1; }
           if (i + 1 < nq) {
-            if (!mbar_wait(&misc->full[st_n], par_n, abort_flag, 1503, i)) break;
+            if (!mbar_wait(&misc->qfull[qs_n], qpar_n, abort_flag, 1503, i)) break;
             tc_fence_after();
-            issue_scores(st_lo0 + st_n * (STAGE_BYTES >> 4), u ^ 1);
+            issue_scores(qs_n, u ^ 1);
           }
+          // the {Q1, Q2, statistics} stage of tile i is free once the warpgroups have read its statistics: e_done(i)
           if (!mbar_wait(&misc->e_done, i & 1, abort_flag, 1504, i)) break;
+          if (!mbar_wait(&misc->afull[as], apar, abort_flag, 1505, i)) break;
           tc_fence_after();
+          mbar_arrive(&misc->qempty[qs]);        // plain arrival: the score MMAs that read this stage completed before e_done(i)
 #pragma unroll
           for (int k = 0; k < BQ / 16; ++k)
-            mma_ss_lo(tb + T_DV, pc_lo + k * 2, sp_lo + ((2 * Q_BYTES) >> 4) + ((8192u >> 4) << 16) - (1u << 16) + k * (2048 >> 4),
+            mma_ss_lo(tb + T_DV, pc_lo + k * 2, a_lo0 + as * (DA_BYTES >> 4) + ((8192u >> 4) << 16) - (1u << 16) + k * (2048 >> 4),
                       IDESC_DV, (i > 0 || k > 0));
           mma_commit(&misc->mma_done);
-          mma_commit(&misc->empty[st]);
-          st = st_n;
-          par = par_n;
+          mma_commit(&misc->aempty[as]);
+          qs = qs_n; qpar = qpar_n;
+          if (++as == AST) { as = 0; apar ^= 1; }
         }
         mma_commit(&misc->acc_full);
       }
@@ -415,7 +442,7 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
     int st = 0;
     for (int i = 0; i < nq; ++i) {
       const int u = i & 1;
-      const float4* stats = reinterpret_cast<const float4*>(smem + OFF_STAGE + st * STAGE_BYTES + 2 * Q_BYTES + DA_BYTES) + g * 16;
+      const float4* stats = reinterpret_cast<const float4*>(smem + OFF_QS + st * QSTAGE_BYTES + 2 * Q_BYTES) + g * 16;
       if (!mbar_wait(&misc->s_full[u], (i >> 1) & 1, abort_flag, 1601 + g, i)) { ok = false; break; }
       tc_fence_after();
       uint32_t s1[16], s2[16], pc[8];
@@ -471,7 +498,7 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
       mbar_arrive(&misc->e_done);
-      if (++st == ST) st = 0;
+      if (++st == QST) st = 0;
     }
     ok = ok && mbar_wait(&misc->acc_full, 0, abort_flag, 1611 + g);
     tc_fence_after();
