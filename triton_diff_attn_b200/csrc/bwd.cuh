@@ -543,6 +543,8 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
 // own columns (TMEM A-operand of dS_b K_b).  The MMAs of sub-tile t+1 are issued before
 // the issuer waits for dS(t), so the warpgroups always find their next scores ready.
 // ------------------------------------------------------------------------------------------------
+// (Separate ring barriers for the V part of a stage, free half a tile before the K part, measured no change here:
+// this kernel does not wait for its loads.  The D = 128 kernels did, see bwd128.cuh.)
 namespace dq64 {
 constexpr int BM = 128, BN = 128, SUB = 64, HD = 64, DV = 128, ST = 2;
 constexpr int Q_BYTES = BM * HD * 2;        // 16 KB
