@@ -696,7 +696,8 @@ def main():
                 pipe.submit(host_in, host_out, host_dl, pr.lam_t, lam_init, rms, args.causal)
             pipe.end()
 
-        e2e_steps = min(args.steps, 50)
+        # enough steps for the steady state to dominate the pipeline's fill and drain, about a second in all
+        e2e_steps = max(10, min(100, int(1000.0 / (2.0 * ms_step))))
         e2e_run(3)
         ms_e2e = timed(lambda: e2e_run(e2e_steps), 1) / e2e_steps
         # each leg alone, a few steps: which of them bounds the overlapped figure
@@ -723,7 +724,7 @@ def main():
                              "host_gbs_all_ranks_overlapped": world * (h2d + d2h) / ms_e2e / 1e6,
                              "bound": max((("h2d", ms_h2d), ("d2h", ms_d2h), ("kernels", ms_k)), key=lambda kv: kv[1])[0],
                              "note": "each leg timed alone (max over ranks); the pipeline can at best reach the longest leg"},
-               "how": "HostStepPipeline: H2D, kernels and D2H of consecutive steps on three streams, double-buffered staging"}
+               "how": "HostStepPipeline: H2D, diffattn_fwd + diffattn_bwd and D2H of consecutive steps on three streams; two ring slots of preallocated device buffers, no allocator call per step"}
         del host_in, host_out, dev_in, leaves
 
     # ---- B=64 H=32 N=4096 D=64 split over the ranks along the batch (same total work at every N)
