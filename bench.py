@@ -50,10 +50,9 @@ WORKLOADS = {
 DEFAULT_WORKLOAD = "b4h16n4096d64"
 SPLIT = (64, 32, 4096, 64, 1.0, 0.5, 0.8, True)                     # batch-sharded workload, split over the ranks
 CPU_SMALL = (2, 16, 512, 32, 1.0, 0.5, 0.8, True)                   # the CPU-runnable shape: B=2 H=16 N=512 D=32, fp32
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture whose
-# summary (command, commit) is profiles/b4h16n4096d64_kernels_ncu.md; reported only for the workload and flags of
-# that capture.
-NCU_TRAFFIC = {"workload": DEFAULT_WORKLOAD, "source": "ncu capture summarised in profiles/b4h16n4096d64_kernels_ncu.md (kernels of commit ec0d096)",
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from an ncu capture of this workload (its summary, with
+# the command, sits under profiles/); reported only for the workload and flags of that capture.
+NCU_TRAFFIC = {"workload": DEFAULT_WORKLOAD, "source": "ncu --set full capture of the kernels of commit ec0d096, summarised under profiles/",
                "bytes": {"diffattn_fwd64_kernel": 308.5e6, "diffattn_bwd_pre_kernel": 254.9e6,
                          "diffattn_bwd_dkdv64_kernel": 381.1e6, "diffattn_bwd_dq64_kernel": 325.3e6}}
 METRIC = "diff-attn fwd+bwd TFLOP/s (credited 28*B*H*N^2*D), fp16"
