@@ -287,18 +287,19 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
 // (P1 - lam P2)^T goes through one K-major shared-memory tile (A operand of dV += Pc^T dA).
 // ------------------------------------------------------------------------------------------------
 namespace dv128 {
-// Two rings, as in the side kernel: {Q1, Q2, statistics} feed the score MMAs and are free once those have completed;
-// dA feeds the dV MMAs one elementwise pass later.
-constexpr int BKV = 128, BQ = 64, HD = 128, DV = 256, QST = 2, AST = 2, NWG = 4;
+// Three rings, by lifetime: {Q1, Q2} feed the score MMAs and are free once those have completed; the per-column
+// statistics (1 KB) are read by the warpgroups until the end of their pass; dA feeds the dV MMAs after that pass.
+constexpr int BKV = 128, BQ = 64, HD = 128, DV = 256, QST = 2, AST = 2, TST = 4, NWG = 4;
 constexpr int K_BYTES = BKV * HD * 2;       // 32 KB: two boxes [128 x 64]
 constexpr int Q_BYTES = BQ * HD * 2;        // 16 KB: two boxes [64 x 64]
 constexpr int DA_BYTES = BQ * DV * 2;       // 32 KB: four boxes [64 x 64]
 constexpr int STAT_BYTES = BQ * 16;
-constexpr int QSTAGE_BYTES = 2 * Q_BYTES + STAT_BYTES;             // 33 KB
+constexpr int QSTAGE_BYTES = 2 * Q_BYTES;                          // 32 KB
 constexpr int PC_BYTES = BKV * BQ * 2;      // 16 KB
 constexpr int OFF_K1 = 0, OFF_K2 = K_BYTES, OFF_PC = 2 * K_BYTES, OFF_QS = OFF_PC + PC_BYTES;      // 80 KB
-constexpr int OFF_DA = OFF_QS + QST * QSTAGE_BYTES;                                                // 146 KB
-constexpr int OFF_MISC = OFF_DA + AST * DA_BYTES;                                                  // 210 KB
+constexpr int OFF_DA = OFF_QS + QST * QSTAGE_BYTES;                                                // 144 KB
+constexpr int OFF_ST = OFF_DA + AST * DA_BYTES;                                                    // 208 KB
+constexpr int OFF_MISC = OFF_ST + TST * STAT_BYTES;                                                // 212 KB
 constexpr int MISC_BYTES = 1024;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
 constexpr int NUM_THREADS = NWG * 128 + 64;
@@ -306,7 +307,7 @@ constexpr int WARP_TMA = NWG * 4, WARP_MMA = NWG * 4 + 1;
 constexpr int T_DV = 0, T_S1 = 256, T_S2 = 384;
 struct Misc {
   uint64_t bar_kv;
-  uint64_t qfull[QST], qempty[QST], afull[AST], aempty[AST];
+  uint64_t qfull[QST], qempty[QST], afull[AST], aempty[AST], tfull[TST], tempty[TST];
   uint64_t s_full[2], e_done, mma_done, acc_full;
   uint32_t tmem_slot;
   int abort_flag;
@@ -333,6 +334,7 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
   if (warp == WARP_TMA && lane == 0) {
     mbar_init(&misc->bar_kv, 1);
     for (int i = 0; i < QST; ++i) { mbar_init(&misc->qfull[i], 1); mbar_init(&misc->qempty[i], 1); }
+    for (int i = 0; i < TST; ++i) { mbar_init(&misc->tfull[i], 1); mbar_init(&misc->tempty[i], 1); }
     for (int i = 0; i < AST; ++i) { mbar_init(&misc->afull[i], 1); mbar_init(&misc->aempty[i], 1); }
     for (int u = 0; u < 2; ++u) mbar_init(&misc->s_full[u], 1);
     mbar_init(&misc->e_done, NWG * 128);
@@ -354,8 +356,8 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
         tma_load_4d(smem + OFF_K1 + c * 16384, &tm_k1, &misc->bar_kv, c * 64, kv_tile * BKV, h_idx, b_idx);
         tma_load_4d(smem + OFF_K2 + c * 16384, &tm_k2, &misc->bar_kv, c * 64, kv_tile * BKV, h_idx, b_idx);
       }
-      int qs = 0, as = 0;
-      uint32_t qpar = 1, apar = 1;
+      int qs = 0, as = 0, ts = 0;
+      uint32_t qpar = 1, apar = 1, tpar = 1;
       for (int i = 0; i < nq; ++i) {
         uint8_t* qp = smem + OFF_QS + qs * QSTAGE_BYTES;
         uint8_t* ap = smem + OFF_DA + as * DA_BYTES;
@@ -365,12 +367,15 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
           tma_load_4d(qp + c * 8192, &tm_q1, &misc->qfull[qs], c * 64, (i0 + i) * BQ, h_idx, b_idx);
           tma_load_4d(qp + Q_BYTES + c * 8192, &tm_q2, &misc->qfull[qs], c * 64, (i0 + i) * BQ, h_idx, b_idx);
         }
-        bulk_load_1d(qp + 2 * Q_BYTES, args.stats + (size_t(bh) * args.n_pad + size_t(i0 + i) * BQ), STAT_BYTES, &misc->qfull[qs]);
+        if (!mbar_wait(&misc->tempty[ts], tpar, abort_flag, 1403, i)) break;
+        mbar_expect_tx(&misc->tfull[ts], STAT_BYTES);
+        bulk_load_1d(smem + OFF_ST + ts * STAT_BYTES, args.stats + (size_t(bh) * args.n_pad + size_t(i0 + i) * BQ), STAT_BYTES, &misc->tfull[ts]);
         if (!mbar_wait(&misc->aempty[as], apar, abort_flag, 1402, i)) break;
         mbar_expect_tx(&misc->afull[as], DA_BYTES);
         for (int c = 0; c < 4; ++c) tma_load_4d(ap + c * 8192, &tm_da, &misc->afull[as], c * 64, (i0 + i) * BQ, bh, 0);
         if (++qs == QST) { qs = 0; qpar ^= 1; }
         if (++as == AST) { as = 0; apar ^= 1; }
+        if (++ts == TST) { ts = 0; tpar ^= 1; }
       }
     }
   } else if (warp == WARP_MMA) {
@@ -391,30 +396,35 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
         for (int k = 0; k < HD / 16; ++k)
           mma_ss_lo(tb + T_S2 + u * BQ, k2_lo + (k / 4) * (16384 >> 4) + (k % 4) * 2,
                     sp_lo + (Q_BYTES >> 4) + (k / 4) * (8192 >> 4) + (k % 4) * 2, IDESC_S, k > 0);
-        mma_commit(&misc->s_full[u]);
+        mma_commit(&misc->s_full[u]);          // (the statistics of the tile were waited for before: s_full implies them)
+        mma_commit(&misc->qempty[qs]);
       };
       bool ok = mbar_wait(&misc->bar_kv, 0, abort_flag, 1501);
       ok = ok && mbar_wait(&misc->qfull[0], 0, abort_flag, 1502);
+      ok = ok && mbar_wait(&misc->tfull[0], 0, abort_flag, 1502);
       if (ok) {
         tc_fence_after();
         issue_scores(0, 0);
-        int qs = 0, as = 0;
-        uint32_t qpar = 0, apar = 0;
+        int qs = 0, as = 0, ts = 0;
+        uint32_t qpar = 0, apar = 0, tpar = 0;
         for (int i = 0; i < nq; ++i) {
           const int u = i & 1;
           int qs_n = qs + 1;
           uint32_t qpar_n = qpar;
           if (qs_n == QST) { qs_n = 0; qpar_n ^= 1; }
+          int ts_n = ts + 1;
+          uint32_t tpar_n = tpar;
+          if (ts_n == TST) { ts_n = 0; tpar_n ^= 1; }
           if (i + 1 < nq) {
             if (!mbar_wait(&misc->qfull[qs_n], qpar_n, abort_flag, 1503, i)) break;
+            if (!mbar_wait(&misc->tfull[ts_n], tpar_n, abort_flag, 1506, i)) break;
             tc_fence_after();
             issue_scores(qs_n, u ^ 1);
           }
-          // the {Q1, Q2, statistics} stage of tile i is free once the warpgroups have read its statistics: e_done(i)
           if (!mbar_wait(&misc->e_done, i & 1, abort_flag, 1504, i)) break;
           if (!mbar_wait(&misc->afull[as], apar, abort_flag, 1505, i)) break;
           tc_fence_after();
-          mbar_arrive(&misc->qempty[qs]);        // plain arrival: the score MMAs that read this stage completed before e_done(i)
+          mbar_arrive(&misc->tempty[ts]);        // the warpgroups have read the statistics of tile i (plain arrival)
 #pragma unroll
           for (int k = 0; k < BQ / 16; ++k)
             mma_ss_lo(tb + T_DV, pc_lo + k * 2, a_lo0 + as * (DA_BYTES >> 4) + ((8192u >> 4) << 16) - (1u << 16) + k * (2048 >> 4),
@@ -422,6 +432,7 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
           mma_commit(&misc->mma_done);
           mma_commit(&misc->aempty[as]);
           qs = qs_n; qpar = qpar_n;
+          ts = ts_n; tpar = tpar_n;
           if (++as == AST) { as = 0; apar ^= 1; }
         }
         mma_commit(&misc->acc_full);
@@ -442,7 +453,7 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
     int st = 0;
     for (int i = 0; i < nq; ++i) {
       const int u = i & 1;
-      const float4* stats = reinterpret_cast<const float4*>(smem + OFF_QS + st * QSTAGE_BYTES + 2 * Q_BYTES) + g * 16;
+      const float4* stats = reinterpret_cast<const float4*>(smem + OFF_ST + st * STAT_BYTES) + g * 16;
       if (!mbar_wait(&misc->s_full[u], (i >> 1) & 1, abort_flag, 1601 + g, i)) { ok = false; break; }
       tc_fence_after();
       uint32_t s1[16], s2[16], pc[8];
@@ -498,7 +509,7 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
       mbar_arrive(&misc->e_done);
-      if (++st == QST) st = 0;
+      if (++st == TST) st = 0;
     }
     ok = ok && mbar_wait(&misc->acc_full, 0, abort_flag, 1611 + g);
     tc_fence_after();
