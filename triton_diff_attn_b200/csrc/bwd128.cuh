@@ -19,7 +19,7 @@ namespace side128 {
 // as those MMAs have completed; Z feeds the S scores AND the output MMAs of its sub-tile, one elementwise pass
 // later.  With one ring of {Z, W} stages the next load could only be requested after the output MMAs, and its whole
 // latency sat between two sub-tiles (the kernel ran at half the tensor pipe's pace).
-constexpr int BM = 128, SUB = 64, HD = 128, DV = 256, ZST = 3, WST = 2, NWG = 4;
+constexpr int BM = 128, SUB = 64, HD = 128, DV = 256, ZST = 4, WST = 3, NWG = 4;
 constexpr int X_BYTES = BM * HD * 2;        // 32 KB: two boxes [128 x 64]
 constexpr int Y_BYTES = BM * DV * 2;        // 64 KB: four boxes [128 x 64]
 constexpr int Z_BYTES = SUB * HD * 2;       // 16 KB: two boxes [64 x 64]
@@ -27,16 +27,26 @@ constexpr int W_BYTES = SUB * DV * 2;       // 32 KB: four boxes [64 x 64]
 constexpr int STAT_BYTES = SUB * 16;        // 1 KB
 constexpr int ZSTAGE_BYTES = Z_BYTES + STAT_BYTES;            // 17 KB: the per-column statistics travel with Z
 constexpr int OFF_X = 0, OFF_Y = X_BYTES, OFF_W = X_BYTES + Y_BYTES;       // 96 KB
-constexpr int OFF_Z = OFF_W + WST * W_BYTES;                               // 160 KB
-constexpr int OFF_MISC = OFF_Z + ZST * ZSTAGE_BYTES;                       // 211 KB
+constexpr int OFF_Z = OFF_W + 2 * W_BYTES;                                 // 160 KB
+// Once Y has been copied into TMEM its 64 KB tile is ring space: the W ring has three stages (its own two and the
+// first half of Y's tile), the Z ring four (its own three and one in the second half of Y's tile).  The stages in
+// Y's tile are first filled for sub-tiles 2 (W) and 3 (Z), after the copy.
+static_assert(WST == 3 && ZST == 4 && Y_BYTES == 2 * W_BYTES && ZSTAGE_BYTES <= W_BYTES, "ring stages inside the Y tile");
+__host__ __device__ constexpr int w_stage_off(int s) { return OFF_Y + ((s + 2) & 3) * W_BYTES; }
+__host__ __device__ constexpr int z_stage_off(int s) { return s < 3 ? OFF_Z + s * ZSTAGE_BYTES : OFF_Y + W_BYTES; }
+constexpr int OFF_MISC = OFF_Z + 3 * ZSTAGE_BYTES;                       // 211 KB
 constexpr int MISC_BYTES = 1024;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
 constexpr int NUM_THREADS = NWG * 128 + 64;
 constexpr int WARP_TMA = NWG * 4, WARP_MMA = NWG * 4 + 1;
-constexpr int T_S = 0, T_T = 128, T_OUT = 256;
+// TMEM: S two 64-column buffers [0,128) | T likewise [128,256) | OUT [256,384) | Y as 16-bit pairs [384,512).
+// Y (the stationary 256-wide operand) is copied from its shared-memory tile into TMEM once per CTA and serves as the
+// TMEM A operand of T = Y W^T: those 16 MMAs per sub-tile then read only W from shared memory (2 KB instead of 6 KB
+// per step), which is what bounds this kernel.
+constexpr int T_S = 0, T_T = 128, T_OUT = 256, T_Y = 384;
 struct Misc {
-  uint64_t bar_xy;
-  uint64_t zfull[ZST], zempty[ZST], wfull[WST], wempty[WST];
+  uint64_t bar_xy, y_ready;
+  uint64_t full[WST], zempty[ZST], wempty[WST];
   uint64_t s_full[2], ds_full[2], acc_full;
   uint32_t tmem_slot;
   int abort_flag;
@@ -72,8 +82,9 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
 
   if (warp == WARP_TMA && lane == 0) {
     mbar_init(&misc->bar_xy, 1);
-    for (int i = 0; i < ZST; ++i) { mbar_init(&misc->zfull[i], 1); mbar_init(&misc->zempty[i], 1); }
-    for (int i = 0; i < WST; ++i) { mbar_init(&misc->wfull[i], 1); mbar_init(&misc->wempty[i], 1); }
+    mbar_init(&misc->y_ready, NWG * 128);
+    for (int i = 0; i < ZST; ++i) mbar_init(&misc->zempty[i], 1);
+    for (int i = 0; i < WST; ++i) { mbar_init(&misc->full[i], 1); mbar_init(&misc->wempty[i], 1); }
     for (int u = 0; u < 2; ++u) { mbar_init(&misc->s_full[u], 1); mbar_init(&misc->ds_full[u], NWG * 128); }
     mbar_init(&misc->acc_full, 1);
     misc->abort_flag = 0;
@@ -93,16 +104,18 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
       int zs = 0, ws = 0;
       uint32_t zpar = 1, wpar = 1;
       for (int t = 0; t < nsub; ++t) {
-        uint8_t* zp = smem + OFF_Z + zs * ZSTAGE_BYTES;
-        uint8_t* wp = smem + OFF_W + ws * W_BYTES;
+        uint8_t* zp = smem + z_stage_off(zs);
+        uint8_t* wp = smem + w_stage_off(ws);
+        if (t == 2 && !mbar_wait(&misc->y_ready, 0, abort_flag, 1103, t)) break;     // stage 2 is Y's tile
         if (!mbar_wait(&misc->zempty[zs], zpar, abort_flag, 1101, t)) break;
-        mbar_expect_tx(&misc->zfull[zs], QSIDE ? Z_BYTES : ZSTAGE_BYTES);
-        for (int c = 0; c < 2; ++c) tma_load_4d(zp + c * 8192, tm_z, &misc->zfull[zs], c * 64, (t0 + t) * SUB, h_idx, b_idx);
-        if (!QSIDE)
-          bulk_load_1d(zp + Z_BYTES, args.stats + (size_t(bh) * args.n_pad + size_t(t0 + t) * SUB), STAT_BYTES, &misc->zfull[zs]);
         if (!mbar_wait(&misc->wempty[ws], wpar, abort_flag, 1102, t)) break;
-        mbar_expect_tx(&misc->wfull[ws], W_BYTES);
-        for (int c = 0; c < 4; ++c) tma_load_4d(wp + c * 8192, &tm_w, &misc->wfull[ws], c * 64, (t0 + t) * SUB, w_c2, w_c3);
+        // one arrival barrier per sub-tile for both operands (indexed like the W ring, the shallower one): the issuer
+        // pays one wait instead of two -- every mbarrier wait costs it 110-150 clocks even when the phase is complete
+        mbar_expect_tx(&misc->full[ws], (QSIDE ? Z_BYTES : ZSTAGE_BYTES) + W_BYTES);
+        for (int c = 0; c < 2; ++c) tma_load_4d(zp + c * 8192, tm_z, &misc->full[ws], c * 64, (t0 + t) * SUB, h_idx, b_idx);
+        if (!QSIDE)
+          bulk_load_1d(zp + Z_BYTES, args.stats + (size_t(bh) * args.n_pad + size_t(t0 + t) * SUB), STAT_BYTES, &misc->full[ws]);
+        for (int c = 0; c < 4; ++c) tma_load_4d(wp + c * 8192, &tm_w, &misc->full[ws], c * 64, (t0 + t) * SUB, w_c2, w_c3);
         if (++zs == ZST) { zs = 0; zpar ^= 1; }
         if (++ws == WST) { ws = 0; wpar ^= 1; }
       }
@@ -111,41 +124,39 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
     if (elect_one()) {
       constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0, BF);
       constexpr uint32_t IDESC_OUT = make_idesc(BM, HD, 0, 1, BF);     // OUT += dS Z, Z MN-major (two 64-column atoms)
-      const uint32_t x_lo = sdesc_lo(smem_u32(smem + OFF_X)), y_lo = sdesc_lo(smem_u32(smem + OFF_Y));
-      const uint32_t z_lo0 = sdesc_lo(smem_u32(smem + OFF_Z)), w_lo0 = sdesc_lo(smem_u32(smem + OFF_W));
+      const uint32_t x_lo = sdesc_lo(smem_u32(smem + OFF_X));
+      const uint32_t s_lo0 = sdesc_lo(smem_u32(smem)), w_lo0 = sdesc_lo(smem_u32(smem + OFF_Y));
       const uint32_t tb = tmem_base;
       // scores of one sub-tile: S from the Z stage zs, T from the W stage ws; W is free once these MMAs have completed
       auto issue_scores = [&](int zs, int ws, int u) {
-        const uint32_t z_lo = z_lo0 + zs * (ZSTAGE_BYTES >> 4), w_lo = w_lo0 + ws * (W_BYTES >> 4);
+        const uint32_t z_lo = s_lo0 + (z_stage_off(zs) >> 4), w_lo = w_lo0 + ((ws + 2) & 3) * (W_BYTES >> 4);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
           mma_ss_lo(tb + T_S + u * SUB, x_lo + (k / 4) * (16384 >> 4) + (k % 4) * 2, z_lo + (k / 4) * (8192 >> 4) + (k % 4) * 2,
                     IDESC_S, k > 0);
 #pragma unroll
         for (int k = 0; k < DV / 16; ++k)
-          mma_ss_lo(tb + T_T + u * SUB, y_lo + (k / 4) * (16384 >> 4) + (k % 4) * 2,
-                    w_lo + (k / 4) * (8192 >> 4) + (k % 4) * 2, IDESC_S, k > 0);
+          mma_ts_lo(tb + T_T + u * SUB, tb + T_Y + k * 8, w_lo + (k / 4) * (8192 >> 4) + (k % 4) * 2, IDESC_S, k > 0);
         mma_commit(&misc->s_full[u]);
         mma_commit(&misc->wempty[ws]);
       };
       bool ok = mbar_wait(&misc->bar_xy, 0, abort_flag, 1201);
-      ok = ok && mbar_wait(&misc->zfull[0], 0, abort_flag, 1202);
-      ok = ok && mbar_wait(&misc->wfull[0], 0, abort_flag, 1202);
+      ok = ok && mbar_wait(&misc->y_ready, 0, abort_flag, 1206);
+      ok = ok && mbar_wait(&misc->full[0], 0, abort_flag, 1202);
       if (ok) {
         tc_fence_after();
         issue_scores(0, 0, 0);
         int zs = 0, ws = 0;                 // stages of sub-tile t
-        uint32_t zpar = 0, wpar = 0;
+        uint32_t wpar = 0;
         for (int t = 0; t < nsub; ++t) {
           const int u = t & 1;
-          const uint32_t sp_lo = z_lo0 + zs * (ZSTAGE_BYTES >> 4);
+          const uint32_t sp_lo = s_lo0 + (z_stage_off(zs) >> 4);
           int zs_n = zs + 1, ws_n = ws + 1;
-          uint32_t zpar_n = zpar, wpar_n = wpar;
-          if (zs_n == ZST) { zs_n = 0; zpar_n ^= 1; }
+          uint32_t wpar_n = wpar;
+          if (zs_n == ZST) zs_n = 0;
           if (ws_n == WST) { ws_n = 0; wpar_n ^= 1; }
           if (t + 1 < nsub) {
-            if (!mbar_wait(&misc->zfull[zs_n], zpar_n, abort_flag, 1203, t)) break;
-            if (!mbar_wait(&misc->wfull[ws_n], wpar_n, abort_flag, 1205, t)) break;
+            if (!mbar_wait(&misc->full[ws_n], wpar_n, abort_flag, 1203, t)) break;
             tc_fence_after();
             issue_scores(zs_n, ws_n, u ^ 1);
           }
@@ -157,7 +168,7 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
             mma_ts_lo(tb + T_OUT, tb + T_S + u * SUB + k * 16, sp_lo + ((8192u >> 4) << 16) - (1u << 16) + k * (2048 >> 4), IDESC_OUT,
                       (t > 0 || k > 0));
           mma_commit(&misc->zempty[zs]);
-          zs = zs_n; zpar = zpar_n;
+          zs = zs_n;
           ws = ws_n; wpar = wpar_n;
         }
         mma_commit(&misc->acc_full);
@@ -183,12 +194,26 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
     const uint32_t down2 = uint32_t(tile * BM + row) >> 1;
     const int down_odd = row & 1;
     const float sgs = DROP ? sg * args.drop_scale : sg;
-    bool ok = true;
+    bool ok = mbar_wait(&misc->bar_xy, 0, abort_flag, 1300 + g);
+    {
+      // Y into TMEM: this thread's row, the 64 columns of box g (128 bytes, swizzled in 16-byte chunks) -> 32 columns
+      uint32_t yv[32];
+      const uint8_t* yrow = smem + OFF_Y + g * 16384 + row * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint4 v = *reinterpret_cast<const uint4*>(yrow + ((c ^ (row & 7)) << 4));
+        yv[4 * c] = v.x; yv[4 * c + 1] = v.y; yv[4 * c + 2] = v.z; yv[4 * c + 3] = v.w;
+      }
+      tmem_st32(tb + T_Y + g * 32, yv);
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&misc->y_ready);
+    }
     int st = 0;
-    for (int t = 0; t < nsub; ++t) {
+    for (int t = 0; ok && t < nsub; ++t) {
       const int u = t & 1;
       const uint32_t t_s = tb + T_S + u * SUB + g * 16, t_t = tb + T_T + u * SUB + g * 16;
-      const float4* stats = reinterpret_cast<const float4*>(smem + OFF_Z + st * ZSTAGE_BYTES + Z_BYTES) + g * 16;
+      const float4* stats = reinterpret_cast<const float4*>(smem + z_stage_off(st) + Z_BYTES) + g * 16;
       if (!mbar_wait(&misc->s_full[u], (t >> 1) & 1, abort_flag, 1301 + g, t)) { ok = false; break; }
       tc_fence_after();
       uint32_t s[16], tt[16], ds[8];
