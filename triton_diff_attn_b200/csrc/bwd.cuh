@@ -24,7 +24,8 @@ struct BwdArgs {
   const float* lse2;
   const float* rstd;
   __half* da;           // workspace [B*H, N, 2D]
-  float4* stats;        // workspace [B*H, N] = {lse1*log2e, lse2*log2e - log2|lam|, E1, sg*E2}, sg = -sign(lam)
+  float4* stats;        // workspace, 16 bytes per row of [B*H, n_pad], NEGATED and interleaved by row pairs (see stat_row):
+                        // x = -lse1*log2e, y = -(lse2*log2e - log2|lam|), z = -E1, w = -sg*E2 with sg = -sign(lam)
   __half* dq1; __half* dq2; __half* dk1; __half* dk2; __half* dv;   // dense
   float* dlambda;
   const void* lambda_ptr;
@@ -37,7 +38,7 @@ struct BwdArgs {
   int d;                // real head dim (64, or 32 with zero-filled padding in the 64-wide tiles)
   int causal;           // 1: query row i sees key columns j <= i only
   int n_pad;            // N rounded up to 128: row pitch of `stats` per (batch, head); rows N..n_pad-1 hold
-                        // {+inf, +inf, 0, 0}, which makes the probabilities of out-of-range query rows exactly 0
+                        // x = y = -inf, z = w = 0, which makes the probabilities of out-of-range query rows exactly 0
   long long rows;       // B*H*N
   uint32_t drop_thresh; // dropout: 0 = off (see sm100.cuh); must equal the forward's
   uint32_t seed_lo, seed_hi;
@@ -48,6 +49,20 @@ struct BwdArgs {
                         // (bwd_fused64.cuh); zeroed by the preprocess kernel, converted by the finishing kernel
   long long dq_acc_f4;  // its size in float4 units
 };
+
+// Row statistics, interleaved by pairs of rows so that a kernel that walks two neighbouring rows (the key-side
+// kernels: two query columns of a thread's 16) gets each quantity of both rows in one 64-bit register pair, the
+// operand form of the packed fp32 instructions: rows 2q and 2q+1 occupy floats
+//   [8q .. 8q+8) = { x(2q), x(2q+1), y(2q), y(2q+1), z(2q), z(2q+1), w(2q), w(2q+1) }.
+// idx = (batch*head) * n_pad + row; n_pad is even, so a pair never straddles two heads.
+__device__ __forceinline__ void stat_store(float4* stats, long long idx, float4 v) {
+  float* f = reinterpret_cast<float*>(stats + (idx & ~1ll)) + (idx & 1);
+  f[0] = v.x; f[2] = v.y; f[4] = v.z; f[6] = v.w;
+}
+__device__ __forceinline__ float4 stat_row(const float4* stats, size_t idx) {
+  const float* f = reinterpret_cast<const float*>(stats + (idx & ~size_t(1))) + (idx & 1);
+  return make_float4(f[0], f[2], f[4], f[6]);
+}
 
 // ------------------------------------------------------------------------------------------------
 // 1. preprocess: one warp per row, DV = 32 * VPL halves per row
@@ -162,7 +177,8 @@ __global__ void __launch_bounds__(256) diffattn_bwd_pre_kernel(const BwdArgs arg
       // -lam P2 = sg P2' and -lam P2 (dP - E2) = P2' (sg dP - w).  lam = 0 gives y = +inf, P2' = 0.
       const float sg = lam < 0.f ? 1.f : -1.f;
       const long long bh_i = row / args.n;
-      args.stats[bh_i * args.n_pad + (row - bh_i * args.n)] = make_float4(l1r[rr] * LOG2E, l2r[rr] * LOG2E - log2f(fabsf(lam)), ea + lam * e2, sg * e2);
+      stat_store(args.stats, bh_i * args.n_pad + (row - bh_i * args.n),
+                 make_float4(-l1r[rr] * LOG2E, log2f(fabsf(lam)) - l2r[rr] * LOG2E, -(ea + lam * e2), -sg * e2));
       dl_acc -= e2;
     }
   }
@@ -191,7 +207,7 @@ __global__ void diffattn_bwd_padstats_kernel(const BwdArgs args, int bh_total) {
   const long long total = (long long)bh_total * pad;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const long long bh_i = i / pad;
-    args.stats[bh_i * args.n_pad + args.n + (i - bh_i * pad)] = make_float4(INFINITY, INFINITY, 0.f, 0.f);
+    stat_store(args.stats, bh_i * args.n_pad + args.n + (i - bh_i * pad), make_float4(-INFINITY, -INFINITY, 0.f, 0.f));
   }
 }
 
@@ -406,6 +422,7 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
     const uint32_t dcol2 = uint32_t(kv_tile * BKV + row) >> 1;
     const int dcol_odd = row & 1;
     const float dscale = DROP ? args.drop_scale : 1.f;
+    const f32x2 sl2_2 = pk2(sl2, sl2), sg_2 = pk2(sg, sg);
     bool ok = true;
     for (int i = 0; i < nq; ++i) {
       const int st = i % ST;
@@ -429,38 +446,43 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
         }
       }
       uint32_t pc[8], d1[8], d2[8];
-      float4 svb[DA_PF];                     // statistics of the next DA_PF columns (see lds_v4)
+      // statistics of the next DA_PF / 2 column pairs (see lds_v4): {x0, x1, y0, y1} and {z0, z1, w0, w1}, negated
+      float4 sva[DA_PF / 2], svb[DA_PF / 2];
 #pragma unroll
-      for (int j = 0; j < DA_PF; ++j) svb[j] = lds_v4(stats + j);
+      for (int j = 0; j < DA_PF / 2; ++j) { sva[j] = lds_v4(stats + 2 * j); svb[j] = lds_v4(stats + 2 * j + 1); }
 #pragma unroll
       for (int jj = 0; jj < 8; ++jj) {
-        float pcv[2], d1v[2], d2v[2];
-        uint32_t h1 = 0, h2 = 0;
-        if constexpr (DROP) {
-          const uint32_t drow2 = uint32_t((i0 + i) * (BQ / 2) + g * 8 + jj);
-          h1 = drop_hash(dkey1, drow2, dcol2);
-          h2 = drop_hash(dkey2, drow2, dcol2);
+        const float4 sa = sva[jj % (DA_PF / 2)], sb = svb[jj % (DA_PF / 2)];
+        if (jj + DA_PF / 2 < 8) {
+          sva[jj % (DA_PF / 2)] = lds_v4(stats + 2 * (jj + DA_PF / 2));
+          svb[jj % (DA_PF / 2)] = lds_v4(stats + 2 * (jj + DA_PF / 2) + 1);
         }
+        float x10, x11, x20, x21;
+        up2(fma2(pk2u(s1[2 * jj], s1[2 * jj + 1]), sl2_2, pk2(sa.x, sa.y)), x10, x11);
+        up2(fma2(pk2u(s2[2 * jj], s2[2 * jj + 1]), sl2_2, pk2(sa.z, sa.w)), x20, x21);
+        const float p10 = ex2(x10), p11 = ex2(x11);
+        const float p20 = ex2(x20), p21 = ex2(x21);     // |lam| P2
+        float pcv[2], d1v[2], d2v[2];
+        if constexpr (DROP) {
+          // dropped positions contribute neither to dV nor to dP; kept ones carry the factor 1/(1-p)
+          const uint32_t drow2 = uint32_t((i0 + i) * (BQ / 2) + g * 8 + jj);
+          const uint32_t h1 = drop_hash(dkey1, drow2, dcol2), h2 = drop_hash(dkey2, drow2, dcol2);
+          const float p1v[2] = {p10, p11}, p2v[2] = {p20, p21};
+          const float nz[2] = {sb.x, sb.y}, nw[2] = {sb.z, sb.w};
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int j = 2 * jj + u;
-          const float4 sv = svb[j % DA_PF];
-          if (j + DA_PF < 16) svb[j % DA_PF] = lds_v4(stats + j + DA_PF);
-          const float p1 = ex2(fmaf(__uint_as_float(s1[j]), sl2, -sv.x));
-          const float p2 = ex2(fmaf(__uint_as_float(s2[j]), sl2, -sv.y));     // |lam| P2
-          const float dpv = __uint_as_float(dp[j]);
-          if constexpr (DROP) {
-            // dropped positions contribute neither to dV nor to dP; kept ones carry the factor 1/(1-p)
+          for (int u = 0; u < 2; ++u) {
+            const float dpv = __uint_as_float(dp[2 * jj + u]);
             const float k1 = drop_keep(h1, 2 * u + dcol_odd, args.drop_thresh) ? dscale : 0.f;
             const float k2 = drop_keep(h2, 2 * u + dcol_odd, args.drop_thresh) ? sg * dscale : 0.f;
-            pcv[u] = fmaf(k2, p2, k1 * p1);
-            d1v[u] = p1 * fmaf(k1, dpv, -sv.z);
-            d2v[u] = p2 * fmaf(k2, dpv, -sv.w);
-          } else {
-            pcv[u] = fmaf(sg, p2, p1);
-            d1v[u] = p1 * (dpv - sv.z);
-            d2v[u] = p2 * fmaf(sg, dpv, -sv.w);
+            pcv[u] = fmaf(k2, p2v[u], k1 * p1v[u]);
+            d1v[u] = p1v[u] * fmaf(k1, dpv, nz[u]);
+            d2v[u] = p2v[u] * fmaf(k2, dpv, nw[u]);
           }
+        } else {
+          const f32x2 p1_2 = pk2(p10, p11), p2_2 = pk2(p20, p21), dp_2 = pk2u(dp[2 * jj], dp[2 * jj + 1]);
+          up2(fma2(sg_2, p2_2, p1_2), pcv[0], pcv[1]);
+          up2(mul2(p1_2, add2(dp_2, pk2(sb.x, sb.y))), d1v[0], d1v[1]);
+          up2(mul2(p2_2, fma2(sg_2, dp_2, pk2(sb.z, sb.w))), d2v[0], d2v[1]);
         }
         pc[jj] = pack2<BF>(pcv[0], pcv[1]);
         d1[jj] = pack2<BF>(d1v[0], d1v[1]);
@@ -715,14 +737,15 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
     const float sl2 = args.sm_scale * 1.4426950408889634f;
     const float lam = load_lambda(args.lambda_ptr, args.lambda_dtype);
     const size_t grow = size_t(bh) * args.n + size_t(q_tile) * BM + row;
-    const float4 sv = args.stats[size_t(bh) * args.n_pad + size_t(q_tile) * BM + row];
-    const float neg_l = br ? -sv.y : -sv.x;
-    const float e = br ? sv.w : sv.z;
+    const float4 sv = stat_row(args.stats, size_t(bh) * args.n_pad + size_t(q_tile) * BM + row);
+    const float neg_l = br ? sv.y : sv.x;
+    const float neg_e = br ? sv.w : sv.z;
     const float sg = (br && !(lam < 0.f)) ? -1.f : 1.f;      // branch 2: -sign(lambda) (|lambda| sits in neg_l, the sign in e)
     const uint32_t dkey = DROP ? drop_key(args.seed_lo, args.seed_hi, uint32_t(bh), uint32_t(br)) : 0u;
     const uint32_t drow2 = uint32_t(q_tile * BM + row) >> 1;
     const int drow_odd = row & 1;
     const float sgs = DROP ? sg * args.drop_scale : sg;
+    const f32x2 sl2_2 = pk2(sl2, sl2), negl_2 = pk2(neg_l, neg_l), sg_2 = pk2(sg, sg), nege_2 = pk2(neg_e, neg_e);
     bool ok = true;
     for (int t = 0; t < nsub; ++t) {
       const int u = t & 1;
@@ -748,16 +771,19 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
       }
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const float p0 = ex2(fmaf(__uint_as_float(s[2 * i]), sl2, neg_l));
-        const float p1 = ex2(fmaf(__uint_as_float(s[2 * i + 1]), sl2, neg_l));
+        float x0, x1;
+        up2(fma2(pk2u(s[2 * i], s[2 * i + 1]), sl2_2, negl_2), x0, x1);
+        const float p0 = ex2(x0), p1 = ex2(x1);
         if constexpr (DROP) {
           // dP reaches a probability only where it was kept, with the factor 1/(1-p)
           const uint32_t hh = drop_hash(dkey, drow2, uint32_t(t * (SUB / 2) + half * 16 + i));
           const float g0 = drop_keep(hh, 2 * drow_odd, args.drop_thresh) ? sgs : 0.f;
           const float g1 = drop_keep(hh, 2 * drow_odd + 1, args.drop_thresh) ? sgs : 0.f;
-          s[i] = pack2<BF>(p0 * fmaf(g0, __uint_as_float(dp[2 * i]), -e), p1 * fmaf(g1, __uint_as_float(dp[2 * i + 1]), -e));
+          s[i] = pack2<BF>(p0 * fmaf(g0, __uint_as_float(dp[2 * i]), neg_e), p1 * fmaf(g1, __uint_as_float(dp[2 * i + 1]), neg_e));
         } else {
-          s[i] = pack2<BF>(p0 * fmaf(sg, __uint_as_float(dp[2 * i]), -e), p1 * fmaf(sg, __uint_as_float(dp[2 * i + 1]), -e));
+          float r0, r1;
+          up2(mul2(pk2(p0, p1), fma2(pk2u(dp[2 * i], dp[2 * i + 1]), sg_2, nege_2)), r0, r1);
+          s[i] = pack2<BF>(r0, r1);
         }
       }
       tmem_st16(t_s, s);

@@ -183,12 +183,13 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
     const float lam = load_lambda(args.lambda_ptr, args.lambda_dtype);
     const float sg = (br && !(lam < 0.f)) ? -1.f : 1.f;      // branch 2: -sign(lambda); |lambda| is in the statistics
     const size_t grow = size_t(bh) * args.n + size_t(tile) * BM + row;
-    float neg_l = 0.f, e = 0.f;
+    float neg_l = 0.f, neg_e = 0.f;        // the statistics are stored negated (BwdArgs::stats)
     if (QSIDE) {
-      const float4 sv = args.stats[size_t(bh) * args.n_pad + size_t(tile) * BM + row];
-      neg_l = br ? -sv.y : -sv.x;
-      e = br ? sv.w : sv.z;
+      const float4 sv = stat_row(args.stats, size_t(bh) * args.n_pad + size_t(tile) * BM + row);
+      neg_l = br ? sv.y : sv.x;
+      neg_e = br ? sv.w : sv.z;
     }
+    const f32x2 sl2_2 = pk2(sl2, sl2), sg_2 = pk2(sg, sg);
     // dropout: `own` is this thread's fixed coordinate (query row on the query side, key column on the key side)
     const uint32_t dkey = DROP ? drop_key(args.seed_lo, args.seed_hi, uint32_t(bh), uint32_t(br)) : 0u;
     const uint32_t down2 = uint32_t(tile * BM + row) >> 1;
@@ -240,36 +241,37 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
             if (i < c0) s[i] = 0xff800000u;
         }
       }
-      float4 svb[DA_PF];                     // key side: statistics of the next DA_PF streamed columns
+      // key side: statistics of the next DA_PF / 2 pairs of streamed columns, {x0, x1, y0, y1} and {z0, z1, w0, w1}
+      float4 sva[DA_PF / 2], svb[DA_PF / 2];
       if (!QSIDE) {
 #pragma unroll
-        for (int j = 0; j < DA_PF; ++j) svb[j] = lds_v4(stats + j);
+        for (int j = 0; j < DA_PF / 2; ++j) { sva[j] = lds_v4(stats + 2 * j); svb[j] = lds_v4(stats + 2 * j + 1); }
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        float v[2];
-        uint32_t hh = 0;
+        f32x2 nl_2 = pk2(neg_l, neg_l), ne_2 = pk2(neg_e, neg_e);
+        if (!QSIDE) {
+          const float4 sa = sva[i % (DA_PF / 2)], sb = svb[i % (DA_PF / 2)];
+          if (i + DA_PF / 2 < 8) {
+            sva[i % (DA_PF / 2)] = lds_v4(stats + 2 * (i + DA_PF / 2));
+            svb[i % (DA_PF / 2)] = lds_v4(stats + 2 * (i + DA_PF / 2) + 1);
+          }
+          nl_2 = br ? pk2(sa.z, sa.w) : pk2(sa.x, sa.y);
+          ne_2 = br ? pk2(sb.z, sb.w) : pk2(sb.x, sb.y);
+        }
+        float x0, x1, v0, v1;
+        up2(fma2(pk2u(s[2 * i], s[2 * i + 1]), sl2_2, nl_2), x0, x1);
+        const f32x2 p_2 = pk2(ex2(x0), ex2(x1));
+        f32x2 sge_2 = sg_2;
         if constexpr (DROP) {
           // streamed index of this pair: key columns on the query side, query rows on the key side
           const uint32_t str2 = uint32_t((QSIDE ? t : t0 + t) * (SUB / 2) + g * 8 + i);
-          hh = QSIDE ? drop_hash(dkey, down2, str2) : drop_hash(dkey, str2, down2);
+          const uint32_t hh = QSIDE ? drop_hash(dkey, down2, str2) : drop_hash(dkey, str2, down2);
+          sge_2 = pk2(drop_keep(hh, QSIDE ? 2 * down_odd : down_odd, args.drop_thresh) ? sgs : 0.f,
+                      drop_keep(hh, QSIDE ? 2 * down_odd + 1 : 2 + down_odd, args.drop_thresh) ? sgs : 0.f);
         }
-#pragma unroll
-        for (int w = 0; w < 2; ++w) {
-          const int j = 2 * i + w;
-          float nl = neg_l, ee = e;
-          if (!QSIDE) {
-            const float4 sv = svb[j % DA_PF];
-            if (j + DA_PF < 16) svb[j % DA_PF] = lds_v4(stats + j + DA_PF);
-            nl = br ? -sv.y : -sv.x;
-            ee = br ? sv.w : sv.z;
-          }
-          const float p = ex2(fmaf(__uint_as_float(s[j]), sl2, nl));
-          float sge = sg;
-          if constexpr (DROP) sge = drop_keep(hh, QSIDE ? 2 * down_odd + w : 2 * w + down_odd, args.drop_thresh) ? sgs : 0.f;
-          v[w] = p * fmaf(sge, __uint_as_float(tt[j]), -ee);
-        }
-        ds[i] = pack2<BF>(v[0], v[1]);
+        up2(mul2(p_2, fma2(sge_2, pk2u(tt[2 * i], tt[2 * i + 1]), ne_2)), v0, v1);
+        ds[i] = pack2<BF>(v0, v1);
       }
       asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
                    ::"r"(t_s), "r"(ds[0]), "r"(ds[1]), "r"(ds[2]), "r"(ds[3]), "r"(ds[4]), "r"(ds[5]), "r"(ds[6]), "r"(ds[7]) : "memory");
@@ -474,6 +476,7 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
     const uint32_t dkey2 = DROP ? drop_key(args.seed_lo, args.seed_hi, uint32_t(bh), 1u) : 0u;
     const uint32_t dcol2 = uint32_t(kv_tile * BKV + row) >> 1;
     const int dcol_odd = row & 1;
+    const f32x2 sl2_2 = pk2(sl2, sl2), sg_2 = pk2(sg, sg);
     bool ok = true;
     int st = 0;
     for (int i = 0; i < nq; ++i) {
@@ -493,31 +496,29 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
             if (j < c0) { s1[j] = 0xff800000u; s2[j] = 0xff800000u; }
         }
       }
-      float4 svb[DA_PF];                     // statistics of the next DA_PF columns (see lds_v4 in bwd.cuh)
+      // {x0, x1, y0, y1} (negated) of the next DA_PF / 2 column pairs (see lds_v4 in bwd.cuh)
+      float4 sva[DA_PF / 2];
 #pragma unroll
-      for (int j = 0; j < DA_PF; ++j) svb[j] = lds_v4(stats + j);
+      for (int j = 0; j < DA_PF / 2; ++j) sva[j] = lds_v4(stats + 2 * j);
 #pragma unroll
       for (int jj = 0; jj < 8; ++jj) {
-        float v[2];
-        uint32_t h1 = 0, h2 = 0;
+        const float4 sa = sva[jj % (DA_PF / 2)];
+        if (jj + DA_PF / 2 < 8) sva[jj % (DA_PF / 2)] = lds_v4(stats + 2 * (jj + DA_PF / 2));
+        float x10, x11, x20, x21, v0, v1;
+        up2(fma2(pk2u(s1[2 * jj], s1[2 * jj + 1]), sl2_2, pk2(sa.x, sa.y)), x10, x11);
+        up2(fma2(pk2u(s2[2 * jj], s2[2 * jj + 1]), sl2_2, pk2(sa.z, sa.w)), x20, x21);
+        const f32x2 p1_2 = pk2(ex2(x10), ex2(x11)), p2_2 = pk2(ex2(x20), ex2(x21));
         if constexpr (DROP) {
           const uint32_t drow2 = uint32_t((i0 + i) * (BQ / 2) + g * 8 + jj);
-          h1 = drop_hash(dkey1, drow2, dcol2);
-          h2 = drop_hash(dkey2, drow2, dcol2);
+          const uint32_t h1 = drop_hash(dkey1, drow2, dcol2), h2 = drop_hash(dkey2, drow2, dcol2);
+          const float ds1 = args.drop_scale, ds2 = sg * args.drop_scale;
+          const f32x2 k1_2 = pk2(drop_keep(h1, dcol_odd, args.drop_thresh) ? ds1 : 0.f, drop_keep(h1, 2 + dcol_odd, args.drop_thresh) ? ds1 : 0.f);
+          const f32x2 k2_2 = pk2(drop_keep(h2, dcol_odd, args.drop_thresh) ? ds2 : 0.f, drop_keep(h2, 2 + dcol_odd, args.drop_thresh) ? ds2 : 0.f);
+          up2(fma2(k2_2, p2_2, mul2(k1_2, p1_2)), v0, v1);
+        } else {
+          up2(fma2(sg_2, p2_2, p1_2), v0, v1);
         }
-#pragma unroll
-        for (int w = 0; w < 2; ++w) {
-          const int j = 2 * jj + w;
-          const float4 sv = svb[j % DA_PF];
-          if (j + DA_PF < 16) svb[j % DA_PF] = lds_v4(stats + j + DA_PF);
-          float k1 = 1.f, k2 = sg;
-          if constexpr (DROP) {
-            k1 = drop_keep(h1, 2 * w + dcol_odd, args.drop_thresh) ? args.drop_scale : 0.f;
-            k2 = drop_keep(h2, 2 * w + dcol_odd, args.drop_thresh) ? sg * args.drop_scale : 0.f;
-          }
-          v[w] = fmaf(k2, ex2(fmaf(__uint_as_float(s2[j]), sl2, -sv.y)), k1 * ex2(fmaf(__uint_as_float(s1[j]), sl2, -sv.x)));
-        }
-        pc[jj] = pack2<BF>(v[0], v[1]);
+        pc[jj] = pack2<BF>(v0, v1);
       }
       // the single Pc tile is free once dV of the previous query tile has been accumulated
       if (i > 0) {

@@ -315,6 +315,7 @@ diffattn_bwd_fused64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __g
     const float dscale = DROP ? args.drop_scale : 1.f;
     uint8_t* const pc_row = smem + OFF_PC + row * 128;
     const int ch0 = ((g * 2) ^ (row & 7)) << 4, ch1 = ((g * 2 + 1) ^ (row & 7)) << 4;
+    const f32x2 sl2_2 = pk2(sl2, sl2), sg_2 = pk2(sg, sg);
     bool ok = true;
     for (int i = 0; i < nq; ++i) {
       const int st = i % ST;
@@ -343,38 +344,43 @@ diffattn_bwd_fused64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __g
         }
       }
       uint32_t pc[8], d1[8], d2[8];
-      float4 svb[DA_PF];                     // statistics of the next DA_PF columns (see lds_v4)
+      // statistics of the next DA_PF / 2 column pairs (see lds_v4): {x0, x1, y0, y1} and {z0, z1, w0, w1}, negated
+      float4 sva[DA_PF / 2], svb[DA_PF / 2];
 #pragma unroll
-      for (int j = 0; j < DA_PF; ++j) svb[j] = lds_v4(stats + j);
+      for (int j = 0; j < DA_PF / 2; ++j) { sva[j] = lds_v4(stats + 2 * j); svb[j] = lds_v4(stats + 2 * j + 1); }
 #pragma unroll
       for (int jj = 0; jj < 8; ++jj) {
-        float pcv[2], d1v[2], d2v[2];
-        uint32_t h1 = 0, h2 = 0;
-        if constexpr (DROP) {
-          const uint32_t drow2 = uint32_t(qt * (BQ / 2) + g * 8 + jj);
-          h1 = drop_hash(dkey1, drow2, dcol2);
-          h2 = drop_hash(dkey2, drow2, dcol2);
+        const float4 sa = sva[jj % (DA_PF / 2)], sb = svb[jj % (DA_PF / 2)];
+        if (jj + DA_PF / 2 < 8) {
+          sva[jj % (DA_PF / 2)] = lds_v4(stats + 2 * (jj + DA_PF / 2));
+          svb[jj % (DA_PF / 2)] = lds_v4(stats + 2 * (jj + DA_PF / 2) + 1);
         }
+        float x10, x11, x20, x21;
+        up2(fma2(pk2u(s1[2 * jj], s1[2 * jj + 1]), sl2_2, pk2(sa.x, sa.y)), x10, x11);
+        up2(fma2(pk2u(s2[2 * jj], s2[2 * jj + 1]), sl2_2, pk2(sa.z, sa.w)), x20, x21);
+        const float p10 = ex2(x10), p11 = ex2(x11);
+        const float p20 = ex2(x20), p21 = ex2(x21);     // |lam| P2
+        float pcv[2], d1v[2], d2v[2];
+        if constexpr (DROP) {
+          // dropped positions contribute neither to dV nor to dP; kept ones carry the factor 1/(1-p)
+          const uint32_t drow2 = uint32_t(qt * (BQ / 2) + g * 8 + jj);
+          const uint32_t h1 = drop_hash(dkey1, drow2, dcol2), h2 = drop_hash(dkey2, drow2, dcol2);
+          const float p1v[2] = {p10, p11}, p2v[2] = {p20, p21};
+          const float nz[2] = {sb.x, sb.y}, nw[2] = {sb.z, sb.w};
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int j = 2 * jj + u;
-          const float4 sv = svb[j % DA_PF];
-          if (j + DA_PF < 16) svb[j % DA_PF] = lds_v4(stats + j + DA_PF);
-          const float p1 = ex2(fmaf(__uint_as_float(s1[j]), sl2, -sv.x));
-          const float p2 = ex2(fmaf(__uint_as_float(s2[j]), sl2, -sv.y));     // |lam| P2
-          const float dpv = __uint_as_float(dp[j]);
-          if constexpr (DROP) {
-            // dropped positions contribute neither to dV nor to dP; kept ones carry the factor 1/(1-p)
+          for (int u = 0; u < 2; ++u) {
+            const float dpv = __uint_as_float(dp[2 * jj + u]);
             const float k1 = drop_keep(h1, 2 * u + dcol_odd, args.drop_thresh) ? dscale : 0.f;
             const float k2 = drop_keep(h2, 2 * u + dcol_odd, args.drop_thresh) ? sg * dscale : 0.f;
-            pcv[u] = fmaf(k2, p2, k1 * p1);
-            d1v[u] = p1 * fmaf(k1, dpv, -sv.z);
-            d2v[u] = p2 * fmaf(k2, dpv, -sv.w);
-          } else {
-            pcv[u] = fmaf(sg, p2, p1);
-            d1v[u] = p1 * (dpv - sv.z);
-            d2v[u] = p2 * fmaf(sg, dpv, -sv.w);
+            pcv[u] = fmaf(k2, p2v[u], k1 * p1v[u]);
+            d1v[u] = p1v[u] * fmaf(k1, dpv, nz[u]);
+            d2v[u] = p2v[u] * fmaf(k2, dpv, nw[u]);
           }
+        } else {
+          const f32x2 p1_2 = pk2(p10, p11), p2_2 = pk2(p20, p21), dp_2 = pk2u(dp[2 * jj], dp[2 * jj + 1]);
+          up2(fma2(sg_2, p2_2, p1_2), pcv[0], pcv[1]);
+          up2(mul2(p1_2, add2(dp_2, pk2(sb.x, sb.y))), d1v[0], d1v[1]);
+          up2(mul2(p2_2, fma2(sg_2, dp_2, pk2(sb.z, sb.w))), d2v[0], d2v[1]);
         }
         pc[jj] = pack2<BF>(pcv[0], pcv[1]);
         d1[jj] = pack2<BF>(d1v[0], d1v[1]);

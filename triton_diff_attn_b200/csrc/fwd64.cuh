@@ -202,6 +202,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
     const uint32_t t_s0 = tmem_base + lane_base + br * 128;
     const uint32_t t_o = tmem_base + lane_base + T_O + br * 128;
     const float sl2 = args.sm_scale * 1.4426950408889634f;
+    const f32x2 sl2_2 = pk2(sl2, sl2);
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     // dropout: this row's half of every 2x2 block hash, keyed by (seed, batch*head, branch)
@@ -234,7 +235,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
       // with the updated maximum after rescaling O_b and l, so P never leaves fp16 range and the final
       // normalisation stays exact.
       float neg = -m_run * sl2;
-      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+      f32x2 sum2[2] = {pk2(0.f, 0.f), pk2(0.f, 0.f)};
       float mx[4];
       uint32_t pk[SUB / 2];
 #pragma unroll
@@ -244,10 +245,10 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
 #pragma unroll
         for (int i = 0; i < SUB / 2; ++i) {
           if (i == HANDOVER_AT) { __syncwarp(); if (lane == 0) mbar_arrive(&misc->turn[br ^ 1]); }
-          const float p0 = ex2v(fmaf(__uint_as_float(sr[2 * i]), sl2, neg));
-          const float p1 = ex2v(fmaf(__uint_as_float(sr[2 * i + 1]), sl2, neg));
-          sum[(2 * i) & 3] += p0;
-          sum[(2 * i + 1) & 3] += p1;
+          float x0, x1;
+          up2(fma2(pk2u(sr[2 * i], sr[2 * i + 1]), sl2_2, pk2(neg, neg)), x0, x1);
+          const float p0 = ex2v(x0), p1 = ex2v(x1);
+          sum2[i & 1] = add2(sum2[i & 1], pk2(p0, p1));
           pk[i] = pack2<BF>(p0, p1);
           mx[i & 3] = max3(mx[i & 3], __uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]));
         }
@@ -278,18 +279,21 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
         }
         if (need) m_run = m_new;
         neg = -m_run * sl2;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) sum[c] = 0.f;
+        sum2[0] = sum2[1] = pk2(0.f, 0.f);
 #pragma unroll
         for (int i = 0; i < SUB / 2; ++i) {
-          const float p0 = ex2(fmaf(__uint_as_float(sr[2 * i]), sl2, neg));
-          const float p1 = ex2(fmaf(__uint_as_float(sr[2 * i + 1]), sl2, neg));
-          sum[(2 * i) & 3] += p0;
-          sum[(2 * i + 1) & 3] += p1;
+          float x0, x1;
+          up2(fma2(pk2u(sr[2 * i], sr[2 * i + 1]), sl2_2, pk2(neg, neg)), x0, x1);
+          const float p0 = ex2(x0), p1 = ex2(x1);
+          sum2[i & 1] = add2(sum2[i & 1], pk2(p0, p1));
           pk[i] = pack2<BF>(p0, p1);
         }
       }
-      l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);     // the softmax denominator is taken before dropout
+      {
+        float sa, sb;
+        up2(add2(sum2[0], sum2[1]), sa, sb);
+        l_run += sa + sb;
+      }     // the softmax denominator is taken before dropout
       if constexpr (DROP) {
 #pragma unroll
         for (int i = 0; i < SUB / 2; ++i)
