@@ -424,10 +424,11 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
     const float dscale = DROP ? args.drop_scale : 1.f;
     const f32x2 sl2_2 = pk2(sl2, sl2), sg_2 = pk2(sg, sg);
     bool ok = true;
+    uint32_t s_ready = 0;            // answers of the early probes (see mbar_probe)
     for (int i = 0; i < nq; ++i) {
       const int st = i % ST;
       const float4* stats = reinterpret_cast<const float4*>(smem + OFF_STAGE + st * STAGE_BYTES + 2 * Q_BYTES + DA_BYTES) + g * 16;
-      if (!mbar_wait(&misc->s_full, i & 1, abort_flag, 601 + g, i)) { ok = false; break; }
+      if (!s_ready && !mbar_wait(&misc->s_full, i & 1, abort_flag, 601 + g, i)) { ok = false; break; }
       tc_fence_after();
       uint32_t s1[16], s2[16], dp[16];
       tmem_ld16(tb + T_S1 + g * 16, s1);
@@ -488,16 +489,11 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
         d1[jj] = pack2<BF>(d1v[0], d1v[1]);
         d2[jj] = pack2<BF>(d2v[0], d2v[1]);
       }
-      // operand buffers of tile i-1 (dS^T columns, and Pc buffer of tile i-2) must have been consumed
-      if (i > 0) {
-        if (!mbar_wait(&misc->mma_done, (i - 1) & 1, abort_flag, 605 + g, i)) { ok = false; break; }
-        tc_fence_after();
-      }
-      // 8 packed columns per warpgroup: the 32x32b.x8 shape
-      asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
-                   ::"r"(tb + T_DS1 + g * 8), "r"(d1[0]), "r"(d1[1]), "r"(d1[2]), "r"(d1[3]), "r"(d1[4]), "r"(d1[5]), "r"(d1[6]), "r"(d1[7]) : "memory");
-      asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
-                   ::"r"(tb + T_DS2 + g * 8), "r"(d2[0]), "r"(d2[1]), "r"(d2[2]), "r"(d2[3]), "r"(d2[4]), "r"(d2[5]), "r"(d2[6]), "r"(d2[7]) : "memory");
+      // The dS^T columns are free once the output MMAs of tile i-1 have completed (mma_done); the Pc buffer of this
+      // tile was last read by tile i-2, whose completion the previous trip waited for.  So the Pc stores and their
+      // proxy fence go first, under the latency of an early look at mma_done (see mbar_probe).
+      static_assert(PCBUF == 2, "the Pc buffer of tile i must be the one tile i-2 used");
+      const uint32_t md_ready = i > 0 ? mbar_probe(&misc->mma_done, (i - 1) & 1) : 1u;
       // Pc tile [128 key rows][64 query columns] fp16, 128-byte rows, 16-byte chunks XOR-swizzled by row
       {
         uint8_t* prow = smem + OFF_PC + (i % PCBUF) * PC_BYTES + row * 128;
@@ -508,6 +504,16 @@ diffattn_bwd_dkdv64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gr
         }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      if (i > 0) {
+        if (!md_ready && !mbar_wait(&misc->mma_done, (i - 1) & 1, abort_flag, 605 + g, i)) { ok = false; break; }
+        tc_fence_after();
+      }
+      s_ready = i + 1 < nq ? mbar_probe(&misc->s_full, (i + 1) & 1) : 0u;
+      // 8 packed columns per warpgroup: the 32x32b.x8 shape
+      asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                   ::"r"(tb + T_DS1 + g * 8), "r"(d1[0]), "r"(d1[1]), "r"(d1[2]), "r"(d1[3]), "r"(d1[4]), "r"(d1[5]), "r"(d1[6]), "r"(d1[7]) : "memory");
+      asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                   ::"r"(tb + T_DS2 + g * 8), "r"(d2[0]), "r"(d2[1]), "r"(d2[2]), "r"(d2[3]), "r"(d2[4]), "r"(d2[5]), "r"(d2[6]), "r"(d2[7]) : "memory");
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&misc->e_done);
