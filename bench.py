@@ -52,9 +52,9 @@ SPLIT = (64, 32, 4096, 64, 1.0, 0.5, 0.8, True)                     # batch-shar
 CPU_SMALL = (2, 16, 512, 32, 1.0, 0.5, 0.8, True)                   # the CPU-runnable shape: B=2 H=16 N=512 D=32, fp32
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from an ncu capture of this workload (its summary, with
 # the command, sits under profiles/); reported only for the workload and flags of that capture.
-NCU_TRAFFIC = {"workload": DEFAULT_WORKLOAD, "source": "ncu --set full capture of the kernels of commit ec0d096, summarised under profiles/",
-               "bytes": {"diffattn_fwd64_kernel": 308.5e6, "diffattn_bwd_pre_kernel": 254.9e6,
-                         "diffattn_bwd_dkdv64_kernel": 381.1e6, "diffattn_bwd_dq64_kernel": 325.3e6}}
+NCU_TRAFFIC = {"workload": DEFAULT_WORKLOAD, "source": "ncu --set full capture of the kernels of commit 7add78a, summarised under profiles/",
+               "bytes": {"diffattn_fwd64_kernel": 311.2e6, "diffattn_bwd_pre_kernel": 255.6e6,
+                         "diffattn_bwd_dkdv64_kernel": 380.9e6, "diffattn_bwd_dq64_kernel": 325.7e6}}
 METRIC = "diff-attn fwd+bwd TFLOP/s (credited 28*B*H*N^2*D), fp16"
 NOMINAL_TFLOPS = 2250.0
 
@@ -767,10 +767,10 @@ def main():
 
     peaks = measured_peaks()
     # executed MMA flops per unit B*H*N^2*D.  D<=64: fwd 12 (S 4 + two P V 8); single-pass backward 20; two-kernel form
-    # dK/dV 16 + dQ 12 (S and dP recomputed).  D=128: fwd 16 (S in both value-column passes), dV + dK kernels 24, dQ kernel 16.
+    # dK/dV 16 + dQ 12 (S and dP recomputed).  D=128: fwd 12 (one CTA per branch, plus the combining kernel), dV + dK kernels 24, dQ kernel 16.
     unit = f_fwd / 8.0
-    tag = "128" if d == 128 else "64"
-    kernels = {f"diffattn_fwd{tag}_kernel": {"ms": ms_fwd, "credited_flops": f_fwd, "executed_mma_flops": unit * (16.0 if d == 128 else 12.0)}}
+    fwd_name = "diffattn_fwd128_branch_kernel + diffattn_fwd128_combine_kernel" if d == 128 else "diffattn_fwd64_kernel"
+    kernels = {fwd_name: {"ms": ms_fwd, "credited_flops": f_fwd, "executed_mma_flops": unit * 12.0}}
     if pr.fused:
         kernels["diffattn_bwd_pre_kernel"] = {"ms": ms_stage["preprocess"], "credited_flops": 0.0, "executed_mma_flops": 0.0}
         kernels["diffattn_bwd_fused64_kernel"] = {"ms": ms_stage["dkdv_dq_single_pass"], "credited_flops": f_bwd, "executed_mma_flops": unit * 20.0}
@@ -798,7 +798,7 @@ def main():
         "whole_step": {"achieved": value / world, "frac_of_measured_sustained": value / world / peaks["sustained"],
                        "frac_of_nominal_2250": value / world / NOMINAL_TFLOPS},
     }
-    ours_per_step = 1 + len(pr.stage_list) + (1 if d == 128 else 0)       # forward + backward kernels (D=128: dV, dK side, dQ side)
+    ours_per_step = 1 + len(pr.stage_list) + (2 if d == 128 else 0)       # forward + backward kernels (D=128: two forward kernels; dV, dK side, dQ side)
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": args.io_dtype,

@@ -308,9 +308,14 @@ int fwd_impl(const DiffAttnParams* p) {
   a.drop_scale = 256.f / float(256u - p->dropout_threshold);
   a.gain = p->gain; a.yg = static_cast<__half*>(p->y_gained);
   if (D == 128) {
-    if ((rc = set_smem(da::diffattn_fwd128_kernel<BF, DROP>, da::fwd128::SMEM_BYTES, p->device))) return rc;
-    dim3 grid128((p->N + 127) / 128, p->B * p->H);
-    da::diffattn_fwd128_kernel<BF, DROP><<<grid128, da::fwd128::NUM_THREADS, da::fwd128::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, a);
+    // one CTA per branch writes A1 (into y) and A2; the combining kernel forms y and rstd in place
+    if ((rc = set_smem(da::diffattn_fwd128_branch_kernel<BF, DROP>, da::fwd128::SMEM_BYTES, p->device))) return rc;
+    dim3 grid128((p->N + 127) / 128, p->B * p->H, 2);
+    da::diffattn_fwd128_branch_kernel<BF, DROP><<<grid128, da::fwd128::NUM_THREADS, da::fwd128::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, a);
+    DA_CUDA(cudaGetLastError());
+    const long long rows128 = (long long)p->B * p->H * p->N;
+    const int blocks128 = (int)std::min<long long>((rows128 + 7) / 8, 148ll * 16);
+    da::diffattn_fwd128_combine_kernel<BF><<<blocks128, 256, 0, stream>>>(a, rows128);
     DA_CUDA(cudaGetLastError());
     return DIFFATTN_OK;
   }
