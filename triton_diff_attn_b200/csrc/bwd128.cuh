@@ -334,7 +334,7 @@ constexpr int WARP_TMA = NWG * 4, WARP_MMA = NWG * 4 + 1;
 constexpr int T_DV = 0, T_S1 = 256, T_S2 = 384;
 struct Misc {
   uint64_t bar_kv;
-  uint64_t qfull[QST], qempty[QST], afull[AST], aempty[AST], tfull[TST], tempty[TST];
+  uint64_t qfull[QST], qempty[QST], afull[AST], aempty[AST], tempty[TST];
   uint64_t s_full[2], e_done, mma_done, acc_full;
   uint32_t tmem_slot;
   int abort_flag;
@@ -361,7 +361,7 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
   if (warp == WARP_TMA && lane == 0) {
     mbar_init(&misc->bar_kv, 1);
     for (int i = 0; i < QST; ++i) { mbar_init(&misc->qfull[i], 1); mbar_init(&misc->qempty[i], 1); }
-    for (int i = 0; i < TST; ++i) { mbar_init(&misc->tfull[i], 1); mbar_init(&misc->tempty[i], 1); }
+    for (int i = 0; i < TST; ++i) mbar_init(&misc->tempty[i], 1);
     for (int i = 0; i < AST; ++i) { mbar_init(&misc->afull[i], 1); mbar_init(&misc->aempty[i], 1); }
     for (int u = 0; u < 2; ++u) mbar_init(&misc->s_full[u], 1);
     mbar_init(&misc->e_done, NWG * 128);
@@ -388,15 +388,16 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
       for (int i = 0; i < nq; ++i) {
         uint8_t* qp = smem + OFF_QS + qs * QSTAGE_BYTES;
         uint8_t* ap = smem + OFF_DA + as * DA_BYTES;
+        // Q1, Q2 and the statistics of a tile arrive on ONE barrier (the Q ring's): every mbarrier wait costs the issuer
+        // 100-150 clocks even when the phase is complete
         if (!mbar_wait(&misc->qempty[qs], qpar, abort_flag, 1401, i)) break;
-        mbar_expect_tx(&misc->qfull[qs], QSTAGE_BYTES);
+        if (!mbar_wait(&misc->tempty[ts], tpar, abort_flag, 1403, i)) break;
+        mbar_expect_tx(&misc->qfull[qs], QSTAGE_BYTES + STAT_BYTES);
         for (int c = 0; c < 2; ++c) {
           tma_load_4d(qp + c * 8192, &tm_q1, &misc->qfull[qs], c * 64, (i0 + i) * BQ, h_idx, b_idx);
           tma_load_4d(qp + Q_BYTES + c * 8192, &tm_q2, &misc->qfull[qs], c * 64, (i0 + i) * BQ, h_idx, b_idx);
         }
-        if (!mbar_wait(&misc->tempty[ts], tpar, abort_flag, 1403, i)) break;
-        mbar_expect_tx(&misc->tfull[ts], STAT_BYTES);
-        bulk_load_1d(smem + OFF_ST + ts * STAT_BYTES, args.stats + (size_t(bh) * args.n_pad + size_t(i0 + i) * BQ), STAT_BYTES, &misc->tfull[ts]);
+        bulk_load_1d(smem + OFF_ST + ts * STAT_BYTES, args.stats + (size_t(bh) * args.n_pad + size_t(i0 + i) * BQ), STAT_BYTES, &misc->qfull[qs]);
         if (!mbar_wait(&misc->aempty[as], apar, abort_flag, 1402, i)) break;
         mbar_expect_tx(&misc->afull[as], DA_BYTES);
         for (int c = 0; c < 4; ++c) tma_load_4d(ap + c * 8192, &tm_da, &misc->afull[as], c * 64, (i0 + i) * BQ, bh, 0);
@@ -428,28 +429,25 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
       };
       bool ok = mbar_wait(&misc->bar_kv, 0, abort_flag, 1501);
       ok = ok && mbar_wait(&misc->qfull[0], 0, abort_flag, 1502);
-      ok = ok && mbar_wait(&misc->tfull[0], 0, abort_flag, 1502);
       if (ok) {
         tc_fence_after();
         issue_scores(0, 0);
         int qs = 0, as = 0, ts = 0;
-        uint32_t qpar = 0, apar = 0, tpar = 0;
+        uint32_t qpar = 0, apar = 0;
         for (int i = 0; i < nq; ++i) {
           const int u = i & 1;
           int qs_n = qs + 1;
           uint32_t qpar_n = qpar;
           if (qs_n == QST) { qs_n = 0; qpar_n ^= 1; }
           int ts_n = ts + 1;
-          uint32_t tpar_n = tpar;
-          if (ts_n == TST) { ts_n = 0; tpar_n ^= 1; }
+          if (ts_n == TST) ts_n = 0;
           if (i + 1 < nq) {
             if (!mbar_wait(&misc->qfull[qs_n], qpar_n, abort_flag, 1503, i)) break;
-            if (!mbar_wait(&misc->tfull[ts_n], tpar_n, abort_flag, 1506, i)) break;
             tc_fence_after();
             issue_scores(qs_n, u ^ 1);
           }
+          if (!mbar_wait(&misc->afull[as], apar, abort_flag, 1505, i)) break;     // long loaded: waited for under the warpgroups' pass
           if (!mbar_wait(&misc->e_done, i & 1, abort_flag, 1504, i)) break;
-          if (!mbar_wait(&misc->afull[as], apar, abort_flag, 1505, i)) break;
           tc_fence_after();
           mbar_arrive(&misc->tempty[ts]);        // the warpgroups have read the statistics of tile i (plain arrival)
 #pragma unroll
@@ -459,7 +457,7 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
           mma_commit(&misc->mma_done);
           mma_commit(&misc->aempty[as]);
           qs = qs_n; qpar = qpar_n;
-          ts = ts_n; tpar = tpar_n;
+          ts = ts_n;
           if (++as == AST) { as = 0; apar ^= 1; }
         }
         mma_commit(&misc->acc_full);
