@@ -662,7 +662,9 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
     // as in the dK/dV kernel were measured here in two forms: split by kind (S | dP | dQ, which needs a committed
     // mbarrier between the dQ and the S issuer because the score buffers are recycled on the tensor pipe's issue
     // order): 1.00 against 0.92 ms; split by branch (S_b and dQ_b | dP, which keeps that order): 0.98 ms.  Both
-    // slower: the single issuer stays.)
+    // slower: the single issuer stays.  So did two issuing warps, one per branch (S_b and dQ_b, dP of alternate sub-tiles,
+    // no barrier between the two): 0.944 against 0.912 ms -- although the elementwise warps that share a scheduler with
+    // the single issuer finish every sub-tile 130-300 clocks after the others.)
     if (elect_one()) {
       constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0, BF);    // S = Q K^T, dP = dA V^T
       const uint32_t IDESC_DQ = make_idesc(BM, args.d, 0, 1, BF);    // dQ += dS K   (K MN-major); head dim 32: 32 columns
