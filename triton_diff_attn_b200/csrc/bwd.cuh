@@ -610,7 +610,8 @@ diffattn_bwd_dq64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid
   Misc* misc = reinterpret_cast<Misc*>(smem + OFF_MISC);
   volatile int* abort_flag = &misc->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q_tile = blockIdx.x, bh = blockIdx.y;
+  // causal: the later a query tile, the more keys it sees -- the heaviest tiles are launched first so that the grid's tail is light
+  const int q_tile = args.causal ? int(gridDim.x) - 1 - int(blockIdx.x) : int(blockIdx.x), bh = blockIdx.y;
   const int b_idx = bh / args.h, h_idx = bh % args.h;
   const int nkv_all = args.n_pad / BN;
   const int nkv = (args.causal && q_tile + 1 < nkv_all) ? q_tile + 1 : nkv_all;   // causal: stop at the diagonal tile

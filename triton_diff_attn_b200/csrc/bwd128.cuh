@@ -67,7 +67,9 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
   Misc* misc = reinterpret_cast<Misc*>(smem + OFF_MISC);
   volatile int* abort_flag = &misc->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x, bh = blockIdx.y, br = blockIdx.z;
+  // causal, query side: the later a query tile, the more keys it sees -- the heaviest tiles are launched first (on the key
+  // side the first key tiles are the heaviest already)
+  const int tile = (QSIDE && args.causal) ? int(gridDim.x) - 1 - int(blockIdx.x) : int(blockIdx.x), bh = blockIdx.y, br = blockIdx.z;
   const int b_idx = bh / args.h, h_idx = bh % args.h;
   // streamed 64-row sub-tiles t0 .. t0+nsub-1 (local index t).  Causal: the query side streams keys up to its
   // diagonal tile, the key side streams queries from its diagonal tile on.

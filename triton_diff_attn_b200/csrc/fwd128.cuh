@@ -62,7 +62,8 @@ diffattn_fwd128_branch_kernel(const __grid_constant__ CUtensorMap tm_q1, const _
   Misc* misc = reinterpret_cast<Misc*>(smem + OFF_MISC);
   volatile int* abort_flag = &misc->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q_tile = blockIdx.x, bh = blockIdx.y, br = blockIdx.z;
+  // causal: the later a query tile, the more keys it sees -- the heaviest tiles are launched first so that the grid's tail is light
+  const int q_tile = args.causal ? int(gridDim.x) - 1 - int(blockIdx.x) : int(blockIdx.x), bh = blockIdx.y, br = blockIdx.z;
   const int b_idx = bh / args.h, h_idx = bh % args.h;
   const int nsub_all = ((args.n + 127) / 128) * 2;     // 64-row sub-tiles, N rounded up to 128 (TMA zero-fills)
   const int nsub = (args.causal && 2 * (q_tile + 1) < nsub_all) ? 2 * (q_tile + 1) : nsub_all;   // causal: stop at the diagonal tile

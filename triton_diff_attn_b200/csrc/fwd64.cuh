@@ -62,7 +62,8 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int q_tile = blockIdx.x;
+  // causal: the later a query tile, the more keys it sees -- the heaviest tiles are launched first so that the grid's tail is light
+  const int q_tile = args.causal ? int(gridDim.x) - 1 - int(blockIdx.x) : int(blockIdx.x);
   const int bh = blockIdx.y;
   const int b_idx = bh / args.h;
   const int h_idx = bh % args.h;
