@@ -312,32 +312,40 @@ diffattn_bwd_side128_kernel(const __grid_constant__ CUtensorMap tm_x0, const __g
 
 // ------------------------------------------------------------------------------------------------
 // dV for D = 128: one CTA = 128 key/value rows; query tiles of 64 rows stream by.
-// TMEM: dV [0,256) | S1^T two 64-column buffers [256,384) | S2^T likewise [384,512).
-// (P1 - lam P2)^T goes through one K-major shared-memory tile (A operand of dV += Pc^T dA).
+// TMEM: dV [0,256) | S1^T [256,320) | S2^T [320,384) | K1 as 16-bit pairs [384,448) | K2 [448,512).
+// K1 and K2 are copied once per CTA from their shared-memory tiles into TMEM and serve as the TMEM A operands of
+// S_b^T = K_b Q_b^T (those MMAs then read only Q_b from shared memory); their 64 KB then hold the two buffers of
+// (P1 - lam P2)^T (K-major A operand of dV += Pc^T dA) and a third stage of the Q ring.  With two Pc buffers a
+// warpgroup never waits for the dV MMAs of the tile before; the scores are single-buffered (the next tile's are issued
+// as soon as this tile's are in registers).
 // ------------------------------------------------------------------------------------------------
 namespace dv128 {
 // Three rings, by lifetime: {Q1, Q2} feed the score MMAs and are free once those have completed; the per-column
 // statistics (1 KB) are read by the warpgroups until the end of their pass; dA feeds the dV MMAs after that pass.
-constexpr int BKV = 128, BQ = 64, HD = 128, DV = 256, QST = 2, AST = 2, TST = 4, NWG = 4;
+constexpr int BKV = 128, BQ = 64, HD = 128, DV = 256, QST = 3, AST = 2, TST = 4, NWG = 4;
 constexpr int K_BYTES = BKV * HD * 2;       // 32 KB: two boxes [128 x 64]
 constexpr int Q_BYTES = BQ * HD * 2;        // 16 KB: two boxes [64 x 64]
 constexpr int DA_BYTES = BQ * DV * 2;       // 32 KB: four boxes [64 x 64]
 constexpr int STAT_BYTES = BQ * 16;
 constexpr int QSTAGE_BYTES = 2 * Q_BYTES;                          // 32 KB
 constexpr int PC_BYTES = BKV * BQ * 2;      // 16 KB
-constexpr int OFF_K1 = 0, OFF_K2 = K_BYTES, OFF_PC = 2 * K_BYTES, OFF_QS = OFF_PC + PC_BYTES;      // 80 KB
-constexpr int OFF_DA = OFF_QS + QST * QSTAGE_BYTES;                                                // 144 KB
-constexpr int OFF_ST = OFF_DA + AST * DA_BYTES;                                                    // 208 KB
-constexpr int OFF_MISC = OFF_ST + TST * STAT_BYTES;                                                // 212 KB
+constexpr int OFF_K1 = 0, OFF_K2 = K_BYTES, OFF_QS = 2 * K_BYTES;                                  // 64 KB
+constexpr int OFF_DA = OFF_QS + 2 * QSTAGE_BYTES;                                                  // 128 KB
+constexpr int OFF_ST = OFF_DA + AST * DA_BYTES;                                                    // 192 KB
+constexpr int OFF_MISC = OFF_ST + TST * STAT_BYTES;                                                // 196 KB
+// after the copy of K1, K2 into TMEM: Pc buffer b at OFF_PC + b * PC_BYTES, Q stage 2 in the second half of the K tiles
+constexpr int OFF_PC = 0;
+static_assert(QST == 3 && 2 * PC_BYTES + QSTAGE_BYTES <= 2 * K_BYTES, "Pc buffers and the third Q stage live in the K tiles");
+__host__ __device__ constexpr int q_stage_off(int s) { return s < 2 ? OFF_QS + s * QSTAGE_BYTES : 2 * PC_BYTES; }
 constexpr int MISC_BYTES = 1024;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
 constexpr int NUM_THREADS = NWG * 128 + 64;
 constexpr int WARP_TMA = NWG * 4, WARP_MMA = NWG * 4 + 1;
-constexpr int T_DV = 0, T_S1 = 256, T_S2 = 384;
+constexpr int T_DV = 0, T_S1 = 256, T_S2 = 320, T_K1 = 384, T_K2 = 448;
 struct Misc {
-  uint64_t bar_kv;
+  uint64_t bar_kv, k_ready;
   uint64_t qfull[QST], qempty[QST], afull[AST], aempty[AST], tempty[TST];
-  uint64_t s_full[2], e_done, mma_done, acc_full;
+  uint64_t s_full, s_free, e_done, mma_done[2], acc_full;
   uint32_t tmem_slot;
   int abort_flag;
 };
@@ -365,9 +373,11 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
     for (int i = 0; i < QST; ++i) { mbar_init(&misc->qfull[i], 1); mbar_init(&misc->qempty[i], 1); }
     for (int i = 0; i < TST; ++i) mbar_init(&misc->tempty[i], 1);
     for (int i = 0; i < AST; ++i) { mbar_init(&misc->afull[i], 1); mbar_init(&misc->aempty[i], 1); }
-    for (int u = 0; u < 2; ++u) mbar_init(&misc->s_full[u], 1);
+    mbar_init(&misc->k_ready, NWG * 128);
+    mbar_init(&misc->s_full, 1);
+    mbar_init(&misc->s_free, NWG * 128);
     mbar_init(&misc->e_done, NWG * 128);
-    mbar_init(&misc->mma_done, 1);
+    for (int u = 0; u < 2; ++u) mbar_init(&misc->mma_done[u], 1);
     mbar_init(&misc->acc_full, 1);
     misc->abort_flag = 0;
     mbar_init_fence();
@@ -388,8 +398,9 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
       int qs = 0, as = 0, ts = 0;
       uint32_t qpar = 1, apar = 1, tpar = 1;
       for (int i = 0; i < nq; ++i) {
-        uint8_t* qp = smem + OFF_QS + qs * QSTAGE_BYTES;
+        uint8_t* qp = smem + q_stage_off(qs);
         uint8_t* ap = smem + OFF_DA + as * DA_BYTES;
+        if (i == 2 && !mbar_wait(&misc->k_ready, 0, abort_flag, 1404, i)) break;      // Q stage 2 lies in the K tiles
         // Q1, Q2 and the statistics of a tile arrive on ONE barrier (the Q ring's): every mbarrier wait costs the issuer
         // 100-150 clocks even when the phase is complete
         if (!mbar_wait(&misc->qempty[qs], qpar, abort_flag, 1401, i)) break;
@@ -412,54 +423,51 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
     if (elect_one()) {
       constexpr uint32_t IDESC_S = make_idesc(BKV, BQ, 0, 0, BF);
       constexpr uint32_t IDESC_DV = make_idesc(BKV, DV, 0, 1, BF);     // N = 256: dA as MN-major B, four atoms 8 KB apart
-      const uint32_t k1_lo = sdesc_lo(smem_u32(smem + OFF_K1)), k2_lo = sdesc_lo(smem_u32(smem + OFF_K2));
-      const uint32_t pc_lo = sdesc_lo(smem_u32(smem + OFF_PC));
-      const uint32_t q_lo0 = sdesc_lo(smem_u32(smem + OFF_QS)), a_lo0 = sdesc_lo(smem_u32(smem + OFF_DA));
+      const uint32_t s_lo0 = sdesc_lo(smem_u32(smem));
+      const uint32_t a_lo0 = sdesc_lo(smem_u32(smem + OFF_DA));
       const uint32_t tb = tmem_base;
-      auto issue_scores = [&](int qs, int u) {
-        const uint32_t sp_lo = q_lo0 + qs * (QSTAGE_BYTES >> 4);
+      // scores of a tile from Q stage qs; Q is free once these MMAs have completed
+      auto issue_scores = [&](int qs) {
+        const uint32_t sp_lo = s_lo0 + (q_stage_off(qs) >> 4);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          mma_ss_lo(tb + T_S1 + u * BQ, k1_lo + (k / 4) * (16384 >> 4) + (k % 4) * 2, sp_lo + (k / 4) * (8192 >> 4) + (k % 4) * 2,
-                    IDESC_S, k > 0);
+          mma_ts_lo(tb + T_S1, tb + T_K1 + k * 8, sp_lo + (k / 4) * (8192 >> 4) + (k % 4) * 2, IDESC_S, k > 0);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k)
-          mma_ss_lo(tb + T_S2 + u * BQ, k2_lo + (k / 4) * (16384 >> 4) + (k % 4) * 2,
-                    sp_lo + (Q_BYTES >> 4) + (k / 4) * (8192 >> 4) + (k % 4) * 2, IDESC_S, k > 0);
-        mma_commit(&misc->s_full[u]);          // (the statistics of the tile were waited for before: s_full implies them)
+          mma_ts_lo(tb + T_S2, tb + T_K2 + k * 8, sp_lo + (Q_BYTES >> 4) + (k / 4) * (8192 >> 4) + (k % 4) * 2, IDESC_S, k > 0);
+        mma_commit(&misc->s_full);             // (the statistics of the tile arrived with Q: s_full implies them)
         mma_commit(&misc->qempty[qs]);
       };
-      bool ok = mbar_wait(&misc->bar_kv, 0, abort_flag, 1501);
+      bool ok = mbar_wait(&misc->k_ready, 0, abort_flag, 1501);
       ok = ok && mbar_wait(&misc->qfull[0], 0, abort_flag, 1502);
       if (ok) {
         tc_fence_after();
-        issue_scores(0, 0);
+        issue_scores(0);
         int qs = 0, as = 0, ts = 0;
         uint32_t qpar = 0, apar = 0;
         for (int i = 0; i < nq; ++i) {
-          const int u = i & 1;
           int qs_n = qs + 1;
           uint32_t qpar_n = qpar;
           if (qs_n == QST) { qs_n = 0; qpar_n ^= 1; }
-          int ts_n = ts + 1;
-          if (ts_n == TST) ts_n = 0;
           if (i + 1 < nq) {
             if (!mbar_wait(&misc->qfull[qs_n], qpar_n, abort_flag, 1503, i)) break;
+            if (!mbar_wait(&misc->s_free, i & 1, abort_flag, 1506, i)) break;       // the scores of tile i are in registers
             tc_fence_after();
-            issue_scores(qs_n, u ^ 1);
+            issue_scores(qs_n);
           }
           if (!mbar_wait(&misc->afull[as], apar, abort_flag, 1505, i)) break;     // long loaded: waited for under the warpgroups' pass
           if (!mbar_wait(&misc->e_done, i & 1, abort_flag, 1504, i)) break;
           tc_fence_after();
           mbar_arrive(&misc->tempty[ts]);        // the warpgroups have read the statistics of tile i (plain arrival)
+          const uint32_t pc_lo = s_lo0 + ((OFF_PC + (i & 1) * PC_BYTES) >> 4);
 #pragma unroll
           for (int k = 0; k < BQ / 16; ++k)
             mma_ss_lo(tb + T_DV, pc_lo + k * 2, a_lo0 + as * (DA_BYTES >> 4) + ((8192u >> 4) << 16) - (1u << 16) + k * (2048 >> 4),
                       IDESC_DV, (i > 0 || k > 0));
-          mma_commit(&misc->mma_done);
+          mma_commit(&misc->mma_done[i & 1]);
           mma_commit(&misc->aempty[as]);
           qs = qs_n; qpar = qpar_n;
-          ts = ts_n;
+          if (++ts == TST) ts = 0;
           if (++as == AST) { as = 0; apar ^= 1; }
         }
         mma_commit(&misc->acc_full);
@@ -477,17 +485,33 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
     const uint32_t dcol2 = uint32_t(kv_tile * BKV + row) >> 1;
     const int dcol_odd = row & 1;
     const f32x2 sl2_2 = pk2(sl2, sl2), sg_2 = pk2(sg, sg);
-    bool ok = true;
+    bool ok = mbar_wait(&misc->bar_kv, 0, abort_flag, 1600 + g);
+    {
+      // K1, K2 into TMEM: this thread's row, the 64 columns of box g (K1 low, K1 high, K2 low, K2 high: 128 bytes,
+      // swizzled in 16-byte chunks) -> 32 columns
+      uint32_t kv[32];
+      const uint8_t* krow = smem + OFF_K1 + g * 16384 + row * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint4 v = *reinterpret_cast<const uint4*>(krow + ((c ^ (row & 7)) << 4));
+        kv[4 * c] = v.x; kv[4 * c + 1] = v.y; kv[4 * c + 2] = v.z; kv[4 * c + 3] = v.w;
+      }
+      tmem_st32(tb + T_K1 + g * 32, kv);
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&misc->k_ready);
+    }
     int st = 0;
-    for (int i = 0; i < nq; ++i) {
-      const int u = i & 1;
+    for (int i = 0; ok && i < nq; ++i) {
       const float4* stats = reinterpret_cast<const float4*>(smem + OFF_ST + st * STAT_BYTES) + g * 16;
-      if (!mbar_wait(&misc->s_full[u], (i >> 1) & 1, abort_flag, 1601 + g, i)) { ok = false; break; }
+      if (!mbar_wait(&misc->s_full, i & 1, abort_flag, 1601 + g, i)) { ok = false; break; }
       tc_fence_after();
       uint32_t s1[16], s2[16], pc[8];
-      tmem_ld16(tb + T_S1 + u * BQ + g * 16, s1);
-      tmem_ld16(tb + T_S2 + u * BQ + g * 16, s2);
+      tmem_ld16(tb + T_S1 + g * 16, s1);
+      tmem_ld16(tb + T_S2 + g * 16, s2);
       tc_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&misc->s_free);
       if (args.causal) {
         const int c0 = kv_tile * BKV + row - ((i0 + i) * BQ + g * 16);   // hidden query columns left of the diagonal
         if (c0 > 0) {
@@ -520,12 +544,12 @@ diffattn_bwd_dv128_kernel(const __grid_constant__ CUtensorMap tm_q1, const __gri
         }
         pc[jj] = pack2<BF>(v0, v1);
       }
-      // the single Pc tile is free once dV of the previous query tile has been accumulated
-      if (i > 0) {
-        if (!mbar_wait(&misc->mma_done, (i - 1) & 1, abort_flag, 1605 + g, i)) { ok = false; break; }
+      // Pc buffer i & 1 is free once dV of tile i-2 has been accumulated (long ago, as a rule)
+      if (i > 1) {
+        if (!mbar_wait(&misc->mma_done[i & 1], ((i >> 1) - 1) & 1, abort_flag, 1605 + g, i)) { ok = false; break; }
       }
       {
-        uint8_t* prow = smem + OFF_PC + row * 128;
+        uint8_t* prow = smem + OFF_PC + (i & 1) * PC_BYTES + row * 128;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           const int chunk = (g * 2 + c) ^ (row & 7);
