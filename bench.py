@@ -767,9 +767,9 @@ def main():
 
     peaks = measured_peaks()
     # executed MMA flops per unit B*H*N^2*D.  D<=64: fwd 12 (S 4 + two P V 8); single-pass backward 20; two-kernel form
-    # dK/dV 16 + dQ 12 (S and dP recomputed).  D=128: fwd 12 (one CTA per branch, plus the combining kernel), dV + dK kernels 24, dQ kernel 16.
+    # dK/dV 16 + dQ 12 (S and dP recomputed).  D=128: fwd 12 (one CTA per branch, clusters of two), dV + dK kernels 24, dQ kernel 16.
     unit = f_fwd / 8.0
-    fwd_name = "diffattn_fwd128_branch_kernel + diffattn_fwd128_combine_kernel" if d == 128 else "diffattn_fwd64_kernel"
+    fwd_name = "diffattn_fwd128_branch_kernel" if d == 128 else "diffattn_fwd64_kernel"
     kernels = {fwd_name: {"ms": ms_fwd, "credited_flops": f_fwd, "executed_mma_flops": unit * 12.0}}
     if pr.fused:
         kernels["diffattn_bwd_pre_kernel"] = {"ms": ms_stage["preprocess"], "credited_flops": 0.0, "executed_mma_flops": 0.0}
@@ -798,7 +798,7 @@ def main():
         "whole_step": {"achieved": value / world, "frac_of_measured_sustained": value / world / peaks["sustained"],
                        "frac_of_nominal_2250": value / world / NOMINAL_TFLOPS},
     }
-    ours_per_step = 1 + len(pr.stage_list) + (2 if d == 128 else 0)       # forward + backward kernels (D=128: two forward kernels; dV, dK side, dQ side)
+    ours_per_step = 1 + len(pr.stage_list) + (1 if d == 128 else 0)       # forward + backward kernels (D=128: dV, dK side, dQ side)
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": args.io_dtype,

@@ -100,8 +100,7 @@ typedef struct DiffAttnParams {
 
 /* Forward.  Reads q1,q2,k1,k2,v,lambda_scale; writes y,a2,lse1,lse2,rstd.
  * Replaces _diff_attention.forward + diff_attn_fwd (reference src/kernel.py:463-514, :21-207).
- * One kernel at head dim <= 64; two at head dim 128 (one CTA per branch, then a combining kernel: between
- * the two, y holds the first branch's output, so y is complete only when the stream has run both). */
+ * One kernel at every head dim; at head dim 128 its CTAs run in clusters of two (one per branch). */
 int diffattn_fwd(const DiffAttnParams* p);
 
 /* Backward.  Reads the forward's inputs and outputs plus dy; writes dq1,dq2,dk1,dk2,dv and adds the

@@ -308,15 +308,19 @@ int fwd_impl(const DiffAttnParams* p) {
   a.drop_scale = 256.f / float(256u - p->dropout_threshold);
   a.gain = p->gain; a.yg = static_cast<__half*>(p->y_gained);
   if (D == 128) {
-    // one CTA per branch writes A1 (into y) and A2; the combining kernel forms y and rstd in place
+    // one CTA per branch; the two CTAs of a query tile form a cluster and exchange A2 through distributed shared memory
     if ((rc = set_smem(da::diffattn_fwd128_branch_kernel<BF, DROP>, da::fwd128::SMEM_BYTES, p->device))) return rc;
-    dim3 grid128((p->N + 127) / 128, p->B * p->H, 2);
-    da::diffattn_fwd128_branch_kernel<BF, DROP><<<grid128, da::fwd128::NUM_THREADS, da::fwd128::SMEM_BYTES, stream>>>(mq1, mq2, mk1, mk2, mv, a);
-    DA_CUDA(cudaGetLastError());
-    const long long rows128 = (long long)p->B * p->H * p->N;
-    const int blocks128 = (int)std::min<long long>((rows128 + 7) / 8, 148ll * 16);
-    da::diffattn_fwd128_combine_kernel<BF><<<blocks128, 256, 0, stream>>>(a, rows128);
-    DA_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((p->N + 127) / 128, p->B * p->H, 2);
+    cfg.blockDim = dim3(da::fwd128::NUM_THREADS);
+    cfg.dynamicSmemBytes = da::fwd128::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 2;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    DA_CUDA(cudaLaunchKernelEx(&cfg, da::diffattn_fwd128_branch_kernel<BF, DROP>, mq1, mq2, mk1, mk2, mv, a));
     return DIFFATTN_OK;
   }
   // outputs leave through TMA stores: dense [B*H, N, 2D] maps with 128-row boxes

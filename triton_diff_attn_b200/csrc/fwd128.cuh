@@ -1,14 +1,18 @@
 // Differential-attention forward for head dim D = 128 (value width 256), sm_100a.
 //
-// Two 256-wide accumulators do not fit in TMEM next to the score buffers, so the two branches run in different CTAs
-// (blockIdx.z) and a small second kernel combines them.  Same softmax scheme as the D <= 64 kernel (fwd.cuh,
-// fwd64.cuh): scores in two alternating 64-column TMEM buffers, one exp pass per sub-tile against the stale running
-// maximum, P written over its scores as the TMEM A operand of P V.  Streamed tiles are 64 rows: {K_b, V}.
+// Two 256-wide accumulators do not fit in TMEM next to the score buffers, so the two branches run in the two CTAs of a
+// thread-block cluster (blockIdx.z = branch).  Same softmax scheme as the D <= 64 kernel (fwd.cuh, fwd64.cuh): scores
+// in two alternating 64-column TMEM buffers, one exp pass per sub-tile against the stale running maximum, P written
+// over its scores as the TMEM A operand of P V.  Streamed tiles are 64 rows: {K_b, V}.  At the end branch 2 hands its
+// A2 = O_2 / l_2 in fp32 to branch 1 through distributed shared memory, and branch 1 forms y and rstd.
 // (An earlier form kept both branches in one CTA and made two passes over the keys, one per 128-column half of V, with
 // the probabilities recomputed in the second: 16 units of B*H*N^2*D and 4 N^2 exponentials per head; it measured
-// 1.97 ms against 1.38 ms for this form at B2 H8 N8192 D128.  The same one-branch-per-CTA form at head dim 64 -- S and O
-// take 256 TMEM columns and 90 KB of shared memory, so two CTAs share an SM -- measured 0.84 ms against 0.81 ms for the
-// D <= 64 kernel of fwd64.cuh at B4 H16 N4096 D64: there nothing is computed twice to begin with.)
+// 1.97 ms against 1.4 ms for this form at B2 H8 N8192 D128.  A form without the cluster -- branch 1 writes A1 as 16-bit
+// values into y, a second kernel combines -- was as fast but lost accuracy where A1 - lambda A2 cancels: with bf16
+// tensors, lambda 0.8, a causal mask and rms_norm two of 400 seeded cases left the tolerance.  The same
+// one-branch-per-CTA form at head dim 64 -- S and O take 256 TMEM columns and 90 KB of shared memory, so two CTAs share
+// an SM -- measured 0.84 ms against 0.81 ms for the D <= 64 kernel of fwd64.cuh at B4 H16 N4096 D64: there nothing is
+// computed twice to begin with.)
 #pragma once
 #include "fwd.cuh"
 #include "sm100.cuh"
@@ -16,11 +20,9 @@
 namespace da {
 
 // ------------------------------------------------------------------------------------------------
-// One branch per CTA (blockIdx.z), one pass: with a single branch the whole 256-wide accumulator fits in TMEM next to
-// the score buffers, so nothing is computed twice (12 units of B*H*N^2*D and 2 N^2 exponentials per head).
-// The CTA of branch 1 writes A1 = P1 V as 16-bit values into y, the CTA of
-// branch 2 writes A2 = P2 V into a2 (its final place); diffattn_fwd128_combine_kernel then forms
-// y = RMSNorm(A1 - lambda A2) (1 - lambda_init) in place and writes rstd.
+// One branch per CTA (blockIdx.z; the two CTAs of a query tile are one cluster), one pass: with a single branch the
+// whole 256-wide accumulator fits in TMEM next to the score buffers, so nothing is computed twice (12 units of
+// B*H*N^2*D and 2 N^2 exponentials per head).
 // TMEM: S two 64-column buffers [0,128) | O [128,384).  Warps 0-3 softmax (thread = query row), 4 TMA, 5 MMA issuer.
 // ------------------------------------------------------------------------------------------------
 namespace fwd128 {
@@ -45,6 +47,7 @@ struct Misc {
   uint64_t full[ST], empty[ST];
   uint64_t s_full[2], p_full[2];
   uint64_t o_done, o_full;
+  uint64_t peer_ready, peer_data;     // arrivals come from the partner CTA of the cluster (the other branch)
   uint32_t tmem_slot;
   int abort_flag;
 };
@@ -76,12 +79,15 @@ diffattn_fwd128_branch_kernel(const __grid_constant__ CUtensorMap tm_q1, const _
     for (int u = 0; u < 2; ++u) { mbar_init(&misc->s_full[u], 1); mbar_init(&misc->p_full[u], 128); }
     mbar_init(&misc->o_done, 1);
     mbar_init(&misc->o_full, 1);
+    mbar_init(&misc->peer_ready, 1);
+    mbar_init(&misc->peer_data, 128);
     misc->abort_flag = 0;
     mbar_init_fence();
   }
   if (warp == WARP_MMA) tmem_alloc(&misc->tmem_slot, 512);
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();          // the partner's mbarriers are initialised before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&misc->tmem_slot);
 
@@ -244,78 +250,110 @@ diffattn_fwd128_branch_kernel(const __grid_constant__ CUtensorMap tm_q1, const _
       mbar_arrive(&misc->p_full[t & 1]);
     }
 
-    // ---- epilogue: A_b = O_b / l_b as 16-bit values; every thread runs every barrier
-    ok = ok && mbar_wait(&misc->o_full, 0, abort_flag, 2311 + br);
+    // ---- epilogue.  The two CTAs of a cluster hold A1 = O_1 / l_1 (branch 1) and A2 = O_2 / l_2 (branch 2) of the same 128
+    // query rows.  Branch 2 writes a2 and hands its A2 in fp32 to branch 1 through distributed shared memory (into branch
+    // 1's key/value ring, idle by then); branch 1 forms y = RMSNorm(A1 - lambda A2) (1 - lambda_init) and rstd.
+    // Every thread runs every barrier; only the global writes depend on `ok`.
+    ok = mbar_wait(&misc->o_full, 0, abort_flag, 2311 + br) && ok;
     tc_fence_after();
     const float inv_l = (DROP ? args.drop_scale : 1.f) / l_run;
     const bool live = ok && !*abort_flag && (q_tile * BM + row < args.n);
-    __half* dst = (br ? args.a2 : args.y) + grow * DV;
+    // exchange tile: 64 chunks of four floats per row, chunk-major (chunk c of row r at (c * 128 + r) * 16 bytes), so that
+    // the 32 rows of a warp touch consecutive 16-byte words
+    uint8_t* xtile = smem + OFF_STAGE;
+    if (br == 1) {
+      const uint32_t x_remote = cluster_map(smem_u32(xtile), 0);
+      ok = mbar_wait_cluster(&misc->peer_ready, 0, abort_flag, 2313) && ok;       // branch 1's ring is idle
+      __half* dst = args.a2 + grow * DV;
 #pragma unroll
-    for (int c = 0; c < DV / 32; ++c) {
-      uint32_t o[32];
-      tmem_ld32(t_o + c * 32, o);
-      tc_wait_ld();
-      if (live) {
+      for (int c = 0; c < DV / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(t_o + c * 32, o);
+        tc_wait_ld();
+        float f[32];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint4 v;
-          v.x = pack2<BF>(__uint_as_float(o[8 * i + 0]) * inv_l, __uint_as_float(o[8 * i + 1]) * inv_l);
-          v.y = pack2<BF>(__uint_as_float(o[8 * i + 2]) * inv_l, __uint_as_float(o[8 * i + 3]) * inv_l);
-          v.z = pack2<BF>(__uint_as_float(o[8 * i + 4]) * inv_l, __uint_as_float(o[8 * i + 5]) * inv_l);
-          v.w = pack2<BF>(__uint_as_float(o[8 * i + 6]) * inv_l, __uint_as_float(o[8 * i + 7]) * inv_l);
-          *reinterpret_cast<uint4*>(dst + c * 32 + 8 * i) = v;
+        for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(o[i]) * inv_l;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          cluster_st_v4(x_remote + uint32_t(((c * 8 + i) * BM + row) * 16), f[4 * i], f[4 * i + 1], f[4 * i + 2], f[4 * i + 3]);
+        if (live) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            *reinterpret_cast<uint4*>(dst + c * 32 + 8 * i) =
+                make_uint4(pack2<BF>(f[8 * i + 0], f[8 * i + 1]), pack2<BF>(f[8 * i + 2], f[8 * i + 3]),
+                           pack2<BF>(f[8 * i + 4], f[8 * i + 5]), pack2<BF>(f[8 * i + 6], f[8 * i + 7]));
         }
       }
+      cluster_mbar_arrive(cluster_map(smem_u32(&misc->peer_data), 0));
+      if (live) args.lse2[grow] = m_run * args.sm_scale + logf(l_run);
+    } else {
+      if (threadIdx.x == 0) cluster_mbar_arrive(cluster_map(smem_u32(&misc->peer_ready), 1));
+      const float lam = load_lambda(args.lambda_ptr, args.lambda_dtype);
+      ok = mbar_wait_cluster(&misc->peer_data, 0, abort_flag, 2314) && ok;
+      const bool live0 = live && ok && !*abort_flag;
+      const float4* xrow = reinterpret_cast<const float4*>(xtile) + row;
+      // first pass: sum of squares of A = A1 - lambda A2 (the accumulator and the exchange tile are read again below)
+      float ssq = 0.f;
+#pragma unroll
+      for (int c = 0; c < DV / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(t_o + c * 32, o);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 z = xrow[(c * 8 + i) * BM];
+          const float a0 = __uint_as_float(o[4 * i + 0]) * inv_l - lam * z.x, a1 = __uint_as_float(o[4 * i + 1]) * inv_l - lam * z.y;
+          const float a2 = __uint_as_float(o[4 * i + 2]) * inv_l - lam * z.z, a3 = __uint_as_float(o[4 * i + 3]) * inv_l - lam * z.w;
+          ssq += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
+        }
+      }
+      const float rstd = rsqrtf(ssq * (1.f / DV) + args.eps);
+      const float ys = args.rms_norm ? args.out_scale * rstd : 1.f;
+#pragma unroll
+      for (int c = 0; c < DV / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(t_o + c * 32, o);
+        tc_wait_ld();
+        float f[32];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 z = xrow[(c * 8 + i) * BM];
+          f[4 * i + 0] = (__uint_as_float(o[4 * i + 0]) * inv_l - lam * z.x) * ys;
+          f[4 * i + 1] = (__uint_as_float(o[4 * i + 1]) * inv_l - lam * z.y) * ys;
+          f[4 * i + 2] = (__uint_as_float(o[4 * i + 2]) * inv_l - lam * z.z) * ys;
+          f[4 * i + 3] = (__uint_as_float(o[4 * i + 3]) * inv_l - lam * z.w) * ys;
+        }
+        if (live0) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int col = c * 32 + 8 * i;
+            *reinterpret_cast<uint4*>(args.y + grow * DV + col) =
+                make_uint4(pack2<BF>(f[8 * i + 0], f[8 * i + 1]), pack2<BF>(f[8 * i + 2], f[8 * i + 3]),
+                           pack2<BF>(f[8 * i + 4], f[8 * i + 5]), pack2<BF>(f[8 * i + 6], f[8 * i + 7]));
+            if (args.gain) {
+              const float4 g0 = __ldg(reinterpret_cast<const float4*>(args.gain + col));
+              const float4 g1 = __ldg(reinterpret_cast<const float4*>(args.gain + col + 4));
+              *reinterpret_cast<uint4*>(args.yg + grow * DV + col) =
+                  make_uint4(pack2<BF>(f[8 * i + 0] * g0.x, f[8 * i + 1] * g0.y), pack2<BF>(f[8 * i + 2] * g0.z, f[8 * i + 3] * g0.w),
+                             pack2<BF>(f[8 * i + 4] * g1.x, f[8 * i + 5] * g1.y), pack2<BF>(f[8 * i + 6] * g1.z, f[8 * i + 7] * g1.w));
+            }
+          }
+        }
+      }
+      if (live0) {
+        args.lse1[grow] = m_run * args.sm_scale + logf(l_run);
+        args.rstd[grow] = rstd;
+      }
     }
-    if (live) (br ? args.lse2 : args.lse1)[grow] = m_run * args.sm_scale + logf(l_run);
   }
 
+  // neither CTA leaves while its partner may still arrive on its barriers or write into its shared memory
+  cluster_sync_all();
   tc_fence_before();
   __syncthreads();
   if (warp == WARP_MMA) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
-  }
-}
-
-// y (holding A1) and a2 -> y = RMSNorm(A1 - lambda A2) (1 - lambda_init), rstd; one warp per row, 8 columns per lane.
-template <bool BF>
-__global__ void __launch_bounds__(256) diffattn_fwd128_combine_kernel(const FwdArgs args, long long rows) {
-  constexpr int DV = 256;
-  const int lane = threadIdx.x & 31;
-  const float lam = load_lambda(args.lambda_ptr, args.lambda_dtype);
-  const long long warp0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
-  for (long long row = warp0; row < rows; row += nwarps) {
-    const size_t off = size_t(row) * DV + lane * 8;
-    const uint4 u1 = *reinterpret_cast<const uint4*>(args.y + off);
-    const uint4 u2 = *reinterpret_cast<const uint4*>(args.a2 + off);
-    const uint32_t w1[4] = {u1.x, u1.y, u1.z, u1.w}, w2[4] = {u2.x, u2.y, u2.z, u2.w};
-    float a[8];
-    float ssq = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 x = unpack2<BF>(w1[i]), z = unpack2<BF>(w2[i]);
-      a[2 * i] = x.x - lam * z.x;
-      a[2 * i + 1] = x.y - lam * z.y;
-      ssq += a[2 * i] * a[2 * i] + a[2 * i + 1] * a[2 * i + 1];
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
-    const float rstd = rsqrtf(ssq * (1.f / DV) + args.eps);
-    const float ys = args.rms_norm ? args.out_scale * rstd : 1.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) a[i] *= ys;
-    *reinterpret_cast<uint4*>(args.y + off) =
-        make_uint4(pack2<BF>(a[0], a[1]), pack2<BF>(a[2], a[3]), pack2<BF>(a[4], a[5]), pack2<BF>(a[6], a[7]));
-    if (args.gain) {
-      const float4 g0 = __ldg(reinterpret_cast<const float4*>(args.gain + lane * 8));
-      const float4 g1 = __ldg(reinterpret_cast<const float4*>(args.gain + lane * 8 + 4));
-      *reinterpret_cast<uint4*>(args.yg + off) =
-          make_uint4(pack2<BF>(a[0] * g0.x, a[1] * g0.y), pack2<BF>(a[2] * g0.z, a[3] * g0.w),
-                     pack2<BF>(a[4] * g1.x, a[5] * g1.y), pack2<BF>(a[6] * g1.z, a[7] * g1.w));
-    }
-    if (lane == 0) args.rstd[row] = rstd;
   }
 }
 

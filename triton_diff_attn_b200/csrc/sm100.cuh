@@ -128,6 +128,57 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, v
   return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, site, iter));
 }
 
+// ---------------------------------- thread-block clusters ----------------------------------
+// The partner CTA's shared memory (distributed shared memory): a local shared-memory address mapped into CTA `rank`.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local_smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_st_v4(uint32_t remote_addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote_addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+// arrival on an mbarrier of the partner CTA; releases this thread's earlier writes (to either CTA) at cluster scope
+__device__ __forceinline__ void cluster_mbar_arrive(uint32_t remote_bar_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar_addr) : "memory");
+}
+// whole cluster: every thread of both CTAs arrives, then waits (like __syncthreads over the cluster)
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Bounded wait on a LOCAL mbarrier whose arrivals come from the partner CTA: acquire at cluster scope, so that the
+// partner's distributed-shared-memory writes before its arrival are visible afterwards.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int site, int iter = 0) {
+  unsigned long long t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
+        : "memory");
+    if (ok) return true;
+    if ((++spins & 0xff) == 0) {
+      if (*abort_flag) return false;
+      unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        if (atomicCAS(&g_status[0], 0, site) == 0) {
+          g_status[1] = blockIdx.x;
+          g_status[2] = blockIdx.y;
+          g_status[3] = iter;
+        }
+        return false;
+      }
+    }
+  }
+}
+
 // named barrier among `nthreads` threads of the CTA (id 1..15; 0 is __syncthreads)
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
