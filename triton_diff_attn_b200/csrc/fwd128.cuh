@@ -292,10 +292,12 @@ diffattn_fwd128_branch_kernel(const __grid_constant__ CUtensorMap tm_q1, const _
       ok = mbar_wait_cluster(&misc->peer_data, 0, abort_flag, 2314) && ok;
       const bool live0 = live && ok && !*abort_flag;
       const float4* xrow = reinterpret_cast<const float4*>(xtile) + row;
-      // first pass: sum of squares of A = A1 - lambda A2 (the accumulator and the exchange tile are read again below)
+      // first pass: sum of squares of A = A1 - lambda A2 (the accumulator and the exchange tile are read again below);
+      // without rms_norm only rstd needs it, and it is gathered in the second pass
       float ssq = 0.f;
 #pragma unroll
       for (int c = 0; c < DV / 32; ++c) {
+        if (!args.rms_norm) break;
         uint32_t o[32];
         tmem_ld32(t_o + c * 32, o);
         tc_wait_ld();
@@ -307,8 +309,8 @@ diffattn_fwd128_branch_kernel(const __grid_constant__ CUtensorMap tm_q1, const _
           ssq += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
         }
       }
-      const float rstd = rsqrtf(ssq * (1.f / DV) + args.eps);
-      const float ys = args.rms_norm ? args.out_scale * rstd : 1.f;
+      const float ys = args.rms_norm ? args.out_scale * rsqrtf(ssq * (1.f / DV) + args.eps) : 1.f;
+      float ssq2 = 0.f;
 #pragma unroll
       for (int c = 0; c < DV / 32; ++c) {
         uint32_t o[32];
@@ -318,10 +320,10 @@ diffattn_fwd128_branch_kernel(const __grid_constant__ CUtensorMap tm_q1, const _
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const float4 z = xrow[(c * 8 + i) * BM];
-          f[4 * i + 0] = (__uint_as_float(o[4 * i + 0]) * inv_l - lam * z.x) * ys;
-          f[4 * i + 1] = (__uint_as_float(o[4 * i + 1]) * inv_l - lam * z.y) * ys;
-          f[4 * i + 2] = (__uint_as_float(o[4 * i + 2]) * inv_l - lam * z.z) * ys;
-          f[4 * i + 3] = (__uint_as_float(o[4 * i + 3]) * inv_l - lam * z.w) * ys;
+          const float a0 = __uint_as_float(o[4 * i + 0]) * inv_l - lam * z.x, a1 = __uint_as_float(o[4 * i + 1]) * inv_l - lam * z.y;
+          const float a2 = __uint_as_float(o[4 * i + 2]) * inv_l - lam * z.z, a3 = __uint_as_float(o[4 * i + 3]) * inv_l - lam * z.w;
+          ssq2 += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
+          f[4 * i + 0] = a0 * ys; f[4 * i + 1] = a1 * ys; f[4 * i + 2] = a2 * ys; f[4 * i + 3] = a3 * ys;
         }
         if (live0) {
 #pragma unroll
@@ -342,7 +344,7 @@ diffattn_fwd128_branch_kernel(const __grid_constant__ CUtensorMap tm_q1, const _
       }
       if (live0) {
         args.lse1[grow] = m_run * args.sm_scale + logf(l_run);
-        args.rstd[grow] = rstd;
+        args.rstd[grow] = rsqrtf(ssq2 * (1.f / DV) + args.eps);
       }
     }
   }
