@@ -18,8 +18,10 @@ namespace da {
 namespace fwd64 {
 constexpr int MISC_BYTES = 4096;
 constexpr int SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024; // +1024 for manual alignment
-// warps 0-7 softmax (branch = warp >> 2, thread = query row); 8 TMA producer; 9 S issuer (both branches); 10, 11 P V
-// issuers of branch 1, 2: one role warp per scheduler (warp % 4).  Twelve warps, three per scheduler, are launched
+// warps 0-7 softmax (branch = warp >> 2, thread = query row); 8 TMA producer; 9 allocates TMEM and is otherwise idle;
+// 10, 11 MMA issuers of branch 1, 2 (S_b and P_b V: S_b of sub-tile t+2 is issued right behind P_b V of sub-tile t, in the
+// same thread's issue order -- with a separate S issuer a completion barrier and that warp's wake-up sat between the
+// two: 0.804 -> 0.787 ms at B4 H16 N4096 D64): one role warp per scheduler (warp % 4).  Twelve warps, three per scheduler, are launched
 // with 168 registers per thread; the role warpgroup then hands registers to the softmax warpgroups (setmaxnreg),
 // which hold a whole 64-column sub-tile of scores plus its packed probabilities per thread.  Per scheduler up to
 // 2 x 224 + 56 = 3 x 168 are available; measured at B4 H16 N4096 D64, 224 (no spill) and 200 run 5 % slower than 184
@@ -80,7 +82,7 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
 
   if (warp == WARP_TMA && lane == 0) {
     mbar_init(&misc->bar_q, 1);
-    for (int i = 0; i < KS; ++i) { mbar_init(&misc->k_full[i], 1); mbar_init(&misc->k_empty[i], 1); }
+        for (int i = 0; i < KS; ++i) { mbar_init(&misc->k_full[i], 1); mbar_init(&misc->k_empty[i], 2); }
     for (int i = 0; i < VS; ++i) { mbar_init(&misc->v_full[i], 1); mbar_init(&misc->v_empty[i], 2); }
     for (int b = 0; b < 2; ++b) {
       for (int u = 0; u < 2; ++u) { mbar_init(&misc->s_full[b][u], 1); mbar_init(&misc->p_full[b][u], 128); }
@@ -131,47 +133,12 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
       }
     }
   } else if (warp == WARP_S) {
-    // ------------------- S issuer: S_b(t) = Q_b K_b(sub-tile t)^T for both branches -------------------
-    // One thread, chosen by elect.sync, runs the whole loop.  (A thread picked by comparing the lane id
-    // issues tcgen05.mma about three times slower: 152 against 48 clocks per instruction, measured.)
-    // Sub-tile t goes to buffer t & 1, which is free once P_b V of sub-tile t-2 has completed, so the
-    // scores of the next sub-tile are ready while the softmax warpgroups work on the current one.
+    // (idle but for the TMEM allocation: completes the role warpgroup, whose registers go to the softmax warpgroups)
     reg_dec<REGS_ROLE>();
-    if (elect_one()) {
-      constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0, BF);   // both operands K-major
-      constexpr uint32_t HALF = (SUB * 128) >> 4;               // 64 rows of 128 bytes, in descriptor units
-      const int kd = args.d >> 4;                               // 16-deep MMA steps over the head dim: head dim 32 skips the zero padding
-      const uint32_t q1_lo = sdesc_lo(smem_u32(smem + OFF_Q1)), q2_lo = sdesc_lo(smem_u32(smem + OFF_Q2));
-      const uint32_t k_lo0 = sdesc_lo(smem_u32(smem + OFF_K));
-      bool ok = mbar_wait(&misc->bar_q, 0, abort_flag, 201);
-      int ks = 0;
-      uint32_t k_par = 0;
-      for (int j = 0; ok && j < nkv; ++j) {
-        const uint32_t k_lo = k_lo0 + ks * ((2 * K_BYTES) >> 4);
-        if (!mbar_wait(&misc->k_full[ks], k_par, abort_flag, 202, j)) break;
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-#pragma unroll
-          for (int br = 0; br < 2; ++br) {
-            if (j > 0) {
-              if (!mbar_wait(&misc->pv_done[br][u], (j - 1) & 1, abort_flag, 203 + u, j)) { ok = false; break; }
-            }
-            tc_fence_after();
-#pragma unroll
-            for (int k = 0; k < HD / 16; ++k)
-              if (k < kd)
-                mma_ss_lo(tmem_base + br * 128 + u * SUB, (br ? q2_lo : q1_lo) + k * 2,
-                          k_lo + br * (K_BYTES >> 4) + u * HALF + k * 2, IDESC_S, k > 0);
-            mma_commit(&misc->s_full[br][u]);
-          }
-          if (!ok) break;
-        }
-        mma_commit(&misc->k_empty[ks]);
-        if (++ks == KS) { ks = 0; k_par ^= 1; }
-      }
-    }
   } else if (warp == WARP_PV || warp == WARP_PV + 1) {
-    // ------------------- P V issuer of one branch: O_b += P_b(t) V(sub-tile t) -------------------
+    // ------------------- MMA issuer of one branch: S_b(t) = Q_b K_b(sub-tile t)^T, O_b += P_b(t) V(sub-tile t) -------------------
+    // One thread, chosen by elect.sync, runs the whole loop.  (A thread picked by comparing the lane id issues
+    // tcgen05.mma about three times slower: 152 against 48 clocks per instruction, measured.)
     reg_dec<REGS_ROLE>();
     if (elect_one()) {
       const int br = warp - WARP_PV;
@@ -179,11 +146,32 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
       constexpr uint32_t HALF = (SUB * 128) >> 4;
       const uint32_t v_lo0 = sdesc_lo(smem_u32(smem + OFF_V), V_BYTES / 2);
       const uint32_t t_o = tmem_base + T_O + br * 128, t_p = tmem_base + br * 128;
-      int vs = 0;
-      uint32_t v_par = 0;
-      bool ok = true;
+      // This warp issues S_b as well: S_b(t+2) goes into the buffer P_b(t) leaves, right behind P_b(t) V in the same
+      // thread's issue order -- no completion barrier and no second warp's wake-up between the two.
+      constexpr uint32_t IDESC_S = make_idesc(BM, SUB, 0, 0, BF);
+      const int kd = args.d >> 4;
+      const uint32_t q_lo = sdesc_lo(smem_u32(smem + (br ? OFF_Q2 : OFF_Q1)));
+      const uint32_t k_lo0 = sdesc_lo(smem_u32(smem + OFF_K));
+      auto issue_s = [&](uint32_t k_lo, int u) {
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          if (k < kd) mma_ss_lo(t_p + u * SUB, q_lo + k * 2, k_lo + br * (K_BYTES >> 4) + u * HALF + k * 2, IDESC_S, k > 0);
+        mma_commit(&misc->s_full[br][u]);
+      };
+      int vs = 0, ks = 0;
+      uint32_t v_par = 0, k_par = 0;
+      bool ok = mbar_wait(&misc->bar_q, 0, abort_flag, 201);
+      ok = ok && mbar_wait(&misc->k_full[0], 0, abort_flag, 202);
+      if (ok) {
+        tc_fence_after();
+        issue_s(k_lo0, 0);
+        issue_s(k_lo0, 1);
+        mma_commit(&misc->k_empty[0]);
+        if (++ks == KS) { ks = 0; k_par ^= 1; }
+      }
       for (int j = 0; ok && j < nkv; ++j) {
         const uint32_t v_lo = v_lo0 + vs * (V_BYTES >> 4);
+        const uint32_t k_lo = k_lo0 + ks * ((2 * K_BYTES) >> 4);       // key tile j+1
         if (!mbar_wait(&misc->v_full[vs], v_par, abort_flag, 205, j)) break;
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
@@ -193,6 +181,16 @@ diffattn_fwd64_kernel(const __grid_constant__ CUtensorMap tm_q1, const __grid_co
           for (int k = 0; k < SUB / 16; ++k)
             mma_ts_lo(t_o, t_p + u * SUB + k * 8, v_lo + u * HALF + k * (2048 >> 4), IDESC_O, (j > 0 || u > 0 || k > 0));
           mma_commit(&misc->pv_done[br][u]);
+          if (j + 1 < nkv) {
+            if (u == 0 && !mbar_wait(&misc->k_full[ks], k_par, abort_flag, 203, j)) { ok = false; break; }
+            tc_fence_after();
+            issue_s(k_lo, u);
+          }
+        }
+        if (!ok) break;
+        if (j + 1 < nkv) {
+          mma_commit(&misc->k_empty[ks]);
+          if (++ks == KS) { ks = 0; k_par ^= 1; }
         }
         mma_commit(&misc->v_empty[vs]);
         if (++vs == VS) { vs = 0; v_par ^= 1; }
