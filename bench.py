@@ -52,8 +52,8 @@ SPLIT = (64, 32, 4096, 64, 1.0, 0.5, 0.8, True)                     # batch-shar
 CPU_SMALL = (2, 16, 512, 32, 1.0, 0.5, 0.8, True)                   # the CPU-runnable shape: B=2 H=16 N=512 D=32, fp32
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from an ncu capture of this workload (its summary, with
 # the command, sits under profiles/); reported only for the workload and flags of that capture.
-NCU_TRAFFIC = {"workload": DEFAULT_WORKLOAD, "source": "ncu --set full capture of the kernels of commit 3a62820, summarised under profiles/",
-               "bytes": {"diffattn_fwd64_kernel": 306.7e6, "diffattn_bwd_pre_kernel": 255.9e6,
+NCU_TRAFFIC = {"workload": DEFAULT_WORKLOAD, "source": "ncu --set full capture of the kernels of commit 99934c7, summarised under profiles/",
+               "bytes": {"diffattn_fwd64_kernel": 306.9e6, "diffattn_bwd_pre_kernel": 255.9e6,
                          "diffattn_bwd_dkdv64_kernel": 380.0e6, "diffattn_bwd_dq64_kernel": 324.5e6}}
 METRIC = "diff-attn fwd+bwd TFLOP/s (credited 28*B*H*N^2*D), fp16"
 NOMINAL_TFLOPS = 2250.0
